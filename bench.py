@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF fused quant-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (config.workload = "llama3_8b_decode_layer_set_m1"): one step is
+one pass of the seven decode GEMVs of a Llama-3-8B-shaped layer at M=1 (six Q4_K
+projections and the Q6_K down_proj) over seeded synthetic GGUF blocks; the metric
+is packed quantized weight bytes streamed per second (GB/s), the numerator the
+reference's own bench uses (tests/bench_quant_matmul.cpp:5-10,207-209).
+
+  value     steps timed on the device with inputs resident in HBM; the K steps are
+            captured in one CUDA graph that rotates over weight replicas whose
+            combined size is several times the L2, so every launch streams cold weights.
+  e2e       the same step through the C-ABI with HOST activation/result buffers:
+            pinned host -> device copy of x, the seven GEMVs, device -> host read
+            of the outputs, every step inside the timed region.
+  roofline  the dominant kernel (Q4_K streaming GEMV on the gate/up shape) timed
+            alone with CUDA events; algorithmic bytes / duration vs the measured HBM peak.
+  extras    config 0 (single Q4_K 4096x4096 GEMV), config 2 (Q8_0, M=1..8), config 3
+            (prefill GEMM) and config 4 (row-sharded LM head + all-gather) numbers.
+
+With N > 1 (one process per GPU under torchrun) every rank runs its own replica of
+the decode layer set on its own activations (weak scaling, no data-path collective)
+and the ranks together run the row-sharded LM head, whose logits are all-gathered
+over NCCL; that number is reported under extras.lm_head.
+
+`--impl reference` times the reference's own CPU code for this path (its host
+decode + sequential FP32 dot from its parity tests, built into oracle/_ref; the
+oracle port when that library is absent) on all host cores, same metric and unit.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from brotensor_b200 import synth  # noqa: E402
+
+WORKLOAD = "llama3_8b_decode_layer_set_m1"
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=f,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- reference arm (CPU)
+
+def cpu_layer_set_pass(mat, threads, layers, acts):
+    nbytes = 0
+    for (name, fmt, N, K), W, x in zip(synth.LLAMA3_8B_LAYER_SET, layers, acts):
+        mat(fmt, W, x, threads=threads)
+        nbytes += W.size
+    return nbytes
+
+
+def run_cpu_arm(kind_wanted: str, steps: int, warmup: int, budget_s: float = 20.0):
+    """Times the CPU implementation on a bounded sample: whole layer-set passes."""
+    import oracle
+    ref = oracle.ref() if kind_wanted == "reference" else None
+    kind = "reference" if ref is not None else "port"
+    mat = ref.matmul if ref is not None else oracle.cpu().matmul
+    cores = os.cpu_count() or 1
+    layers = [synth.make_blocks(fmt, N, K, seed=100 + i) for i, (_, fmt, N, K) in enumerate(synth.LLAMA3_8B_LAYER_SET)]
+    acts = [synth.make_activations(1, K, seed=100 + i) for i, (_, _, _, K) in enumerate(synth.LLAMA3_8B_LAYER_SET)]
+    t0 = time.perf_counter()
+    nbytes = cpu_layer_set_pass(mat, cores, layers, acts)
+    one = time.perf_counter() - t0
+    # bounded: as many of the requested steps as fit in the time budget (at least one)
+    w = max(0, min(warmup, int(2.0 / max(one, 1e-9))))
+    k = max(1, min(steps, int(budget_s / max(one, 1e-9))))
+    for _ in range(w):
+        cpu_layer_set_pass(mat, cores, layers, acts)
+    t0 = time.perf_counter()
+    for _ in range(k):
+        cpu_layer_set_pass(mat, cores, layers, acts)
+    dt = time.perf_counter() - t0
+    gbs = nbytes * k / dt / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": f"{k} full passes of the 7-GEMV layer set ({nbytes} packed bytes each), {w} warm-up passes"}, k, w, dt / k * 1e3
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--replicas", type=int, default=8)
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    layer_bytes = sum(synth.packed_bytes(f, n, k) for _, f, n, k in synth.LLAMA3_8B_LAYER_SET)
+    config = {"workload": WORKLOAD, "gemvs_per_step": 7, "M": 1, "packed_weight_bytes_per_step": layer_bytes,
+              "l2": f"graph rotates over {args.replicas} weight replicas ({args.replicas * layer_bytes >> 20} MiB >> 126 MiB L2)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cb, k, w, ms = run_cpu_arm("reference", args.steps, max(args.warmup, 0))
+        print(json.dumps({
+            "impl": "reference", "metric": "q4k_q6k_decode_gemv_packed_weight_GBps", "value": cb["value"],
+            "unit": "GB/s", "n_gpus": args.gpus, "steps": k, "warmup": w, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config, "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}))
+        return
+
+    import torch
+    import torch.distributed as dist
+    from brotensor_b200 import ops
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    K_steps, W_steps, R = args.steps, max(args.warmup, 3), args.replicas
+    peaks = measured_peaks()
+
+    # ---- resident inputs: R replicas of the layer set (distinct seeds), activations per layer
+    t_setup = time.time()
+    host_layers = [synth.make_blocks(fmt, N, K, seed=100 + i + 1000 * rank)
+                   for i, (_, fmt, N, K) in enumerate(synth.LLAMA3_8B_LAYER_SET)]
+    replicas = []
+    for r in range(R):
+        rep = []
+        for W in host_layers:
+            t = torch.from_numpy(W).cuda()
+            if r:  # cheap decorrelation of replica contents, layout and statistics unchanged
+                t = torch.roll(t, shifts=r * 144 * 210 * 34)
+            rep.append(t.contiguous())
+        replicas.append(rep)
+    acts_h = [synth.make_activations(1, K, seed=100 + i) for i, (_, _, _, K) in enumerate(synth.LLAMA3_8B_LAYER_SET)]
+    acts = [torch.from_numpy(a).cuda() for a in acts_h]
+    outs = [torch.empty((1, N), dtype=torch.float32, device="cuda") for _, _, N, _ in synth.LLAMA3_8B_LAYER_SET]
+
+    def step(r):
+        for (name, fmt, N, K), W, x, y in zip(synth.LLAMA3_8B_LAYER_SET, replicas[r % R], acts, outs):
+            ops.gemv(fmt, W, x, N, out=y)
+
+    # parity gate on this rank's inputs before anything is timed
+    import oracle
+    step(0)
+    torch.cuda.synchronize()
+    cpu = oracle.cpu()
+    worst = 0.0
+    for (name, fmt, N, K), Wh, xh, y in zip(synth.LLAMA3_8B_LAYER_SET, host_layers, acts_h, outs):
+        if rank == 0 and name in ("k_proj", "o_proj", "down_proj"):
+            worst = max(worst, oracle.rel_l2(y.cpu().numpy(), cpu.matmul(fmt, Wh, xh, threads=os.cpu_count() or 1)))
+    assert worst < 2e-3, f"parity gate failed: rel-L2 {worst}"
+
+    for i in range(W_steps):
+        step(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    cap_stream = torch.cuda.Stream()
+    with torch.cuda.graph(g, stream=cap_stream):
+        for i in range(K_steps):
+            step(i)
+    g.replay()  # one untimed replay settles the graph upload
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # the timed region is repeated to give the clock sampler something to see; the
+    # reported time is the mean over identical K-step graphs
+    reps = 5
+    times = []
+    for _ in range(reps):
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms_total = float(np.median(times))
+    t = torch.tensor([ms_total], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_per_step = ms_total / K_steps
+    value = world * layer_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel: Q4_K streaming GEMV on the gate/up shape, timed alone
+    _, fmt_d, N_d, K_d = synth.LLAMA3_8B_LAYER_SET[4]
+    alg_bytes = synth.packed_bytes(fmt_d, N_d, K_d) + 4 * K_d + 4 * N_d
+    gd = torch.cuda.CUDAGraph()
+    n_dom = 64
+    with torch.cuda.graph(gd, stream=cap_stream):
+        for i in range(n_dom):
+            ops.gemv(fmt_d, replicas[i % R][4 + (i // R) % 2], acts[4], N_d, out=outs[4])
+    gd.replay()
+    torch.cuda.synchronize()
+    dts = []
+    for _ in range(10):
+        e0.record()
+        gd.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        dts.append(e0.elapsed_time(e1) / n_dom)
+    dom_ms = float(np.median(dts))
+    achieved = alg_bytes / (dom_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "gemv_stream_kernel<Q4_K> 14336x4096 M=1", "achieved": achieved,
+                "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "algorithmic_bytes_per_launch": alg_bytes,
+                "us_per_launch": dom_ms * 1e3}
+
+    # ---- e2e: host buffers through the C-ABI every step
+    acts_pin = [torch.from_numpy(a).pin_memory() for a in acts_h]
+    outs_pin = [torch.empty((1, N), dtype=torch.float32).pin_memory() for _, _, N, _ in synth.LLAMA3_8B_LAYER_SET]
+
+    def e2e_step(r):
+        for (name, fmt, N, K), W, xp, x, y, yp in zip(synth.LLAMA3_8B_LAYER_SET, replicas[r % R], acts_pin, acts, outs, outs_pin):
+            x.copy_(xp, non_blocking=True)
+            ops.gemv(fmt, W, x, N, out=y)
+            yp.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()  # the caller reads the step's result
+
+    for i in range(W_steps):
+        e2e_step(i)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(K_steps):
+        e2e_step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3) / K_steps
+    t = torch.tensor([e2e_ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    h2d = sum(4 * K for _, _, _, K in synth.LLAMA3_8B_LAYER_SET)
+    d2h = sum(4 * N for _, _, N, _ in synth.LLAMA3_8B_LAYER_SET)
+    e2e = {"value": world * layer_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "note": "weights stay resident (model state); activations and results cross PCIe every step"}
+    assert ops.device_status() == 0
+
+    extras = {}
+    if not args.no_extras:
+        try:
+            from brotensor_b200 import bench_extras
+            extras = bench_extras.run(rank, world, peaks, cap_stream)
+        except Exception as ex:  # extras never take the headline down
+            extras = {"error": repr(ex)}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_baseline, _, _, _ = run_cpu_arm("port", 10, 1, budget_s=12.0)
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "q4k_q6k_decode_gemv_packed_weight_GBps", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": K_steps, "warmup": W_steps, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "frac_of_hbm_peak": value / world / peaks["hbm_gbs"], "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "e2e": e2e, "gpu_launches": 7 * K_steps, "clocks": clocks, "extras": extras,
+            "setup_s": round(time.time() - t_setup, 1)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

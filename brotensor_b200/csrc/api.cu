@@ -1,0 +1,257 @@
+// C-ABI entry points (include/b200q.h): argument validation, routing between
+// kernels and error reporting. No compute happens on the host and nothing here
+// falls back to a CPU path.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace b200q {
+
+int launch_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows, int K, cudaStream_t st);
+int launch_gemv_simple(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
+                       int M, int N, int K, cudaStream_t st);
+int launch_gemv_stream(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
+                       int M, int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken);
+void stream_set_option(int which, int value);
+int stream_get_option(int which);
+size_t gemm_tc_workspace_bytes(int fmt, int x_dtype, int M, int N, int K);
+int launch_gemm_tc(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
+                   int N, int K, void* ws, size_t ws_bytes, int sms, int* status, cudaStream_t st, bool* taken);
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+// One status word per device, living in the module's global memory.
+__device__ int g_dev_status;
+
+constexpr int kMaxDev = 64;
+struct DevInfo {
+    bool ready = false;
+    int sms = 0;
+    size_t smem_optin = 0;
+    int* status = nullptr;
+    std::atomic<unsigned long long> tc_calls[3];
+};
+static DevInfo g_dev[kMaxDev];
+static std::mutex g_dev_mu;
+
+static int fmt_slot(int fmt) { return fmt == kQ4_K ? 0 : fmt == kQ6_K ? 1 : fmt == kQ8_0 ? 2 : -1; }
+
+static int dev_info(DevInfo** out) {
+    int dev = -1;
+    B200Q_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDev) return fail(B200Q_ERR_CUDA, "device ordinal %d out of range", dev);
+    DevInfo& d = g_dev[dev];
+    if (!d.ready) {
+        std::lock_guard<std::mutex> lk(g_dev_mu);
+        if (!d.ready) {
+            int sms = 0, smem = 0;
+            B200Q_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            B200Q_CUDA_TRY(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+            void* p = nullptr;
+            B200Q_CUDA_TRY(cudaGetSymbolAddress(&p, g_dev_status));
+            d.sms = sms;
+            d.smem_optin = (size_t)smem;
+            d.status = static_cast<int*>(p);
+            for (auto& c : d.tc_calls) c.store(0);
+            d.ready = true;
+        }
+    }
+    *out = &d;
+    return B200Q_OK;
+}
+
+int* device_status_word(int dev) { return (dev >= 0 && dev < kMaxDev && g_dev[dev].ready) ? g_dev[dev].status : nullptr; }
+
+static int g_opt_gemv_path = 0;
+static int g_opt_gemm_path = 0;
+
+static bool dt_ok(int dt) { return dt == B200Q_DT_F32 || dt == B200Q_DT_F16 || dt == B200Q_DT_BF16; }
+static int dt_size(int dt) { return dt == B200Q_DT_F32 ? 4 : 2; }
+static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+static int check_linear_args(const char* op, int fmt, const void* W, const void* X, int x_dtype, const void* Y,
+                             int y_dtype, int M, int N, int K) {
+    const int be = b200q_block_elems(fmt);
+    if (!be) return fail(B200Q_ERR_BAD_ARG, "%s: unknown block format %d", op, fmt);
+    if (!dt_ok(x_dtype) || !dt_ok(y_dtype)) return fail(B200Q_ERR_BAD_ARG, "%s: unknown dtype (x %d, y %d)", op, x_dtype, y_dtype);
+    if (M < 0 || N < 0 || K <= 0) return fail(B200Q_ERR_BAD_ARG, "%s: negative shape (M %d, N %d, K %d)", op, M, N, K);
+    if (K % be) return fail(B200Q_ERR_BAD_ARG, "%s: K (%d) must be a multiple of %d", op, K, be);
+    if (M == 0 || N == 0) return B200Q_OK;
+    if (!W || !X || !Y) return fail(B200Q_ERR_BAD_ARG, "%s: null pointer", op);
+    if (!aligned(W, fmt == kQ4_K ? 4 : 2)) return fail(B200Q_ERR_BAD_ARG, "%s: W is not aligned to its block header", op);
+    if (!aligned(X, 16)) return fail(B200Q_ERR_BAD_ARG, "%s: X must be 16-byte aligned", op);
+    if (!aligned(Y, (size_t)dt_size(y_dtype))) return fail(B200Q_ERR_BAD_ARG, "%s: Y is not aligned to its element size", op);
+    return B200Q_OK;
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+int b200q_abi_version(void) { return 1; }
+
+const char* b200q_status_str(int s) {
+    switch (s) {
+        case B200Q_OK: return "ok";
+        case B200Q_ERR_BAD_ARG: return "bad argument";
+        case B200Q_ERR_UNSUPPORTED: return "unsupported shape or layout";
+        case B200Q_ERR_CUDA: return "CUDA error";
+        case B200Q_ERR_TIMEOUT: return "device-side wait timed out";
+        case B200Q_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    }
+    return "unknown status";
+}
+
+const char* b200q_last_error(void) { return g_err; }
+
+int b200q_block_elems(int fmt) { return fmt == kQ8_0 ? 32 : (fmt == kQ4_K || fmt == kQ6_K) ? 256 : 0; }
+int b200q_block_bytes(int fmt) { return fmt == kQ8_0 ? 34 : fmt == kQ4_K ? 144 : fmt == kQ6_K ? 210 : 0; }
+size_t b200q_packed_bytes(int fmt, int64_t rows, int K) {
+    const int be = b200q_block_elems(fmt);
+    if (!be || rows < 0 || K < 0 || K % be) return 0;
+    return (size_t)rows * (size_t)(K / be) * (size_t)b200q_block_bytes(fmt);
+}
+
+int b200q_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows, int K, void* stream) {
+    const int be = b200q_block_elems(fmt);
+    if (!be) return fail(B200Q_ERR_BAD_ARG, "dequant: unknown block format %d", fmt);
+    if (!dt_ok(out_dtype)) return fail(B200Q_ERR_BAD_ARG, "dequant: unknown output dtype %d", out_dtype);
+    if (rows < 0 || K <= 0 || K % be) return fail(B200Q_ERR_BAD_ARG, "dequant: K (%d) must be a positive multiple of %d", K, be);
+    if (rows == 0) return B200Q_OK;
+    if (!W || !out) return fail(B200Q_ERR_BAD_ARG, "dequant: null pointer");
+    if (!aligned(W, fmt == kQ4_K ? 4 : 2)) return fail(B200Q_ERR_BAD_ARG, "dequant: W is not aligned to its block header");
+    if (!aligned(out, 16)) return fail(B200Q_ERR_BAD_ARG, "dequant: output must be 16-byte aligned");
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    return launch_dequant(fmt, W, out, out_dtype, rows, K, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
+               int N, int K, void* stream) {
+    if (int rc = check_linear_args("gemv", fmt, W, X, x_dtype, Y, y_dtype, M, N, K)) return rc;
+    if (M > 8) return fail(B200Q_ERR_UNSUPPORTED, "gemv: M (%d) exceeds 8 activation rows; use b200q_gemm", M);
+    if (M == 0 || N == 0) return B200Q_OK;
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (g_opt_gemv_path != 1) {
+        bool taken = false;
+        if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->smem_optin, d->status, st, &taken))
+            return rc;
+        if (taken) return B200Q_OK;
+        if (g_opt_gemv_path == 2)
+            return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the streaming kernel", M, N, K, fmt);
+    }
+    return launch_gemv_simple(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
+}
+
+size_t b200q_gemm_workspace_bytes(int fmt, int x_dtype, int M, int N, int K) {
+    if (!b200q_block_elems(fmt) || M <= 0 || N <= 0 || K <= 0) return 0;
+    return gemm_tc_workspace_bytes(fmt, x_dtype, M, N, K);
+}
+
+int b200q_gemm(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
+               int N, int K, void* ws, size_t ws_bytes, void* stream) {
+    if (int rc = check_linear_args("gemm", fmt, W, X, x_dtype, Y, y_dtype, M, N, K)) return rc;
+    if (M == 0 || N == 0) return B200Q_OK;
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (g_opt_gemm_path != 1) {
+        bool taken = false;
+        if (int rc = launch_gemm_tc(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, ws, ws_bytes, d->sms, d->status, st, &taken))
+            return rc;
+        if (taken) {
+            d->tc_calls[fmt_slot(fmt)].fetch_add(1);
+            return B200Q_OK;
+        }
+        if (g_opt_gemm_path == 2)
+            return fail(B200Q_ERR_UNSUPPORTED, "gemm: shape (M %d, N %d, K %d, fmt %d) is outside the tensor-core kernel", M, N, K, fmt);
+    }
+    // Shapes the tensor-core kernel does not take: passes of up to 8 activation rows
+    // through the decode GEMV (W is re-read once per pass).
+    const size_t xs = (size_t)dt_size(x_dtype) * K, ys = (size_t)dt_size(y_dtype) * N;
+    for (int m0 = 0; m0 < M; m0 += 8) {
+        const int mm = M - m0 < 8 ? M - m0 : 8;
+        if (int rc = b200q_gemv(fmt, W, static_cast<const char*>(X) + xs * m0, x_dtype, bias,
+                                static_cast<char*>(Y) + ys * m0, y_dtype, mm, N, K, stream))
+            return rc;
+    }
+    return B200Q_OK;
+}
+
+int b200q_linear(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
+                 int N, int K, void* ws, size_t ws_bytes, void* stream) {
+    if (M <= 8) return b200q_gemv(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, stream);
+    return b200q_gemm(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, ws, ws_bytes, stream);
+}
+
+unsigned long long b200q_tc_calls_consume(int fmt) {
+    const int s = fmt_slot(fmt);
+    int dev = -1;
+    if (s < 0 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return 0;
+    return g_dev[dev].tc_calls[s].exchange(0);
+}
+unsigned long long brotensor_q4k_wmma_calls_consume(void) { return b200q_tc_calls_consume(kQ4_K); }
+unsigned long long brotensor_q6k_wmma_calls_consume(void) { return b200q_tc_calls_consume(kQ6_K); }
+unsigned long long brotensor_q8_0_wmma_calls_consume(void) { return b200q_tc_calls_consume(kQ8_0); }
+
+int b200q_device_status(int* status_out) {
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    B200Q_CUDA_TRY(cudaDeviceSynchronize());
+    int v = 0;
+    B200Q_CUDA_TRY(cudaMemcpy(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (v != 0) {
+        const int zero = 0;
+        B200Q_CUDA_TRY(cudaMemcpy(d->status, &zero, sizeof(int), cudaMemcpyHostToDevice));
+    }
+    if (status_out) *status_out = v;
+    if (v != 0) return fail(B200Q_ERR_TIMEOUT, "a kernel's bounded wait ran out (device status %d)", v);
+    return B200Q_OK;
+}
+
+int b200q_set_option(const char* key, int value) {
+    if (!key) return fail(B200Q_ERR_BAD_ARG, "set_option: null key");
+    if (!strcmp(key, "gemv_path")) g_opt_gemv_path = value;
+    else if (!strcmp(key, "gemm_path")) g_opt_gemm_path = value;
+    else if (!strcmp(key, "gemv_stages")) stream_set_option(0, value);
+    else if (!strcmp(key, "pdl")) stream_set_option(1, value);
+    else if (!strcmp(key, "gemv_stage_kb")) stream_set_option(2, value);
+    else if (!strcmp(key, "gemv_grid")) stream_set_option(3, value);
+    else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
+    return B200Q_OK;
+}
+int b200q_get_option(const char* key, int* out) {
+    if (!key || !out) return fail(B200Q_ERR_BAD_ARG, "get_option: null argument");
+    if (!strcmp(key, "gemv_path")) *out = g_opt_gemv_path;
+    else if (!strcmp(key, "gemm_path")) *out = g_opt_gemm_path;
+    else if (!strcmp(key, "gemv_stages")) *out = stream_get_option(0);
+    else if (!strcmp(key, "pdl")) *out = stream_get_option(1);
+    else if (!strcmp(key, "gemv_stage_kb")) *out = stream_get_option(2);
+    else if (!strcmp(key, "gemv_grid")) *out = stream_get_option(3);
+    else return fail(B200Q_ERR_BAD_ARG, "get_option: unknown key '%s'", key);
+    return B200Q_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,96 @@
+"""Thin torch-tensor front end of the C-ABI, used by the tests and the benchmark.
+
+Argument meaning follows brotensor's ops (include/brotensor/ops/quant.h): W is a
+(N, K) quantized weight given as its raw GGUF block bytes, X is (M, K), the
+result is (M, N). torch only supplies device memory and the current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _capi as capi
+from .synth import BLOCK_BYTES, BLOCK_ELEMS
+
+_DT = {torch.float32: capi.F32, torch.float16: capi.F16, torch.bfloat16: capi.BF16}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check_w(fmt: int, W: torch.Tensor, N: int, K: int) -> None:
+    if W.dtype != torch.uint8 or not W.is_cuda or not W.is_contiguous():
+        raise ValueError("W must be a contiguous CUDA uint8 tensor holding raw GGUF blocks")
+    if K % BLOCK_ELEMS[fmt]:
+        raise ValueError(f"K ({K}) must be a multiple of {BLOCK_ELEMS[fmt]}")
+    need = N * (K // BLOCK_ELEMS[fmt]) * BLOCK_BYTES[fmt]
+    if W.numel() != need:
+        raise ValueError(f"W holds {W.numel()} bytes, ({N}, {K}) needs {need}")
+
+
+def dequant(fmt: int, W: torch.Tensor, N: int, K: int, out_dtype=torch.float16) -> torch.Tensor:
+    _check_w(fmt, W, N, K)
+    out = torch.empty((N, K), dtype=out_dtype, device=W.device)
+    with torch.cuda.device(W.device):
+        capi.check(capi.lib().b200q_dequant(fmt, W.data_ptr(), out.data_ptr(), _DT[out_dtype], N, K, _stream()))
+    return out
+
+
+def _linear(entry: str, fmt, W, X, N, bias, out, out_dtype, ws):
+    if X.dim() == 1:
+        X = X.unsqueeze(0)
+    M, K = X.shape
+    _check_w(fmt, W, N, K)
+    if not X.is_contiguous():
+        raise ValueError("X must be contiguous")
+    if bias is not None and (bias.dtype != X.dtype or bias.numel() != N):
+        raise ValueError("bias must have N elements of X's dtype")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or (torch.float16 if X.dtype == torch.float16 else torch.float32),
+                          device=X.device)
+    L = capi.lib()
+    bptr = bias.data_ptr() if bias is not None else None
+    with torch.cuda.device(W.device):
+        if entry == "gemv":
+            rc = L.b200q_gemv(fmt, W.data_ptr(), X.data_ptr(), _DT[X.dtype], bptr, out.data_ptr(), _DT[out.dtype],
+                              M, N, K, _stream())
+        else:
+            need = L.b200q_gemm_workspace_bytes(fmt, _DT[X.dtype], M, N, K)
+            if ws is None and need:
+                ws = torch.empty(need, dtype=torch.uint8, device=X.device)
+            f = L.b200q_gemm if entry == "gemm" else L.b200q_linear
+            rc = f(fmt, W.data_ptr(), X.data_ptr(), _DT[X.dtype], bptr, out.data_ptr(), _DT[out.dtype], M, N, K,
+                   ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, _stream())
+    capi.check(rc)
+    return out
+
+
+def gemv(fmt, W, X, N, bias=None, out=None, out_dtype=None):
+    """Y(M,N) = X(M,K) @ decode(W).T (+bias), 1 <= M <= 8."""
+    return _linear("gemv", fmt, W, X, N, bias, out, out_dtype, None)
+
+
+def gemm(fmt, W, X, N, bias=None, out=None, out_dtype=None, ws=None):
+    """Prefill GEMM on the tensor cores, any M."""
+    return _linear("gemm", fmt, W, X, N, bias, out, out_dtype, ws)
+
+
+def linear(fmt, W, X, N, bias=None, out=None, out_dtype=None, ws=None):
+    """Routing of the batched ops: M <= 8 -> gemv, else gemm."""
+    return _linear("linear", fmt, W, X, N, bias, out, out_dtype, ws)
+
+
+def set_option(key: str, value: int) -> None:
+    capi.check(capi.lib().b200q_set_option(key.encode(), value))
+
+
+def device_status() -> int:
+    """Synchronises; returns 0 or raises if a kernel's bounded wait ran out."""
+    import ctypes
+    v = ctypes.c_int(0)
+    capi.check(capi.lib().b200q_device_status(ctypes.byref(v)))
+    return v.value
+
+
+def tc_calls_consume(fmt: int) -> int:
+    return int(capi.lib().b200q_tc_calls_consume(fmt))

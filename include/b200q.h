@@ -1,0 +1,134 @@
+/*
+ * b200q — C-ABI of the B200 (sm_100a) GGUF fused quant-matmul backend.
+ *
+ * This is the whole boundary between a host library and the CUDA kernels:
+ * plain pointers, sizes and a stream handle, no C++ or framework types. The
+ * C++ host layer in brotensor_b200/host (Tensor / Device dispatch with
+ * brotensor's op signatures) and the Python harness both sit on top of it.
+ *
+ * Every entry point works on the CUDA device that is current on the calling
+ * thread (brotensor's dispatcher selects it before calling the backend slot,
+ * src/dispatch.cpp:73-81), enqueues on `stream` (a cudaStream_t; NULL is the
+ * legacy default stream) and returns without synchronising. Pointers are
+ * device pointers unless stated otherwise. No entry point allocates or frees
+ * device memory.
+ *
+ * Return value: B200Q_OK or one of the B200Q_ERR_* codes; b200q_last_error()
+ * gives the message of the calling thread's most recent failure. There is no
+ * CPU fallback: without a usable CUDA device every compute call fails with
+ * B200Q_ERR_CUDA.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes. */
+#define B200Q_OK 0
+#define B200Q_ERR_BAD_ARG 1      /* null pointer, negative size, unknown format or dtype */
+#define B200Q_ERR_UNSUPPORTED 2  /* legal arguments outside what the kernels cover */
+#define B200Q_ERR_CUDA 3         /* a CUDA runtime call or launch failed */
+#define B200Q_ERR_TIMEOUT 4      /* a bounded device-side wait ran out (see b200q_device_status) */
+#define B200Q_ERR_WORKSPACE 5    /* workspace missing, misaligned or too small */
+
+/* Block formats; the values are brotensor's Dtype tags (include/brotensor/tensor.h:26-47). */
+#define B200Q_FMT_Q8_0 14 /*  32 elements /  34 B: fp16 d, int8 qs[32]                       */
+#define B200Q_FMT_Q4_K 22 /* 256 elements / 144 B: fp16 d, fp16 dmin, u8 scales[12], u8 qs[128] */
+#define B200Q_FMT_Q6_K 24 /* 256 elements / 210 B: u8 ql[128], u8 qh[64], i8 scales[16], fp16 d */
+
+/* Activation / output element types; the values are brotensor's Dtype tags. */
+#define B200Q_DT_F32 0
+#define B200Q_DT_F16 1
+#define B200Q_DT_BF16 4
+
+/* Library facts (no device needed). */
+int b200q_abi_version(void);
+const char* b200q_status_str(int status);
+const char* b200q_last_error(void);
+int b200q_block_elems(int fmt);                          /* 0 for an unknown format */
+int b200q_block_bytes(int fmt);                          /* 0 for an unknown format */
+size_t b200q_packed_bytes(int fmt, int64_t rows, int K); /* 0 if K is not a multiple of the block */
+
+/*
+ * Block decode. W: rows x K quantized, row-major [rows][K/elems][block bytes];
+ * out: rows x K of out_dtype. The FP32 result is the exact decoded value and
+ * the 16-bit results are its round-to-nearest-even, i.e. bit-identical to the
+ * reference's host decode.
+ * Replaces dequant_q4k_to_fp16 / dequant_q6k_to_fp16 / dequant_q8_0_to_fp16
+ * (include/brotensor/ops/quant.h:45,73,100; src/cuda/q4k.cu:297-324,
+ * q6k.cu:232-259, q8_0.cu:195-222). Rows beyond 65535 are handled.
+ */
+int b200q_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows, int K, void* stream);
+
+/*
+ * Decode GEMV for 1..8 activation rows:
+ *   Y(M,N) = X(M,K) * decode(W(N,K))^T (+ bias(N)),   FP32 accumulation.
+ * X is M x K of x_dtype (row-major, leading dimension K), bias is N elements
+ * of x_dtype or NULL, Y is M x N of y_dtype (leading dimension N). The weight
+ * is streamed from HBM once whatever M is.
+ * Replaces linear_forward_q4k_fp16 / _q6k_ / _q8_0_ (quant.h:52,79,105;
+ * src/cuda/q4k.cu:326-362, q6k.cu:261-297, q8_0.cu:224-259) and the small-B
+ * branch of the batched forms (q4k.cu:413-418, which re-reads W per row).
+ */
+int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
+               int M, int N, int K, void* stream);
+
+/*
+ * Prefill GEMM on the tensor cores, any M >= 1:
+ *   Y(M,N) = X(M,K) * decode(W(N,K))^T (+ bias(N)),   FP16 operands, FP32 accumulation.
+ * `ws` is caller-owned scratch of at least b200q_gemm_workspace_bytes() bytes,
+ * 256-byte aligned (it holds the activations converted to the operand layout);
+ * it may be NULL when that size is 0. Calls that share a workspace must be
+ * ordered on one stream.
+ * Replaces the tensor-core branch of linear_forward_batched_q4k_fp16 / _q6k_ /
+ * _q8_0_ (quant.h:61,87,111; src/cuda/q4k_wmma.cu:56-332, q6k_wmma.cu:62-377,
+ * q8_0_wmma.cu:54-309).
+ */
+size_t b200q_gemm_workspace_bytes(int fmt, int x_dtype, int M, int N, int K);
+int b200q_gemm(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
+               int M, int N, int K, void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * Routing used by the batched ops: M <= 8 goes to b200q_gemv, larger M to
+ * b200q_gemm (brotensor routes B >= 4 to its WMMA kernel, q4k_wmma.cu:320-326).
+ */
+int b200q_linear(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
+                 int M, int N, int K, void* ws, size_t ws_bytes, void* stream);
+
+/*
+ * How many tensor-core GEMM launches were made for `fmt` on this thread's
+ * device since the last call; reading resets the count. The three named
+ * aliases are the hooks brotensor's parity tests link against
+ * (src/cuda/q4k_wmma.cu:337-348, q6k_wmma.cu:381-392, q8_0_wmma.cu:313-324).
+ */
+unsigned long long b200q_tc_calls_consume(int fmt);
+unsigned long long brotensor_q4k_wmma_calls_consume(void);
+unsigned long long brotensor_q6k_wmma_calls_consume(void);
+unsigned long long brotensor_q8_0_wmma_calls_consume(void);
+
+/*
+ * Device-side status word of the current device: 0, or a code left by a kernel
+ * whose bounded wait ran out (the kernel stops waiting and returns; it never
+ * traps). Synchronises the device; reading resets the word.
+ */
+int b200q_device_status(int* status_out);
+
+/*
+ * Tuning knobs for benchmarks and tests (process-wide, not thread-safe):
+ *   "gemv_path"   0 = automatic, 1 = force the plain-load kernel, 2 = force the streaming kernel
+ *   "gemv_stages" ring depth of the streaming kernel (2..8)
+ *   "pdl"         1 = launch GEMV kernels with programmatic dependent launch
+ * Returns B200Q_ERR_BAD_ARG for an unknown key.
+ */
+int b200q_set_option(const char* key, int value);
+int b200q_get_option(const char* key, int* value_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

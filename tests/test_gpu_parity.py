@@ -1,0 +1,238 @@
+"""GPU parity tests: every result of the CUDA library (through the C-ABI) against
+the CPU oracle on the same seeded inputs and against the committed golden vectors.
+
+Tolerances. Block decode: bit-exact (FP32, and FP16/BF16 = round-to-nearest-even
+of it). Matmul: relative L2 error <= 2e-3 against the FP32 host reference — the
+bound the benchmark specification states — plus the reference tests' own absolute
+bounds (5e-2 / 1e-1) on their own cases.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from brotensor_b200 import ops, synth
+
+pytestmark = pytest.mark.gpu
+
+REL_L2 = 2e-3
+FMTS = [(oracle.Q4_K, "q4k"), (oracle.Q6_K, "q6k"), (oracle.Q8_0, "q8_0")]
+TORCH_DT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def host_f32(t):
+    return t.float().cpu().numpy()
+
+
+def as_dtype_np(x, name):
+    """fp32 array rounded to the activation dtype and back (what the kernel sees)."""
+    t = torch.from_numpy(np.ascontiguousarray(x)).to(TORCH_DT[name])
+    return t, t.float().numpy()
+
+
+@pytest.fixture(autouse=True)
+def _clean_state():
+    ops.set_option("gemv_path", 0)
+    yield
+    ops.set_option("gemv_path", 0)
+    assert ops.device_status() == 0
+
+
+# ---------------------------------------------------------------- block decode
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_dequant_bit_exact_golden(fmt, name, golden):
+    g = golden(name + "_parity")
+    W = dev(g["A_W"])
+    f32 = ops.dequant(fmt, W, 64, 256, torch.float32).cpu().numpy()
+    assert np.array_equal(f32.view(np.uint32), g["A_Wdeq"].view(np.uint32))
+    f16 = ops.dequant(fmt, W, 64, 256, torch.float16).cpu().numpy()
+    assert np.array_equal(f16.view(np.uint16), g["A_Wdeq_fp16"])
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("rows,K", [(1, 256), (3, 512), (257, 1024), (148 * 16 + 5, 2048)])
+def test_dequant_bit_exact_synthetic(fmt, name, rows, K, cpu_oracle):
+    Wh = synth.make_blocks(fmt, rows, K, seed=rows + K)
+    W = dev(Wh)
+    want32 = cpu_oracle.dequant_f32(fmt, Wh, rows, K)
+    got32 = ops.dequant(fmt, W, rows, K, torch.float32).cpu().numpy()
+    assert np.array_equal(got32.view(np.uint32), want32.view(np.uint32))
+    got16 = ops.dequant(fmt, W, rows, K, torch.float16).cpu().numpy()
+    assert np.array_equal(got16.view(np.uint16), cpu_oracle.dequant_16(fmt, Wh, rows, K, 1))
+    gotbf = ops.dequant(fmt, W, rows, K, torch.bfloat16).view(torch.int16).cpu().numpy()
+    assert np.array_equal(gotbf.view(np.uint16), cpu_oracle.dequant_16(fmt, Wh, rows, K, 4))
+
+
+def test_dequant_rows_beyond_grid_y_limit(cpu_oracle):
+    """70 000 one-block rows: the reference regression case for gridDim.y > 65535
+    (tests/test_q8_0_parity.cpp:296-361): full decode == decode of the two halves."""
+    rows, K = 70000, 32
+    Wh = synth.make_blocks(oracle.Q8_0, rows, K, seed=9)
+    full = ops.dequant(oracle.Q8_0, dev(Wh), rows, K).cpu().numpy()
+    h0 = rows // 2
+    a = ops.dequant(oracle.Q8_0, dev(Wh[: h0 * 34]), h0, K).cpu().numpy()
+    b = ops.dequant(oracle.Q8_0, dev(Wh[h0 * 34:]), rows - h0, K).cpu().numpy()
+    assert np.array_equal(full.view(np.uint16), np.concatenate([a, b]).view(np.uint16))
+    assert np.array_equal(full.view(np.uint16), cpu_oracle.dequant_16(oracle.Q8_0, Wh, rows, K, 1))
+
+
+# ---------------------------------------------------------------- reference test cases
+
+@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_reference_parity_cases(fmt, name, path, golden):
+    """Cases B, C, D, E, F, G of the reference parity tests with FP16 activations
+    and FP16 outputs (the reference contract) and the reference's absolute bounds."""
+    ops.set_option("gemv_path", path)
+    g = golden(name + "_parity")
+    W = dev(g["A_W"])
+    x = dev(g["B_x"]).half()
+    y = ops.gemv(fmt, W, x, 64)
+    assert y.dtype == torch.float16 and tuple(y.shape) == (1, 64)
+    assert np.abs(host_f32(y)[0] - g["B_y"]).max() < 5e-2
+    yb = ops.gemv(fmt, W, x, 64, bias=dev(g["C_bias"]).half())
+    assert np.abs(host_f32(yb)[0] - g["C_y"]).max() < 5e-2
+    Y = ops.linear(fmt, W, dev(g["D_X"]).half(), 64)
+    assert np.abs(host_f32(Y) - g["D_Y"]).max() < 5e-2
+    for label, tol in (("E", 5e-2), ("F", 5e-2), ("G", 1e-1)):
+        X = g[label + "_X"]
+        n = g[label + "_Y"].shape[1]
+        Y = ops.linear(fmt, dev(g[label + "_W"]), dev(X).half(), n)
+        assert np.abs(host_f32(Y) - g[label + "_Y"]).max() < tol
+        # and the tight bound with FP32 activations / outputs
+        Y32 = ops.linear(fmt, dev(g[label + "_W"]), dev(X), n)
+        assert oracle.rel_l2(host_f32(Y32), g[label + "_Y"]) < REL_L2
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_prefill_lcg_case(fmt, name, golden):
+    """tests/test_quant_prefill_parity.cpp: arbitrary block bytes, B=16, with and without bias."""
+    g = golden("prefill_lcg")
+    W = dev(g[name + "_W"])
+    X = torch.from_numpy(g[name + "_X_fp16"].view(np.float16)).cuda()
+    b = torch.from_numpy(g[name + "_bias_fp16"].view(np.float16)).cuda()
+    Y = ops.linear(fmt, W, X, 96)
+    Yb = ops.linear(fmt, W, X, 96, bias=b)
+    for got, want in ((Y, g[name + "_Y"]), (Yb, g[name + "_Y_bias"])):
+        err = np.abs(host_f32(got) - want)
+        assert np.all(err <= 3e-2 + 5e-2 * np.abs(want))  # the reference test's bound (:133-145)
+    Y32 = ops.linear(fmt, W, X, 96, out_dtype=torch.float32)
+    assert oracle.rel_l2(host_f32(Y32), g[name + "_Y"]) < REL_L2
+
+
+# ---------------------------------------------------------------- decode GEMV vs oracle
+
+SHAPES = {
+    oracle.Q4_K: [(1, 256), (7, 512), (17, 1024), (100, 4096), (1000, 2048), (148 * 16 + 3, 512)],
+    oracle.Q6_K: [(1, 256), (7, 2048), (17, 4096), (100, 6144), (1000, 2048), (148 * 16 + 3, 2048), (9, 768)],
+    oracle.Q8_0: [(1, 32), (7, 256), (17, 1024), (100, 4096), (1000, 2048), (148 * 16 + 3, 512), (9, 96)],
+}
+
+
+@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8])
+def test_gemv_matches_oracle(fmt, name, M, path, cpu_oracle):
+    ops.set_option("gemv_path", path)
+    for N, K in SHAPES[fmt]:
+        Wh = synth.make_blocks(fmt, N, K, seed=N * 7 + K)
+        Xh = synth.make_activations(M, K, seed=N + K + M)
+        want = cpu_oracle.matmul(fmt, Wh, Xh, threads=8)
+        got = ops.gemv(fmt, dev(Wh), dev(Xh), N)
+        assert got.dtype == torch.float32
+        e = oracle.rel_l2(host_f32(got), want)
+        assert e < REL_L2, f"N={N} K={K} M={M} rel_l2={e}"
+
+
+@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("xdt,ydt", [("f16", "f16"), ("bf16", "f32"), ("f32", "bf16"), ("bf16", "bf16"), ("f16", "f32")])
+def test_gemv_dtypes_and_bias(fmt, name, xdt, ydt, path, cpu_oracle):
+    ops.set_option("gemv_path", path)
+    N, K, M = 333, 4096 if fmt != oracle.Q6_K else 2048, 3
+    Wh = synth.make_blocks(fmt, N, K, seed=21)
+    xt, xr = as_dtype_np(synth.make_activations(M, K, seed=22), xdt)
+    bt, br = as_dtype_np(synth.make_activations(1, N, seed=23)[0], xdt)
+    want = cpu_oracle.matmul(fmt, Wh, xr, bias=br, threads=8)
+    got = ops.gemv(fmt, dev(Wh), xt.cuda(), N, bias=bt.cuda(), out_dtype=TORCH_DT[ydt])
+    assert got.dtype == TORCH_DT[ydt]
+    # the output rounding of a 16-bit Y is part of the contract: allow its half-ulp on top
+    tol = REL_L2 + (2.0 ** -9 if ydt == "bf16" else 2.0 ** -12 if ydt == "f16" else 0.0)
+    assert oracle.rel_l2(host_f32(got), want) < tol
+
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+def test_stream_and_plain_kernels_agree(fmt, name):
+    """Two independent kernels, same inputs: agreement far inside the tolerance."""
+    N, K, M = 2500, 4096 if fmt != oracle.Q6_K else 6144, 8
+    W = dev(synth.make_blocks(fmt, N, K, seed=31))
+    X = dev(synth.make_activations(M, K, seed=32))
+    ops.set_option("gemv_path", 1)
+    a = ops.gemv(fmt, W, X, N)
+    ops.set_option("gemv_path", 2)
+    b = ops.gemv(fmt, W, X, N)
+    assert oracle.rel_l2(host_f32(b), host_f32(a)) < 1e-4
+
+
+def test_gemv_is_deterministic_and_linear():
+    fmt, N, K = oracle.Q4_K, 4096, 4096
+    W = dev(synth.make_blocks(fmt, N, K, seed=41))
+    x1 = dev(synth.make_activations(1, K, seed=42))
+    x2 = dev(synth.make_activations(1, K, seed=43))
+    a = ops.gemv(fmt, W, x1, N)
+    assert torch.equal(a, ops.gemv(fmt, W, x1, N))
+    s = ops.gemv(fmt, W, x1 + x2, N)
+    assert oracle.rel_l2(host_f32(s), host_f32(a + ops.gemv(fmt, W, x2, N))) < 1e-3
+    # stacked rows give the same answers as single rows
+    both = ops.gemv(fmt, W, torch.cat([x1, x2]), N)
+    assert oracle.rel_l2(host_f32(both[0]), host_f32(a[0])) < 1e-5
+
+
+# ---------------------------------------------------------------- benchmark configurations at full size
+
+def test_config0_q4k_4096(cpu_oracle):
+    fmt, N, K = oracle.Q4_K, 4096, 4096
+    Wh = synth.make_blocks(fmt, N, K, seed=0)
+    Xh = synth.make_activations(1, K, seed=0)
+    want, want64 = cpu_oracle.matmul(fmt, Wh, Xh, threads=8, want_f64=True)
+    got = host_f32(ops.gemv(fmt, dev(Wh), dev(Xh), N))
+    assert oracle.rel_l2(got, want) < REL_L2
+    assert oracle.rel_l2(got, want64) < REL_L2
+
+
+def test_config1_llama_layer_set(cpu_oracle):
+    for i, (lname, fmt, N, K) in enumerate(synth.LLAMA3_8B_LAYER_SET):
+        Wh = synth.make_blocks(fmt, N, K, seed=100 + i)
+        Xh = synth.make_activations(1, K, seed=100 + i)
+        want = cpu_oracle.matmul(fmt, Wh, Xh, threads=8)
+        got = host_f32(ops.gemv(fmt, dev(Wh), dev(Xh), N))
+        e = oracle.rel_l2(got, want)
+        assert e < REL_L2, f"{lname}: {e}"
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+def test_config2_q8_0_small_batch(M, cpu_oracle):
+    fmt, N, K = oracle.Q8_0, 14336, 4096
+    Wh = synth.make_blocks(fmt, N, K, seed=2)
+    Xh = synth.make_activations(M, K, seed=2)
+    want = cpu_oracle.matmul(fmt, Wh, Xh, threads=8)
+    got = host_f32(ops.linear(fmt, dev(Wh), dev(Xh), N))
+    assert oracle.rel_l2(got, want) < REL_L2
+
+
+# ---------------------------------------------------------------- error behaviour
+
+def test_bad_arguments_raise():
+    from brotensor_b200 import B200QError
+    W = dev(synth.make_blocks(oracle.Q4_K, 4, 256, seed=1))
+    x = dev(synth.make_activations(9, 256, seed=1))
+    with pytest.raises(B200QError):
+        ops.gemv(oracle.Q4_K, W, x, 4)  # M > 8
+    with pytest.raises(ValueError):
+        ops.gemv(oracle.Q4_K, W, x[:1, :128].contiguous(), 4)  # K not a block multiple
+    assert ops.gemv(oracle.Q4_K, W[:0], x[:1], 0).shape == (1, 0)
