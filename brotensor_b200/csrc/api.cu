@@ -16,6 +16,8 @@ int launch_gemv_simple(int fmt, const void* W, const void* X, int x_dtype, const
                        int M, int N, int K, cudaStream_t st);
 int launch_gemv_stream(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
                        int M, int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken);
+int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
+                   int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken);
 void stream_set_option(int which, int value);
 int stream_get_option(int which);
 size_t gemm_tc_workspace_bytes(int fmt, int x_dtype, int M, int N, int K);
@@ -154,9 +156,18 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
     DevInfo* d;
     if (int rc = dev_info(&d)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (g_opt_gemv_path != 1) {
+    // 0 = automatic, 1 = plain-load kernel, 2 = warp-MMA streaming kernel, 3 = integer-dot streaming kernel
+    if (g_opt_gemv_path == 0 || g_opt_gemv_path == 3) {
         bool taken = false;
-        if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->smem_optin, d->status, st, &taken))
+        if (int rc = launch_gemv_dp(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->smem_optin - 1024, d->status, st, &taken))
+            return rc;
+        if (taken) return B200Q_OK;
+        if (g_opt_gemv_path == 3)
+            return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the integer-dot kernel", M, N, K, fmt);
+    }
+    if (g_opt_gemv_path == 0 || g_opt_gemv_path == 2) {
+        bool taken = false;
+        if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->smem_optin - 1024, d->status, st, &taken))
             return rc;
         if (taken) return B200Q_OK;
         if (g_opt_gemv_path == 2)

@@ -54,7 +54,7 @@ int* device_status_word(int dev);  // device pointer to this device's status wor
 #define B200Q_CUDA_TRY(expr)                                                                          \
     do {                                                                                              \
         cudaError_t e_ = (expr);                                                                      \
-        if (e_ != cudaSuccess)                                                                        \
+        if (e_ != cudaSuccess && (cudaGetLastError(), true)) /* report once, leave no sticky error */ \
             return ::b200q::fail(B200Q_ERR_CUDA, "CUDA error %d (%s) at %s:%d in `%s`", (int)e_,      \
                                  cudaGetErrorString(e_), __FILE__, __LINE__, #expr);                  \
     } while (0)
@@ -266,6 +266,25 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
+}
+// Shared-memory accesses with a compile-time byte offset folded into the instruction.
+template <int IMM>
+__device__ __forceinline__ uint4 lds128i(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr), "n"(IMM));
+    return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint32_t lds32i(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     unsigned short v;

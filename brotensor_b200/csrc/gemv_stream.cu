@@ -28,70 +28,9 @@
 // (src/cuda/q4k.cu:159-224), linear_q6k_fp16_gemv_kernel (q6k.cu:117-176) and
 // linear_q8_0_fp16_gemv_kernel (q8_0.cu:75-138) plus their host-side widening
 // rules (q4k.cu:243-281).
-#include "common.cuh"
+#include "stream_common.cuh"
 
 namespace b200q {
-
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kStreamThreads = kConsumerThreads + 32;  // + producer warp
-constexpr int kTileRows = 16;
-constexpr int kMaxStages = 8;
-
-struct StreamParams {
-    const uint8_t* W;
-    const void* X;
-    const void* bias;
-    void* Y;
-    int* status;
-    int M, N, K;
-    int x_dtype, y_dtype;  // B200Q_DT_* of X/bias and of Y
-    int row_bytes;       // bytes of one weight row
-    int chunks_per_row;  // K / chunk elements
-    int slice_chunks;    // chunks per stage
-    int n_slices;        // stages per row tile
-    int row_stride;      // bytes between rows inside a stage (padded)
-    int n_stages;        // ring depth
-    // shared-memory offsets (bytes from the 128-byte aligned base)
-    int off_xhi, off_xlo, off_sxhi, off_sxlo, off_red, off_stage;
-};
-
-template <int FMT>
-struct Chunk {
-    static constexpr int blocks = Blk<FMT>::chunk_blocks;
-    static constexpr int bytes = Blk<FMT>::bytes * blocks;
-    static constexpr int elems = Blk<FMT>::elems * blocks;
-    // work units (16 rows x 256 elements) per chunk
-    static constexpr int units = elems / 256;
-};
-
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded mbarrier wait with an abort flag shared by the CTA. Returns false when
-// the wait was abandoned (by this thread's timeout or because another thread of
-// the CTA already gave up).
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                              int code) {
-    for (int i = 0; i < 128; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    for (;;) {
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > 1000000000ull) {  // one second
-            *abort_flag = 1;
-            if (status) atomicCAS(status, 0, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
 
 // Slot of (t = k-group owner lane, m = activation row) inside one 4*MG*8-byte page
 // of the staged activations; chosen so a warp's B-fragment loads hit distinct banks.
@@ -488,25 +427,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const St
     grid_dep_launch();
 
     if (warp == kConsumerWarps) {
-        // ---- producer: weights do not depend on the previous kernel, start at once
-        for (int it = 0; it < total_iters; ++it) {
-            const int slot = it % p.n_stages;
-            const uint32_t par = ((it / p.n_stages) & 1) ^ 1;
-            if (!wait_or_abort(smem_u32(&bar_empty[slot]), par, &abort_flag, p.status, kDevTimeoutEmpty)) break;
-            const int tile = it / p.n_slices, slice = it - tile * p.n_slices;
-            const int row0 = row_begin + tile * kTileRows;
-            const int nrows = min(kTileRows, row_end - row0);
-            const int c0 = slice * p.slice_chunks;
-            const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
-            const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
-            const uint32_t full = smem_u32(&bar_full[slot]);
-            if (lane == 0) mbar_arrive_expect_tx(full, bytes * (uint32_t)nrows);
-            __syncwarp();
-            if (lane < nrows) {
-                const uint8_t* src = p.W + (size_t)(row0 + lane) * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
-                bulk_g2s(smem_u32(smem + p.off_stage + slot * stage_bytes + lane * p.row_stride), src, bytes, full);
-            }
-        }
+        stream_producer<FMT>(p, smem_u32(smem), bar_full, bar_empty, &abort_flag, row_begin, row_end, total_iters, lane);
         return;
     }
 
@@ -668,7 +589,7 @@ static int launch_stream_k(const StreamPlan& pl, cudaStream_t st) {
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};

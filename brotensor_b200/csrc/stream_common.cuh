@@ -1,0 +1,130 @@
+// Pieces shared by the two streaming decode-GEMV kernels (gemv_stream.cu: warp-MMA
+// consumers for 5..8 activation rows; gemv_dp.cu: integer dot-product consumers for
+// 1..4 rows): launch parameters, the shared-memory ring geometry, the bounded
+// mbarrier wait and the producer warp that streams weight rows with bulk copies.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200q {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kStreamThreads = kConsumerThreads + 32;  // + producer warp
+constexpr int kTileRows = 16;
+constexpr int kMaxStages = 8;
+
+struct StreamParams {
+    const uint8_t* W;
+    const void* X;
+    const void* bias;
+    void* Y;
+    int* status;
+    int M, N, K;
+    int x_dtype, y_dtype;  // B200Q_DT_* of X/bias and of Y
+    int row_bytes;       // bytes of one weight row
+    int chunks_per_row;  // K / chunk elements
+    int slice_chunks;    // chunks per stage
+    int n_slices;        // stages per row tile
+    int row_stride;      // bytes between rows inside a stage (padded)
+    int n_stages;        // ring depth
+    // shared-memory offsets (bytes from the 128-byte aligned base)
+    int off_xhi, off_xlo, off_sxhi, off_sxlo, off_red, off_stage;
+};
+
+template <int FMT>
+struct Chunk {
+    static constexpr int blocks = Blk<FMT>::chunk_blocks;
+    static constexpr int bytes = Blk<FMT>::bytes * blocks;
+    static constexpr int elems = Blk<FMT>::elems * blocks;
+    // work units (16 rows x 256 elements) per chunk
+    static constexpr int units = elems / 256;
+};
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Bounded mbarrier wait with an abort flag shared by the CTA. Returns false when
+// the wait was abandoned (by this thread's timeout or because another thread of
+// the CTA already gave up).
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                              int code) {
+    for (int i = 0; i < 128; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > 1000000000ull) {  // one second
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }
+
+
+// Producer warp: streams the CTA's contiguous row range through the ring, one bulk
+// copy per weight row and stage. Weights do not depend on the stream-ordered
+// predecessor, so this starts before griddepcontrol.wait.
+template <int FMT>
+__device__ __forceinline__ void stream_producer(const StreamParams& p, uint32_t smem_base, uint64_t* bar_full,
+                                                uint64_t* bar_empty, volatile int* abort_flag, int row_begin,
+                                                int row_end, int total_iters, int lane) {
+    const int stage_bytes = kTileRows * p.row_stride;
+    for (int it = 0; it < total_iters; ++it) {
+        const int slot = it % p.n_stages;
+        const uint32_t par = ((it / p.n_stages) & 1) ^ 1;
+        if (!wait_or_abort(smem_u32(&bar_empty[slot]), par, abort_flag, p.status, kDevTimeoutEmpty)) break;
+        const int tile = it / p.n_slices, slice = it - tile * p.n_slices;
+        const int row0 = row_begin + tile * kTileRows;
+        const int nrows = min(kTileRows, row_end - row0);
+        const int c0 = slice * p.slice_chunks;
+        const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
+        const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
+        const uint32_t full = smem_u32(&bar_full[slot]);
+        if (lane == 0) mbar_arrive_expect_tx(full, bytes * (uint32_t)nrows);
+        __syncwarp();
+        if (lane < nrows) {
+            const uint8_t* src = p.W + (size_t)(row0 + lane) * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
+            bulk_g2s(smem_base + p.off_stage + slot * stage_bytes + lane * p.row_stride, src, bytes, full);
+        }
+    }
+}
+
+// Ring geometry for a stage of 16 rows x slice: the largest slice (in chunks) whose
+// stage fits `target` bytes, the row stride padded to `pad_mod` (mod 128) so rows
+// start in different banks, and as many stages (<= want) as fit `avail`.
+template <int FMT>
+inline bool plan_ring(StreamParams& p, size_t avail, size_t target, int want_stages, int pad_mod) {
+    int sc = p.chunks_per_row;
+    if (want_stages < 2) want_stages = 2;
+    if (want_stages > kMaxStages) want_stages = kMaxStages;
+    for (;;) {
+        int rs = sc * Chunk<FMT>::bytes;
+        rs += ((pad_mod - (rs % 128)) + 128) % 128;
+        const size_t sb = (size_t)kTileRows * rs;
+        int ns = (int)(avail / sb);
+        if (ns > want_stages) ns = want_stages;
+        if ((sb <= target && ns >= 2) || sc == 1) {
+            if (ns < 2) return false;
+            p.slice_chunks = sc;
+            p.row_stride = rs;
+            p.n_stages = ns;
+            p.n_slices = (p.chunks_per_row + sc - 1) / sc;
+            return true;
+        }
+        sc = (sc + 1) / 2;
+    }
+}
+
+void stream_set_option(int which, int value);
+int stream_get_option(int which);
+
+}  // namespace b200q

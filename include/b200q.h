@@ -120,8 +120,10 @@ int b200q_device_status(int* status_out);
 
 /*
  * Tuning knobs for benchmarks and tests (process-wide, not thread-safe):
- *   "gemv_path"   0 = automatic, 1 = force the plain-load kernel, 2 = force the streaming kernel
- *   "gemv_stages" ring depth of the streaming kernel (2..8)
+ *   "gemv_path"   0 = automatic, 1 = plain-load kernel, 2 = warp-MMA streaming kernel,
+ *                 3 = integer-dot streaming kernel (a forced path fails on shapes it does not take)
+ *   "gemv_stages" ring depth of the streaming kernels (2..8); "gemv_stage_kb" stage size target;
+ *   "gemv_grid"   CTA count (0 = one per SM)
  *   "pdl"         1 = launch GEMV kernels with programmatic dependent launch
  * Returns B200Q_ERR_BAD_ARG for an unknown key.
  */

@@ -1,0 +1,58 @@
+// Backend tables and dispatcher of the b200 host layer. Same mechanism as
+// brotensor's (include/brotensor/detail/dispatch.h:24-143, src/dispatch.cpp): one
+// function-pointer slot per public op whose type is the public signature, one
+// allocator table per backend, device resolution from the first committed operand.
+// Only the nine quant slots exist here.
+#pragma once
+
+#include <cstddef>
+#include <initializer_list>
+
+#include "../tensor.h"
+
+namespace brotensor_b200::detail {
+
+using DequantFn = void (*)(const Tensor& W, Tensor& out);
+using LinearFn = void (*)(const Tensor& W, const Tensor* bias, const Tensor& x, Tensor& y);
+
+struct OpsVTable {
+    DequantFn dequant_q4k_to_fp16 = nullptr;
+    LinearFn linear_forward_q4k_fp16 = nullptr;
+    LinearFn linear_forward_batched_q4k_fp16 = nullptr;
+    DequantFn dequant_q8_0_to_fp16 = nullptr;
+    LinearFn linear_forward_q8_0_fp16 = nullptr;
+    LinearFn linear_forward_batched_q8_0_fp16 = nullptr;
+    DequantFn dequant_q6k_to_fp16 = nullptr;
+    LinearFn linear_forward_q6k_fp16 = nullptr;
+    LinearFn linear_forward_batched_q6k_fp16 = nullptr;
+};
+
+struct AllocVTable {
+    void* (*alloc)(std::size_t bytes, int device_index) = nullptr;
+    void (*free)(void* ptr, int device_index) = nullptr;
+    void (*memcpy_h2d)(void* dst, const void* src, std::size_t n, int device_index) = nullptr;
+    void (*memcpy_d2h)(void* dst, const void* src, std::size_t n, int device_index) = nullptr;
+    void (*memcpy_d2d)(void* dst, const void* src, std::size_t n, int device_index) = nullptr;
+    void (*memcpy_peer)(void* dst, int dst_device, const void* src, int src_device, std::size_t n) = nullptr;
+    void (*memset_zero)(void* dst, std::size_t n, int device_index) = nullptr;
+    void (*sync)(int device_index) = nullptr;
+    bool (*mem_info)(std::size_t* free_bytes, std::size_t* total_bytes, int device_index) = nullptr;
+    bool (*device_name)(char* out, std::size_t cap, int device_index) = nullptr;
+};
+
+// Registering a device type twice replaces its tables.
+void register_backend(DeviceType dt, const OpsVTable& ops, const AllocVTable& alloc);
+const OpsVTable& ops_for(Device d);      // throws if the backend is not registered
+const AllocVTable& alloc_for(Device d);  // throws if the backend is not registered
+bool is_registered(Device d);
+void set_cuda_device_count(int count);
+int get_cuda_device_count();
+
+// Resolve the op's device from the first operand with storage; every other operand
+// with storage must agree, else std::runtime_error. Null optionals are skipped.
+// Selects that CUDA device for the calling thread before returning its table.
+const OpsVTable& dispatch_with_opts(const Tensor& a, std::initializer_list<const Tensor*> opts);
+void adopt_output(Tensor& t, Device d);
+[[noreturn]] void throw_not_implemented(const char* op_name, Device d);
+
+}  // namespace brotensor_b200::detail

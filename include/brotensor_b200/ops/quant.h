@@ -1,0 +1,32 @@
+// The nine GGUF quant ops, with brotensor's signatures and argument meaning
+// (include/brotensor/ops/quant.h:45-112).
+//
+//   dequant_*_to_fp16(W, W_fp16)                  W (out,in) quant -> (out,in), resized
+//   linear_forward_*_fp16(W, bias, x, y)          y(out,1) = W x (+bias)
+//   linear_forward_batched_*_fp16(W, bias, X, Y)  Y(B,out) = X(B,in) W^T (+bias)
+//
+// Superset of the reference contract: besides FP16, x / X may be FP32 or BF16 (bias
+// has x's dtype). The output keeps its dtype when the caller pre-sized it as FP32,
+// FP16 or BF16 with the right shape; otherwise it is resized to FP16 for FP16
+// activations (the reference behaviour) and to FP32 for FP32 / BF16 activations.
+// The dequant ops keep a pre-sized FP32 / BF16 destination likewise, else FP16.
+// Errors are std::runtime_error("brotensor: <op>: <reason>") as in the reference.
+#pragma once
+
+#include "../tensor.h"
+
+namespace brotensor_b200 {
+
+void dequant_q4k_to_fp16(const Tensor& W_q4k, Tensor& W_fp16);
+void linear_forward_q4k_fp16(const Tensor& W_q4k, const Tensor* bias, const Tensor& x, Tensor& y);
+void linear_forward_batched_q4k_fp16(const Tensor& W_q4k, const Tensor* bias, const Tensor& X_BD, Tensor& Y_BD);
+
+void dequant_q8_0_to_fp16(const Tensor& W_q8, Tensor& W_fp16);
+void linear_forward_q8_0_fp16(const Tensor& W_q8, const Tensor* bias, const Tensor& x, Tensor& y);
+void linear_forward_batched_q8_0_fp16(const Tensor& W_q8, const Tensor* bias, const Tensor& X_BD, Tensor& Y_BD);
+
+void dequant_q6k_to_fp16(const Tensor& W_q6k, Tensor& W_fp16);
+void linear_forward_q6k_fp16(const Tensor& W_q6k, const Tensor* bias, const Tensor& x, Tensor& y);
+void linear_forward_batched_q6k_fp16(const Tensor& W_q6k, const Tensor* bias, const Tensor& X_BD, Tensor& Y_BD);
+
+}  // namespace brotensor_b200

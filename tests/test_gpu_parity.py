@@ -167,16 +167,37 @@ def test_gemv_dtypes_and_bias(fmt, name, xdt, ydt, path, cpu_oracle):
 
 
 @pytest.mark.parametrize("fmt,name", FMTS)
-def test_stream_and_plain_kernels_agree(fmt, name):
-    """Two independent kernels, same inputs: agreement far inside the tolerance."""
-    N, K, M = 2500, 4096 if fmt != oracle.Q6_K else 6144, 8
+def test_three_kernels_agree(fmt, name):
+    """Three independent kernels on the same inputs: plain-load FP32, warp-MMA streaming
+    (FP16 activations; hi+lo halves when they fit in shared memory, which M=8 at this K
+    does not, so one FP16 rounding of x: about 2e-4) and integer-dot streaming
+    (int16 fixed-point activations per 128-element group: about 7e-5)."""
+    N, K = 2500, 4096 if fmt != oracle.Q6_K else 6144
     W = dev(synth.make_blocks(fmt, N, K, seed=31))
-    X = dev(synth.make_activations(M, K, seed=32))
-    ops.set_option("gemv_path", 1)
-    a = ops.gemv(fmt, W, X, N)
-    ops.set_option("gemv_path", 2)
-    b = ops.gemv(fmt, W, X, N)
-    assert oracle.rel_l2(host_f32(b), host_f32(a)) < 1e-4
+    for M, path, tol in ((8, 2, 5e-4), (4, 3, 2e-4), (1, 3, 2e-4), (2, 2, 1e-5)):
+        X = dev(synth.make_activations(M, K, seed=32 + M))
+        ops.set_option("gemv_path", 1)
+        a = ops.gemv(fmt, W, X, N)
+        ops.set_option("gemv_path", path)
+        b = ops.gemv(fmt, W, X, N)
+        e = oracle.rel_l2(host_f32(b), host_f32(a))
+        assert e < tol, f"M={M} path={path}: {e}"
+
+
+def test_integer_dot_kernel_is_robust_to_outliers(cpu_oracle):
+    """Activations with a few huge entries: per-group fixed-point scaling keeps the
+    error inside the bound (a per-row scale would not)."""
+    fmt, N, K = oracle.Q4_K, 512, 4096
+    Wh = synth.make_blocks(fmt, N, K, seed=51)
+    Xh = synth.make_activations(2, K, seed=52)
+    Xh[0, 7] = 900.0
+    Xh[0, 2049] = -350.0
+    Xh[1, 4000] = 2.5e4
+    Xh[1, 128:256] = 0.0
+    want = cpu_oracle.matmul(fmt, Wh, Xh, threads=8)
+    ops.set_option("gemv_path", 3)
+    got = host_f32(ops.gemv(fmt, dev(Wh), dev(Xh), N))
+    assert oracle.rel_l2(got, want) < REL_L2
 
 
 def test_gemv_is_deterministic_and_linear():
