@@ -52,16 +52,19 @@ __device__ __forceinline__ int dp2a_hi_ss(uint32_t x, uint32_t b, int c) {
     return d;
 }
 
-// Staged activations: group gg of row m is 16 segments of eight int16 (256 bytes);
-// segment i sits at position i ^ (gg & 7), so lanes working on consecutive groups read
-// the same segment number from different banks. All shared-memory traffic below goes
-// through explicit ld.shared / st.shared with 32-bit shared addresses.
+// Staged activations: group gg of row m is 16 segments of eight int16. Groups are laid
+// out at a stride of 272 bytes (256 + 16), so lanes working on consecutive groups read
+// the same segment number from consecutive 16-byte bank groups (conflict-free) and a
+// segment's address is the group's base plus a compile-time offset. All shared-memory
+// traffic below goes through explicit ld.shared / st.shared with 32-bit addresses.
+constexpr int kXGroupStride = 272;
+
 template <int FMT, typename XT>
-__device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase, int tid) {
+__device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase, int tid, int nthreads) {
     const XT* X = static_cast<const XT*>(p.X);
     const int segs = p.K >> 3, groups = p.K >> 7;
     const int total = segs * p.M;  // K % 256 == 0, so a multiple of 32
-    for (int idx = tid; idx < total; idx += kConsumerThreads) {
+    for (int idx = tid; idx < total; idx += nthreads) {
         const int m = idx / segs, seg = idx - m * segs;
         const int gg = seg >> 4, i = seg & 15;
         float v[8];
@@ -103,7 +106,7 @@ __device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase,
         o.y = (uint32_t)(q[2] & 0xFFFF) | ((uint32_t)q[3] << 16);
         o.z = (uint32_t)(q[4] & 0xFFFF) | ((uint32_t)q[5] << 16);
         o.w = (uint32_t)(q[6] & 0xFFFF) | ((uint32_t)q[7] << 16);
-        sts128(sbase + p.off_xhi + (uint32_t)((m * groups + gg) * 256 + ((i ^ (gg & 7)) << 4)), o);
+        sts128(sbase + p.off_xhi + (uint32_t)((m * groups + gg) * kXGroupStride + (i << 4)), o);
         if (i == 0) sts32(sbase + p.off_xlo + (uint32_t)(m * groups + gg) * 4, (uint32_t)(127 - e) << 23);
         if constexpr (FMT == kQ4_K) {  // sums over 32 elements = 4 segments
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -118,28 +121,71 @@ __device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase,
 
 // Shared-memory addresses an item needs for the staged activations.
 struct XAddr {
-    uint32_t x16, xsc, sxi;  // region bases (x16 256-byte aligned)
+    uint32_t x16, xsc, sxi;  // region bases
     int groups, K;
 };
-// Address of segment `I` of group gg, row m: xg = base of the group XOR-ed with the rotation.
+__device__ __forceinline__ uint32_t x_group(const XAddr& xa, int m, int gg) {
+    return xa.x16 + (uint32_t)((m * xa.groups + gg) * kXGroupStride);
+}
 template <int I>
-__device__ __forceinline__ uint4 x_seg(uint32_t xg) { return lds128i<0>(xg ^ (uint32_t)(I << 4)); }
+__device__ __forceinline__ uint4 x_seg(uint32_t xg) { return lds128i<16 * I>(xg); }
 
 // ---- one item = one 128-element group of two weight rows ---------------------------
 // rowA/rowB: shared addresses of this stage's bytes of the two rows; gi: group index
 // inside the stage; gg: group index along the whole row; acc[r][m]: FP32 partial sums.
+// Loads are written in the order they should issue (the asm statements keep it): all
+// weight loads of the item first, activations one step ahead of their use.
+
+template <int C2>
+__device__ __forceinline__ void q4k_load_x(uint32_t xg, uint4 (&x)[8]) {
+    x[0] = x_seg<8 * C2 + 0>(xg); x[1] = x_seg<8 * C2 + 1>(xg); x[2] = x_seg<8 * C2 + 2>(xg); x[3] = x_seg<8 * C2 + 3>(xg);
+    x[4] = x_seg<8 * C2 + 4>(xg); x[5] = x_seg<8 * C2 + 5>(xg); x[6] = x_seg<8 * C2 + 6>(xg); x[7] = x_seg<8 * C2 + 7>(xg);
+}
+
+// 32 bytes of quants (two uint4) against 64 activations: low nibbles pair with x[0..3],
+// high nibbles (left in place, i.e. times 16) with x[4..7].
+__device__ __forceinline__ void q4k_dot(const uint4& q0, const uint4& q1, const uint4 (&x)[8], int& cl, int& ch) {
+    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    // two independent chains per nibble set keep the integer pipe busy
+    int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const uint32_t l0 = w[2 * s] & 0x0F0F0F0Fu, l1 = w[2 * s + 1] & 0x0F0F0F0Fu;
+        const uint32_t h0 = w[2 * s] & 0xF0F0F0F0u, h1 = w[2 * s + 1] & 0xF0F0F0F0u;
+        a0 = dp2a_lo_su(x[s].x, l0, a0);
+        a0 = dp2a_hi_su(x[s].y, l0, a0);
+        a1 = dp2a_lo_su(x[s].z, l1, a1);
+        a1 = dp2a_hi_su(x[s].w, l1, a1);
+        b0 = dp2a_lo_su(x[4 + s].x, h0, b0);
+        b0 = dp2a_hi_su(x[4 + s].y, h0, b0);
+        b1 = dp2a_lo_su(x[4 + s].z, h1, b1);
+        b1 = dp2a_hi_su(x[4 + s].w, h1, b1);
+    }
+    cl = a0 + a1;
+    ch = (b0 + b1) >> 4;  // exact: every term is a multiple of 16
+}
 
 template <int MT>
 __device__ __forceinline__ void item_q4k(uint32_t rowA, uint32_t rowB, int gi, int gg, const XAddr& xa,
                                          float (&acc)[2][MT]) {
     const int b = gi >> 1, hb = gi & 1;
-    const uint32_t pr[2] = {rowA + (uint32_t)b * 144u, rowB + (uint32_t)b * 144u};
+    const uint32_t prA = rowA + (uint32_t)b * 144u, prB = rowB + (uint32_t)b * 144u;
+    const uint32_t qaA = prA + 64u * hb, qaB = prB + 64u * hb;
+    const uint4 hA = lds128i<0>(prA), hB = lds128i<0>(prB);
+    uint4 q[2][2][2];  // [c2][row][half]
+    q[0][0][0] = lds128i<16>(qaA); q[0][0][1] = lds128i<32>(qaA);
+    q[0][1][0] = lds128i<16>(qaB); q[0][1][1] = lds128i<32>(qaB);
+    uint4 x[8];
+    q4k_load_x<0>(x_group(xa, 0, gg), x);
+    q[1][0][0] = lds128i<48>(qaA); q[1][0][1] = lds128i<64>(qaA);
+    q[1][1][0] = lds128i<48>(qaB); q[1][1][1] = lds128i<64>(qaB);
+
+    // the four 6-bit scales / mins of sub-blocks 4*hb .. 4*hb+3, one per byte
     uint32_t scw[2], mw[2];
     float d[2], dm[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        const uint4 h = lds128i<0>(pr[r]);
-        // the four 6-bit scales / mins of sub-blocks 4*hb .. 4*hb+3, one per byte
+        const uint4 h = r ? hB : hA;
         const uint32_t sclo = h.y & 0x3f3f3f3fu, schi = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
         const uint32_t mlo = h.z & 0x3f3f3f3fu, mhi = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
         scw[r] = hb ? schi : sclo;
@@ -147,7 +193,6 @@ __device__ __forceinline__ void item_q4k(uint32_t rowA, uint32_t rowB, int gi, i
         d[r] = h2f(h.x & 0xFFFFu);
         dm[r] = h2f(h.x >> 16);
     }
-    const uint32_t qa[2] = {pr[0] + 64u * hb, pr[1] + 64u * hb};
     int isum[2][MT];
 #pragma unroll
     for (int r = 0; r < 2; ++r)
@@ -155,46 +200,26 @@ __device__ __forceinline__ void item_q4k(uint32_t rowA, uint32_t rowB, int gi, i
         for (int m = 0; m < MT; ++m) isum[r][m] = 0;
 #pragma unroll
     for (int c2 = 0; c2 < 2; ++c2) {
-        // 32 bytes of quants per row: low nibbles = sub-block 2*c2, high nibbles = 2*c2+1
-        uint32_t lo[2][8], hi[2][8];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const uint4 q0 = c2 ? lds128i<48>(qa[r]) : lds128i<16>(qa[r]);
-            const uint4 q1 = c2 ? lds128i<64>(qa[r]) : lds128i<32>(qa[r]);
-            const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                lo[r][k] = w[k] & 0x0F0F0F0Fu;
-                hi[r][k] = (w[k] >> 4) & 0x0F0F0F0Fu;
-            }
-        }
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-            const uint32_t xg = xa.x16 + (uint32_t)((m * xa.groups + gg) * 256 + ((gg & 7) << 4));
-            uint4 xl[4], xh[4];  // segments 8*c2+0..3 (low-nibble sub-block), 8*c2+4..7 (high-nibble)
-            if (c2 == 0) {
-                xl[0] = x_seg<0>(xg); xl[1] = x_seg<1>(xg); xl[2] = x_seg<2>(xg); xl[3] = x_seg<3>(xg);
-                xh[0] = x_seg<4>(xg); xh[1] = x_seg<5>(xg); xh[2] = x_seg<6>(xg); xh[3] = x_seg<7>(xg);
-            } else {
-                xl[0] = x_seg<8>(xg); xl[1] = x_seg<9>(xg); xl[2] = x_seg<10>(xg); xl[3] = x_seg<11>(xg);
-                xh[0] = x_seg<12>(xg); xh[1] = x_seg<13>(xg); xh[2] = x_seg<14>(xg); xh[3] = x_seg<15>(xg);
+            // activations of the next (c2, m) step are requested before this step's math
+            uint4 xn[8];
+            const bool has_next = !(c2 == 1 && m == MT - 1);
+            if (has_next) {
+                const int mn = (m + 1 < MT) ? m + 1 : 0;
+                if ((m + 1 < MT ? c2 : c2 + 1) == 0) q4k_load_x<0>(x_group(xa, mn, gg), xn);
+                else q4k_load_x<1>(x_group(xa, mn, gg), xn);
             }
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                int cl = 0, ch = 0;
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    cl = dp2a_lo_su(xl[s].x, lo[r][2 * s], cl);
-                    cl = dp2a_hi_su(xl[s].y, lo[r][2 * s], cl);
-                    cl = dp2a_lo_su(xl[s].z, lo[r][2 * s + 1], cl);
-                    cl = dp2a_hi_su(xl[s].w, lo[r][2 * s + 1], cl);
-                    ch = dp2a_lo_su(xh[s].x, hi[r][2 * s], ch);
-                    ch = dp2a_hi_su(xh[s].y, hi[r][2 * s], ch);
-                    ch = dp2a_lo_su(xh[s].z, hi[r][2 * s + 1], ch);
-                    ch = dp2a_hi_su(xh[s].w, hi[r][2 * s + 1], ch);
-                }
+                int cl, ch;
+                q4k_dot(q[c2][r][0], q[c2][r][1], x, cl, ch);
                 // |sc * c| <= 63 * 32*15*16383 = 4.95e8 and four of them fit an int32
                 isum[r][m] += (int)((scw[r] >> (16 * c2)) & 0xFFu) * cl + (int)((scw[r] >> (16 * c2 + 8)) & 0xFFu) * ch;
+            }
+            if (has_next) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) x[k] = xn[k];
             }
         }
     }
@@ -212,45 +237,52 @@ __device__ __forceinline__ void item_q4k(uint32_t rowA, uint32_t rowB, int gi, i
 }
 
 template <int J>
-__device__ __forceinline__ void q8_block_words(uint32_t base, float& d, uint32_t (&qs)[8]) {
+__device__ __forceinline__ void q8_block_words(uint32_t base, uint32_t (&w)[9]) {
     // block J of the group starts at 34*J: 4-byte aligned for even J, 2 (mod 4) for odd J
     constexpr int O = (J & 1) ? 34 * J - 2 : 34 * J;
-    const uint32_t w[9] = {lds32i<O>(base),      lds32i<O + 4>(base),  lds32i<O + 8>(base),
-                           lds32i<O + 12>(base), lds32i<O + 16>(base), lds32i<O + 20>(base),
-                           lds32i<O + 24>(base), lds32i<O + 28>(base), lds32i<O + 32>(base)};
-    if (J & 1) {
-        d = h2f(w[0] >> 16);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) qs[k] = w[k + 1];
-    } else {
-        d = h2f(w[0] & 0xFFFFu);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) qs[k] = __byte_perm(w[k], w[k + 1], 0x5432);
-    }
+    w[0] = lds32i<O>(base);      w[1] = lds32i<O + 4>(base);  w[2] = lds32i<O + 8>(base);
+    w[3] = lds32i<O + 12>(base); w[4] = lds32i<O + 16>(base); w[5] = lds32i<O + 20>(base);
+    w[6] = lds32i<O + 24>(base); w[7] = lds32i<O + 28>(base); w[8] = lds32i<O + 32>(base);
 }
 
 template <int MT, int J>
 __device__ __forceinline__ void q8_block(const uint32_t (&pr)[2], int gg, const XAddr& xa, float (&acc)[2][MT]) {
-    uint32_t qs[2][8];
-    float d[2];
-    q8_block_words<J>(pr[0], d[0], qs[0]);
-    q8_block_words<J>(pr[1], d[1], qs[1]);
+    uint32_t w[2][9];
+    q8_block_words<J>(pr[0], w[0]);
+    q8_block_words<J>(pr[1], w[1]);
+    uint4 xv[MT][4];
+    float xs[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
-        const uint32_t xg = xa.x16 + (uint32_t)((m * xa.groups + gg) * 256 + ((gg & 7) << 4));
-        const uint4 xv[4] = {x_seg<4 * J>(xg), x_seg<4 * J + 1>(xg), x_seg<4 * J + 2>(xg), x_seg<4 * J + 3>(xg)};
-        const float xs = __uint_as_float(lds32i<0>(xa.xsc + (uint32_t)(m * xa.groups + gg) * 4u));
+        const uint32_t xg = x_group(xa, m, gg);
+        xv[m][0] = x_seg<4 * J>(xg); xv[m][1] = x_seg<4 * J + 1>(xg);
+        xv[m][2] = x_seg<4 * J + 2>(xg); xv[m][3] = x_seg<4 * J + 3>(xg);
+        xs[m] = __uint_as_float(lds32i<0>(xa.xsc + (uint32_t)(m * xa.groups + gg) * 4u));
+    }
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            int c = 0;
+    for (int r = 0; r < 2; ++r) {
+        uint32_t qs[8];
+        float d;
+        if (J & 1) {
+            d = h2f(w[r][0] >> 16);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) qs[k] = w[r][k + 1];
+        } else {
+            d = h2f(w[r][0] & 0xFFFFu);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) qs[k] = __byte_perm(w[r][k], w[r][k + 1], 0x5432);
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            int c0 = 0, c1 = 0;
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
-                c = dp2a_lo_ss(xv[s].x, qs[r][2 * s], c);
-                c = dp2a_hi_ss(xv[s].y, qs[r][2 * s], c);
-                c = dp2a_lo_ss(xv[s].z, qs[r][2 * s + 1], c);
-                c = dp2a_hi_ss(xv[s].w, qs[r][2 * s + 1], c);
+                c0 = dp2a_lo_ss(xv[m][s].x, qs[2 * s], c0);
+                c0 = dp2a_hi_ss(xv[m][s].y, qs[2 * s], c0);
+                c1 = dp2a_lo_ss(xv[m][s].z, qs[2 * s + 1], c1);
+                c1 = dp2a_hi_ss(xv[m][s].w, qs[2 * s + 1], c1);
             }
-            acc[r][m] = fmaf(d[r] * xs, (float)c, acc[r][m]);
+            acc[r][m] = fmaf(d * xs[m], (float)(c0 + c1), acc[r][m]);
         }
     }
 }
@@ -271,11 +303,10 @@ __device__ __forceinline__ float biased_s8_to_f32(uint32_t u, int idx) {
 }
 
 template <int N, int K0 = 0>
-__device__ __forceinline__ void funnel_words(uint32_t a, uint32_t sh, uint32_t* out) {
-    // out[k] = bytes 4k .. 4k+3 of the stream that starts sh/8 bytes after `a`
+__device__ __forceinline__ void load_words(uint32_t a, uint32_t* out) {
     if constexpr (K0 < N) {
-        out[K0] = __funnelshift_r(lds32i<4 * K0>(a), lds32i<4 * K0 + 4>(a), sh);
-        funnel_words<N, K0 + 1>(a, sh, out);
+        out[K0] = lds32i<4 * K0>(a);
+        load_words<N, K0 + 1>(a, out);
     }
 }
 
@@ -283,35 +314,40 @@ template <int MT, int H, int Q>
 __device__ __forceinline__ void q6_sub(const uint32_t (&ql)[2][16], const uint32_t (&qh)[2][8],
                                        const uint32_t (&su)[2][2], int gg, const XAddr& xa, float (&accg)[2][MT]) {
     // sub-block (Q, H): 16 elements at 32*Q + 16*H of the group, raw6 = nibble | two qh bits << 4
-    uint32_t v[2][4];
+    constexpr int SI = 2 * Q + H;  // scale byte and 16-element sum index inside the group
+    uint4 x0[MT], x1[MT];
+    int sx[MT];
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+    for (int m = 0; m < MT; ++m) {
+        const uint32_t xg = x_group(xa, m, gg);
+        x0[m] = x_seg<4 * Q + 2 * H>(xg);
+        x1[m] = x_seg<4 * Q + 2 * H + 1>(xg);
+        sx[m] = (int)lds32i<4 * SI>(xa.sxi + (uint32_t)(m * (xa.K >> 4) + gg * 8) * 4u);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        uint32_t v[4];
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const uint32_t a = ql[r][4 * H + 8 * (Q & 1) + w], hb = qh[r][4 * H + w];
             const uint32_t nib = (Q < 2 ? a : (a >> 4)) & 0x0F0F0F0Fu;
             const uint32_t h2 = (Q == 0 ? hb << 4 : Q == 1 ? hb << 2 : Q == 2 ? hb : hb >> 2) & 0x30303030u;
-            v[r][w] = nib | h2;
+            v[w] = nib | h2;
         }
-    constexpr int SI = 2 * Q + H;  // scale byte and 16-element sum index inside the group
+        const float scf = biased_s8_to_f32(su[r][SI >> 2], SI & 3);
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        const uint32_t xg = xa.x16 + (uint32_t)((m * xa.groups + gg) * 256 + ((gg & 7) << 4));
-        const uint4 x0 = x_seg<4 * Q + 2 * H>(xg), x1 = x_seg<4 * Q + 2 * H + 1>(xg);
-        const int sx = (int)lds32i<4 * SI>(xa.sxi + (uint32_t)(m * (xa.K >> 4) + gg * 8) * 4u);
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            int c = 0;
-            c = dp2a_lo_su(x0.x, v[r][0], c);
-            c = dp2a_hi_su(x0.y, v[r][0], c);
-            c = dp2a_lo_su(x0.z, v[r][1], c);
-            c = dp2a_hi_su(x0.w, v[r][1], c);
-            c = dp2a_lo_su(x1.x, v[r][2], c);
-            c = dp2a_hi_su(x1.y, v[r][2], c);
-            c = dp2a_lo_su(x1.z, v[r][3], c);
-            c = dp2a_hi_su(x1.w, v[r][3], c);
+        for (int m = 0; m < MT; ++m) {
+            int c0 = 0, c1 = 0;
+            c0 = dp2a_lo_su(x0[m].x, v[0], c0);
+            c0 = dp2a_hi_su(x0[m].y, v[0], c0);
+            c1 = dp2a_lo_su(x0[m].z, v[1], c1);
+            c1 = dp2a_hi_su(x0[m].w, v[1], c1);
+            c0 = dp2a_lo_su(x1[m].x, v[2], c0);
+            c0 = dp2a_hi_su(x1[m].y, v[2], c0);
+            c1 = dp2a_lo_su(x1[m].z, v[3], c1);
+            c1 = dp2a_hi_su(x1[m].w, v[3], c1);
             // sum (raw6 - 32) * x = c - 32 * sum x
-            accg[r][m] = fmaf(biased_s8_to_f32(su[r][SI >> 2], SI & 3), (float)(c - 32 * sx), accg[r][m]);
+            accg[r][m] = fmaf(scf, (float)(c0 + c1 - 32 * sx[m]), accg[r][m]);
         }
     }
 }
@@ -323,17 +359,26 @@ __device__ __forceinline__ void item_q6k(uint32_t rowA, uint32_t rowB, int gi, i
     // blocks are 210 bytes: odd blocks of a 16-byte aligned chunk start at 2 (mod 4). Read
     // aligned words from 2 bytes earlier and funnel-shift; for even blocks the shift is 0.
     const uint32_t sh = (uint32_t)(bi & 1) * 16u;
+    uint32_t rl[2][17], rh[2][9], rs[2][3], rd[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t L = (r ? rowB : rowA) + (uint32_t)(bi * 210 - (bi & 1) * 2);
+        load_words<17>(L + 64u * G, rl[r]);
+        load_words<9>(L + 128u + 32u * G, rh[r]);
+        load_words<3>(L + 192u + 8u * G, rs[r]);
+        rd[r] = lds32i<208>(L);
+    }
     uint32_t ql[2][16], qh[2][8], su[2][2];
     float d[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-        const uint32_t L = (r ? rowB : rowA) + (uint32_t)(bi * 210 - (bi & 1) * 2);
-        funnel_words<16>(L + 64u * G, sh, ql[r]);
-        funnel_words<8>(L + 128u + 32u * G, sh, qh[r]);
-        funnel_words<2>(L + 192u + 8u * G, sh, su[r]);
-        su[r][0] ^= 0x80808080u;
-        su[r][1] ^= 0x80808080u;
-        d[r] = h2f((lds32i<208>(L) >> sh) & 0xFFFFu);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) ql[r][k] = __funnelshift_r(rl[r][k], rl[r][k + 1], sh);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) qh[r][k] = __funnelshift_r(rh[r][k], rh[r][k + 1], sh);
+        su[r][0] = __funnelshift_r(rs[r][0], rs[r][1], sh) ^ 0x80808080u;
+        su[r][1] = __funnelshift_r(rs[r][1], rs[r][2], sh) ^ 0x80808080u;
+        d[r] = h2f((rd[r] >> sh) & 0xFFFFu);
     }
     float accg[2][MT];
 #pragma unroll
@@ -356,12 +401,17 @@ __device__ __forceinline__ void item_q6k(uint32_t rowA, uint32_t rowB, int gi, i
     }
 }
 
-template <int FMT, int MT>
-__global__ void __launch_bounds__(kStreamThreads, 1) gemv_dp_kernel(const StreamParams p) {
+// NG independent pipelines inside one CTA: pipeline g has eight consumer warps, its own
+// producer warp, its own ring of p.n_stages stages and its own barriers, and works on
+// the row tiles t with t % NG == g. The pipelines share only the staged activations,
+// so twice as many warps hide each other's latencies without any coupling between
+// their barrier phases.
+template <int FMT, int MT, int NG>
+__global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_kernel(const StreamParams p) {
     extern __shared__ uint8_t smem_raw[];
-    const uint32_t sbase = (smem_u32(smem_raw) + 255u) & ~255u;  // shared-space address, 256-byte aligned
-    __shared__ uint64_t bar_full[kMaxStages];
-    __shared__ uint64_t bar_empty[kMaxStages];
+    const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;  // shared-space address
+    __shared__ uint64_t bar_full[NG][kMaxStages];
+    __shared__ uint64_t bar_empty[NG][kMaxStages];
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -369,122 +419,188 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_dp_kernel(const Stream
     const int row_begin = (int)((long long)p.N * blockIdx.x / G);
     const int row_end = (int)((long long)p.N * (blockIdx.x + 1) / G);
     const int n_tiles = (row_end - row_begin + kTileRows - 1) / kTileRows;
-    const int total_iters = n_tiles * p.n_slices;
     const int stage_bytes = kTileRows * p.row_stride;
 
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < p.n_stages; ++s) {
-            mbar_init(smem_u32(&bar_full[s]), 1);
-            mbar_init(smem_u32(&bar_empty[s]), kConsumerWarps);
-        }
+        for (int g = 0; g < NG; ++g)
+            for (int s = 0; s < p.n_stages; ++s) {
+                mbar_init(smem_u32(&bar_full[g][s]), 1);
+                mbar_init(smem_u32(&bar_empty[g][s]), kConsumerWarps);
+            }
         fence_mbar_init();
     }
     __syncthreads();
     grid_dep_launch();
 
-    if (warp == kConsumerWarps) {
-        stream_producer<FMT>(p, sbase, bar_full, bar_empty, &abort_flag, row_begin, row_end, total_iters, lane);
+    constexpr int kConsumers = kConsumerWarps * NG;
+    if (warp >= kConsumers) {
+        // ---- producer of pipeline g: weights do not depend on the stream-ordered
+        // predecessor, so the copies start before griddepcontrol.wait
+        const int g = warp - kConsumers;
+        const uint32_t ring = sbase + (uint32_t)(p.off_stage + g * p.n_stages * stage_bytes);
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int tile = g; tile < n_tiles; tile += NG) {
+            const int row0 = row_begin + tile * kTileRows;
+            const int nrows = min(kTileRows, row_end - row0);
+            for (int slice = 0; slice < p.n_slices; ++slice) {
+                if (!wait_or_abort(smem_u32(&bar_empty[g][slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty)) return;
+                const int c0 = slice * p.slice_chunks;
+                const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
+                const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
+                const uint32_t full = smem_u32(&bar_full[g][slot]);
+                if (lane == 0) mbar_arrive_expect_tx(full, bytes * (uint32_t)nrows);
+                __syncwarp();
+                if (lane < nrows) {
+                    const uint8_t* src = p.W + (size_t)(row0 + lane) * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
+                    bulk_g2s(ring + slot * stage_bytes + lane * p.row_stride, src, bytes, full);
+                }
+                if (++slot == p.n_stages) {
+                    slot = 0;
+                    phase ^= 1;
+                }
+            }
+        }
         return;
     }
 
+    // ---- consumers
     grid_dep_wait();  // activations (and Y) belong to the stream-ordered predecessor
-    if (p.x_dtype == B200Q_DT_F32) stage_x16<FMT, float>(p, sbase, tid);
-    else if (p.x_dtype == B200Q_DT_F16) stage_x16<FMT, __half>(p, sbase, tid);
-    else stage_x16<FMT, __nv_bfloat16>(p, sbase, tid);
-    consumer_bar_sync();
+    if (p.x_dtype == B200Q_DT_F32) stage_x16<FMT, float>(p, sbase, tid, kConsumers * 32);
+    else if (p.x_dtype == B200Q_DT_F16) stage_x16<FMT, __half>(p, sbase, tid, kConsumers * 32);
+    else stage_x16<FMT, __nv_bfloat16>(p, sbase, tid, kConsumers * 32);
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
 
     const XAddr xa = {sbase + (uint32_t)p.off_xhi, sbase + (uint32_t)p.off_xlo, sbase + (uint32_t)p.off_sxhi, p.K >> 7, p.K};
     constexpr int kGroupsPerChunk = Chunk<FMT>::elems / 128;
+    const int g = warp / kConsumerWarps, wl = warp % kConsumerWarps;
+    const uint32_t ring = sbase + (uint32_t)(p.off_stage + g * p.n_stages * stage_bytes);
     bool live = true;
+    int slot = 0;
+    uint32_t phase = 0;
     float acc[2][MT];
 #pragma unroll
     for (int r = 0; r < 2; ++r)
 #pragma unroll
         for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
 
-    for (int it = 0; it < total_iters; ++it) {
-        const int slot = it % p.n_stages;
-        const int tile = it / p.n_slices, slice = it - tile * p.n_slices;
+    for (int tile = g; tile < n_tiles; tile += NG) {
         const int row0 = row_begin + tile * kTileRows;
         const int nrows = min(kTileRows, row_end - row0);
-        if (live) {
-            const bool ok = wait_or_abort(smem_u32(&bar_full[slot]), (it / p.n_stages) & 1, &abort_flag, p.status, kDevTimeoutFull);
-            live = __all_sync(0xffffffffu, ok);
-        }
-        if (live && 2 * warp < nrows) {
-            const int c0 = slice * p.slice_chunks;
-            const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
-            const int ng = nch * kGroupsPerChunk, g0 = c0 * kGroupsPerChunk;
-            const uint32_t rowA = sbase + (uint32_t)(p.off_stage + slot * stage_bytes + (2 * warp) * p.row_stride);
-            // a tile with an odd row count has no second row for its last pair: reuse the first
-            const uint32_t rowB = (2 * warp + 1 < nrows) ? rowA + (uint32_t)p.row_stride : rowA;
-            for (int gi = lane; gi < ng; gi += 32) {
-                if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
-                else if constexpr (FMT == kQ8_0) item_q8_0<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
-                else item_q6k<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
+        for (int slice = 0; slice < p.n_slices; ++slice) {
+            if (live) {
+                // keep the decision warp-uniform
+                const bool ok = wait_or_abort(smem_u32(&bar_full[g][slot]), phase, &abort_flag, p.status, kDevTimeoutFull);
+                live = __all_sync(0xffffffffu, ok);
+            }
+            if (live && 2 * wl < nrows) {
+                const int c0 = slice * p.slice_chunks;
+                const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
+                const int ng = nch * kGroupsPerChunk, g0 = c0 * kGroupsPerChunk;
+                const uint32_t rowA = ring + (uint32_t)(slot * stage_bytes + (2 * wl) * p.row_stride);
+                // a tile with an odd row count has no second row for its last pair: reuse the first
+                const uint32_t rowB = (2 * wl + 1 < nrows) ? rowA + (uint32_t)p.row_stride : rowA;
+                for (int gi = lane; gi < ng; gi += 32) {
+                    if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
+                    else if constexpr (FMT == kQ8_0) item_q8_0<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
+                    else item_q6k<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_empty[g][slot]));
+            if (++slot == p.n_stages) {
+                slot = 0;
+                phase ^= 1;
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_empty[slot]));
-
-        if (slice == p.n_slices - 1) {
+        // the row's partial sums live in this warp's lanes: combine and write
 #pragma unroll
-            for (int r = 0; r < 2; ++r)
+        for (int r = 0; r < 2; ++r)
 #pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    float s = acc[r][m];
+            for (int m = 0; m < MT; ++m) {
+                float s = acc[r][m];
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                    acc[r][m] = 0.f;
-                    const int rr = 2 * warp + r;
-                    if (lane == 0 && rr < nrows && m < p.M && !*(volatile int*)&abort_flag) {
-                        const int n = row0 + rr;
-                        if (p.bias) {
-                            if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(p.bias)[n];
-                            else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(p.bias)[n]);
-                            else s += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
-                        }
-                        const size_t o = (size_t)m * p.N + n;
-                        if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
-                        else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(s);
-                        else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(s);
+                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                acc[r][m] = 0.f;
+                const int rr = 2 * wl + r;
+                if (lane == 0 && rr < nrows && m < p.M && !*(volatile int*)&abort_flag) {
+                    const int n = row0 + rr;
+                    if (p.bias) {
+                        if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(p.bias)[n];
+                        else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(p.bias)[n]);
+                        else s += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
                     }
+                    const size_t o = (size_t)m * p.N + n;
+                    if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
+                    else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(s);
+                    else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(s);
                 }
-        }
+            }
     }
 }
 
 // ---- host side ------------------------------------------------------------------------
 
+static int g_opt_groups = 2;
+void dp_set_groups(int v) { g_opt_groups = v < 1 ? 1 : (v > 2 ? 2 : v); }
+int dp_get_groups() { return g_opt_groups; }
+
+// p.n_stages is the ring depth of ONE pipeline; `ng` pipelines share the shared memory.
 template <int FMT>
-static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, StreamParams& p, int& grid, size_t& smem) {
+static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, StreamParams& p, int& grid, size_t& smem) {
     if (K % Chunk<FMT>::elems != 0 || M > 4) return false;
     p.M = M; p.N = N; p.K = K;
     p.row_bytes = (K / Blk<FMT>::elems) * Blk<FMT>::bytes;
     p.chunks_per_row = K / Chunk<FMT>::elems;
     size_t off = 0;
-    p.off_xhi = (int)off; off += (size_t)2 * K * M;                     // int16 activations (multiple of 256)
-    p.off_xlo = (int)off; off += (((size_t)4 * (K / 128) * M) + 127) & ~size_t(127);  // per-group 2^-e
+    p.off_xhi = (int)off; off += ((size_t)kXGroupStride * (K / 128) * M + 127) & ~size_t(127);  // int16 activations
+    p.off_xlo = (int)off; off += (((size_t)4 * (K / 128) * M) + 127) & ~size_t(127);            // per-group 2^-e
     const size_t sums = FMT == kQ4_K ? (size_t)4 * (K / 32) * M : FMT == kQ6_K ? (size_t)4 * (K / 16) * M : 0;
     p.off_sxhi = (int)off; off += (sums + 127) & ~size_t(127);
     p.off_sxlo = p.off_red = (int)off;
     p.off_stage = (int)off;
-    if (off + 256 + 4096 > smem_max) return false;
-    // Q4_K lanes read 16-byte vectors at a 144-byte stride, Q8_0 8-byte ... at 136: any
-    // row stride works for the lanes of one row; pad rows to 16 (mod 128) to spread the
-    // two rows of a pair.
-    if (!plan_ring<FMT>(p, smem_max - off - 256, (size_t)stream_get_option(2) * 1024, stream_get_option(0), 16))
-        return false;
-    smem = off + (size_t)p.n_stages * kTileRows * p.row_stride + 256;
+    if (off + 128 + 4096 > smem_max) return false;
+    const size_t avail = smem_max - off - 128;
+    // A lane works on one 128-element group, so a slice should hold a multiple of 32
+    // groups per row: take the largest such slice whose stage is within the target
+    // (at least 32 groups when the row has them), then as many stages as fit.
+    constexpr int gpc = Chunk<FMT>::elems / 128;  // groups per chunk: 2 (Q4_K, Q8_0) or 16 (Q6_K)
+    const int cpr = p.chunks_per_row;
+    const size_t target = (size_t)stream_get_option(2) * 1024;
+    int want = stream_get_option(0);
+    want = want < 2 ? 2 : (want > kMaxStages ? kMaxStages : want);
+    int best = 0;
+    for (int sc = 1; sc <= cpr; ++sc) {
+        const int groups = sc * gpc;
+        if (groups % 32 != 0 && sc != cpr && groups < 32) continue;
+        int rs = sc * Chunk<FMT>::bytes;
+        rs += ((16 - (rs % 128)) + 128) % 128;
+        const size_t sb = (size_t)kTileRows * rs;
+        if (sb * 2 * ng > avail) break;
+        if (best && sb > target) break;
+        if (groups % 32 == 0 || sc == cpr) best = sc;
+        else if (!best) best = sc;
+    }
+    if (!best) return false;
+    p.slice_chunks = best;
+    p.row_stride = best * Chunk<FMT>::bytes;
+    p.row_stride += ((16 - (p.row_stride % 128)) + 128) % 128;  // rows padded to 16 (mod 128)
+    p.n_slices = (cpr + best - 1) / best;
+    const size_t sb = (size_t)kTileRows * p.row_stride;
+    int ns = (int)(avail / (sb * ng));
+    if (ns > want) ns = want;
+    if (ns < 2) return false;
+    p.n_stages = ns;
+    smem = off + (size_t)ns * ng * sb + 128;
     grid = stream_get_option(3) > 0 ? stream_get_option(3) : sms;
     if (grid > N) grid = N;
     return true;
 }
 
-template <int FMT, int MT>
+template <int FMT, int MT, int NG>
 static int launch_dp_k(const StreamParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = gemv_dp_kernel<FMT, MT>;
+    auto kern = gemv_dp_kernel<FMT, MT, NG>;
     static bool configured[64] = {};
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
@@ -494,7 +610,7 @@ static int launch_dp_k(const StreamParams& p, int grid, size_t smem, cudaStream_
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kStreamThreads);
+    cfg.blockDim = dim3((kConsumerWarps + 1) * NG * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -506,13 +622,23 @@ static int launch_dp_k(const StreamParams& p, int grid, size_t smem, cudaStream_
     return B200Q_OK;
 }
 
+template <int FMT, int MT>
+static int launch_dp_g(const StreamParams& p, int ng, int grid, size_t smem, cudaStream_t st) {
+    return ng == 2 ? launch_dp_k<FMT, MT, 2>(p, grid, smem, st) : launch_dp_k<FMT, MT, 1>(p, grid, smem, st);
+}
+
 template <int FMT>
 static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N,
                        int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken) {
     StreamParams p = {};
     int grid = 0;
     size_t smem = 0;
-    *taken = plan_dp<FMT>(M, N, K, sms, smem_max, p, grid, smem);
+    int ng = g_opt_groups;
+    *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, p, grid, smem);
+    if (!*taken && ng == 2) {  // two pipelines do not fit: one
+        ng = 1;
+        *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, p, grid, smem);
+    }
     if (!*taken) return B200Q_OK;
     p.W = static_cast<const uint8_t*>(W);
     p.X = X;
@@ -522,10 +648,10 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
     p.x_dtype = x_dtype;
     p.y_dtype = y_dtype;
     switch (M) {
-        case 1: return launch_dp_k<FMT, 1>(p, grid, smem, st);
-        case 2: return launch_dp_k<FMT, 2>(p, grid, smem, st);
-        case 3: return launch_dp_k<FMT, 3>(p, grid, smem, st);
-        default: return launch_dp_k<FMT, 4>(p, grid, smem, st);
+        case 1: return launch_dp_g<FMT, 1>(p, ng, grid, smem, st);
+        case 2: return launch_dp_g<FMT, 2>(p, ng, grid, smem, st);
+        case 3: return launch_dp_g<FMT, 3>(p, ng, grid, smem, st);
+        default: return launch_dp_g<FMT, 4>(p, ng, grid, smem, st);
     }
 }
 

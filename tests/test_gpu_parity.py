@@ -34,11 +34,21 @@ def as_dtype_np(x, name):
     return t, t.float().numpy()
 
 
+# (gemv_path, pipelines): plain-load kernel; automatic routing with one / two
+# producer-consumer pipelines per CTA in the integer-dot kernel
+PATHS = [(1, 2), (0, 1), (0, 2)]
+
+
+def set_path(path):
+    ops.set_option("gemv_path", path[0])
+    ops.set_option("gemv_groups", path[1])
+
+
 @pytest.fixture(autouse=True)
 def _clean_state():
-    ops.set_option("gemv_path", 0)
+    set_path((0, 2))
     yield
-    ops.set_option("gemv_path", 0)
+    set_path((0, 2))
     assert ops.device_status() == 0
 
 
@@ -83,12 +93,12 @@ def test_dequant_rows_beyond_grid_y_limit(cpu_oracle):
 
 # ---------------------------------------------------------------- reference test cases
 
-@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("fmt,name", FMTS)
 def test_reference_parity_cases(fmt, name, path, golden):
     """Cases B, C, D, E, F, G of the reference parity tests with FP16 activations
     and FP16 outputs (the reference contract) and the reference's absolute bounds."""
-    ops.set_option("gemv_path", path)
+    set_path(path)
     g = golden(name + "_parity")
     W = dev(g["A_W"])
     x = dev(g["B_x"]).half()
@@ -134,11 +144,11 @@ SHAPES = {
 }
 
 
-@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("fmt,name", FMTS)
 @pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8])
 def test_gemv_matches_oracle(fmt, name, M, path, cpu_oracle):
-    ops.set_option("gemv_path", path)
+    set_path(path)
     for N, K in SHAPES[fmt]:
         Wh = synth.make_blocks(fmt, N, K, seed=N * 7 + K)
         Xh = synth.make_activations(M, K, seed=N + K + M)
@@ -149,11 +159,11 @@ def test_gemv_matches_oracle(fmt, name, M, path, cpu_oracle):
         assert e < REL_L2, f"N={N} K={K} M={M} rel_l2={e}"
 
 
-@pytest.mark.parametrize("path", [1, 0])
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("fmt,name", FMTS)
 @pytest.mark.parametrize("xdt,ydt", [("f16", "f16"), ("bf16", "f32"), ("f32", "bf16"), ("bf16", "bf16"), ("f16", "f32")])
 def test_gemv_dtypes_and_bias(fmt, name, xdt, ydt, path, cpu_oracle):
-    ops.set_option("gemv_path", path)
+    set_path(path)
     N, K, M = 333, 4096 if fmt != oracle.Q6_K else 2048, 3
     Wh = synth.make_blocks(fmt, N, K, seed=21)
     xt, xr = as_dtype_np(synth.make_activations(M, K, seed=22), xdt)
