@@ -175,10 +175,14 @@ __device__ __forceinline__ void item_q4k(uint32_t rowA, uint32_t rowB, int gi, i
     uint4 q[2][2][2];  // [c2][row][half]
     q[0][0][0] = lds128i<16>(qaA); q[0][0][1] = lds128i<32>(qaA);
     q[0][1][0] = lds128i<16>(qaB); q[0][1][1] = lds128i<32>(qaB);
-    uint4 x[8];
-    q4k_load_x<0>(x_group(xa, 0, gg), x);
+    // activations: x0 serves chunk 0, x1 chunk 1 of activation row m; the loads of the
+    // next step are written before the math of the current one
+    uint4 x0[8], x1[8];
+    const uint32_t xg0 = x_group(xa, 0, gg);
+    q4k_load_x<0>(xg0, x0);
     q[1][0][0] = lds128i<48>(qaA); q[1][0][1] = lds128i<64>(qaA);
     q[1][1][0] = lds128i<48>(qaB); q[1][1][1] = lds128i<64>(qaB);
+    q4k_load_x<1>(xg0, x1);
 
     // the four 6-bit scales / mins of sub-blocks 4*hb .. 4*hb+3, one per byte
     uint32_t scw[2], mw[2];
@@ -193,45 +197,31 @@ __device__ __forceinline__ void item_q4k(uint32_t rowA, uint32_t rowB, int gi, i
         d[r] = h2f(h.x & 0xFFFFu);
         dm[r] = h2f(h.x >> 16);
     }
-    int isum[2][MT];
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int m = 0; m < MT; ++m) isum[r][m] = 0;
-#pragma unroll
-    for (int c2 = 0; c2 < 2; ++c2) {
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            // activations of the next (c2, m) step are requested before this step's math
-            uint4 xn[8];
-            const bool has_next = !(c2 == 1 && m == MT - 1);
-            if (has_next) {
-                const int mn = (m + 1 < MT) ? m + 1 : 0;
-                if ((m + 1 < MT ? c2 : c2 + 1) == 0) q4k_load_x<0>(x_group(xa, mn, gg), xn);
-                else q4k_load_x<1>(x_group(xa, mn, gg), xn);
-            }
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                int cl, ch;
-                q4k_dot(q[c2][r][0], q[c2][r][1], x, cl, ch);
-                // |sc * c| <= 63 * 32*15*16383 = 4.95e8 and four of them fit an int32
-                isum[r][m] += (int)((scw[r] >> (16 * c2)) & 0xFFu) * cl + (int)((scw[r] >> (16 * c2 + 8)) & 0xFFu) * ch;
-            }
-            if (has_next) {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) x[k] = xn[k];
-            }
-        }
-    }
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
+        int isum[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            int cl, ch;
+            q4k_dot(q[0][r][0], q[0][r][1], x0, cl, ch);
+            // |sc * c| <= 63 * 32*15*16383 = 4.95e8 and four of them fit an int32
+            isum[r] = (int)(scw[r] & 0xFFu) * cl + (int)((scw[r] >> 8) & 0xFFu) * ch;
+        }
+        if (m + 1 < MT) q4k_load_x<0>(x_group(xa, m + 1, gg), x0);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            int cl, ch;
+            q4k_dot(q[1][r][0], q[1][r][1], x1, cl, ch);
+            isum[r] += (int)((scw[r] >> 16) & 0xFFu) * cl + (int)(scw[r] >> 24) * ch;
+        }
+        if (m + 1 < MT) q4k_load_x<1>(x_group(xa, m + 1, gg), x1);
         const uint4 sv = lds128i<0>(xa.sxi + (uint32_t)(m * (xa.K >> 5) + gg * 4) * 4u);
         const float xs = __uint_as_float(lds32i<0>(xa.xsc + (uint32_t)(m * xa.groups + gg) * 4u));
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             const int imin = (int)(mw[r] & 0xFFu) * (int)sv.x + (int)((mw[r] >> 8) & 0xFFu) * (int)sv.y +
                              (int)((mw[r] >> 16) & 0xFFu) * (int)sv.z + (int)(mw[r] >> 24) * (int)sv.w;
-            acc[r][m] = fmaf(xs, d[r] * (float)isum[r][m] - dm[r] * (float)imin, acc[r][m]);
+            acc[r][m] = fmaf(xs, d[r] * (float)isum[r] - dm[r] * (float)imin, acc[r][m]);
         }
     }
 }
@@ -514,29 +504,29 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 phase ^= 1;
             }
         }
-        // the row's partial sums live in this warp's lanes: combine and write
+        // the rows' partial sums live in this warp's lanes: lanes 0..15 finish the first
+        // row of the pair, lanes 16..31 the second (five shuffles for both), then write
 #pragma unroll
-        for (int r = 0; r < 2; ++r)
+        for (int m = 0; m < MT; ++m) {
+            const bool up = lane >= 16;
+            float s = (up ? acc[1][m] : acc[0][m]) + __shfl_xor_sync(0xffffffffu, up ? acc[0][m] : acc[1][m], 16);
 #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                float s = acc[r][m];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                acc[r][m] = 0.f;
-                const int rr = 2 * wl + r;
-                if (lane == 0 && rr < nrows && m < p.M && !*(volatile int*)&abort_flag) {
-                    const int n = row0 + rr;
-                    if (p.bias) {
-                        if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(p.bias)[n];
-                        else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(p.bias)[n]);
-                        else s += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
-                    }
-                    const size_t o = (size_t)m * p.N + n;
-                    if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
-                    else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(s);
-                    else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(s);
+            for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            acc[0][m] = acc[1][m] = 0.f;
+            const int rr = 2 * wl + (up ? 1 : 0);
+            if ((lane & 15) == 0 && rr < nrows && m < p.M && !*(volatile int*)&abort_flag) {
+                const int n = row0 + rr;
+                if (p.bias) {
+                    if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(p.bias)[n];
+                    else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(p.bias)[n]);
+                    else s += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
                 }
+                const size_t o = (size_t)m * p.N + n;
+                if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
+                else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(s);
+                else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(s);
             }
+        }
     }
 }
 
@@ -591,10 +581,17 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, Strea
     int ns = (int)(avail / (sb * ng));
     if (ns > want) ns = want;
     if (ns < 2) return false;
-    p.n_stages = ns;
-    smem = off + (size_t)ns * ng * sb + 128;
     grid = stream_get_option(3) > 0 ? stream_get_option(3) : sms;
     if (grid > N) grid = N;
+    // a ring deeper than the stages a pipeline will ever see only takes shared memory
+    // away from the next kernel, which under programmatic dependent launch can move in
+    // beside this one and prefetch its weights
+    const int rows_per_cta = (N + grid - 1) / grid;
+    const int tiles = (rows_per_cta + kTileRows - 1) / kTileRows;
+    const int stages_seen = ((tiles + ng - 1) / ng) * p.n_slices;
+    if (ns > stages_seen) ns = stages_seen < 1 ? 1 : stages_seen;
+    p.n_stages = ns;
+    smem = off + (size_t)ns * ng * sb + 128;
     return true;
 }
 
