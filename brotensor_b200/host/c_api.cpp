@@ -1,0 +1,214 @@
+// Flat C entry points over the C++ host layer, for callers without a C++ toolchain
+// (the Python tests and the benchmark's end-to-end arm bind them with ctypes). They add
+// no behaviour: every call goes through Tensor / the dispatcher / the public ops, so what
+// is measured or tested through them is the plugin path a C++ user takes.
+#include <cstring>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "brotensor_b200/gguf.h"
+#include "brotensor_b200/ops/quant.h"
+#include "brotensor_b200/runtime.h"
+
+using namespace brotensor_b200;
+
+namespace {
+thread_local std::string t_err;
+template <typename F>
+int guarded(F&& f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception& e) {
+        t_err = e.what();
+        return -1;
+    }
+}
+Dtype fmt_dtype(int fmt) { return static_cast<Dtype>(fmt); }
+
+struct Session {
+    const Tensor* W;
+    Tensor x, y, bias;
+    bool has_bias = false;
+    int M;
+};
+}  // namespace
+
+extern "C" {
+
+const char* b200h_last_error() { return t_err.c_str(); }
+
+// Brings the backends up; returns the number of CUDA devices (0 on a CPU-only host).
+int b200h_init() {
+    if (guarded([] { init(); })) return -1;
+    return cuda_device_count();
+}
+
+// ---- weights -----------------------------------------------------------------------------
+// `device` < 0 keeps the tensor on the host. Returns an owning handle or NULL.
+void* b200h_weight_from_host(int fmt, const void* bytes, int rows, int cols, int device) {
+    Tensor* t = nullptr;
+    if (guarded([&] {
+            const Device d = device < 0 ? Device::CPU : Device::cuda(device);
+            const Dtype dt = fmt_dtype(fmt);
+            t = new Tensor(Tensor::from_raw_bytes_on(d, bytes, rows, cols, dt,
+                                                     dtype_storage_bytes(dt, static_cast<std::int64_t>(rows) * cols)));
+        }))
+        return nullptr;
+    return t;
+}
+void b200h_tensor_free(void* t) { delete static_cast<Tensor*>(t); }
+void* b200h_tensor_data(void* t) { return static_cast<Tensor*>(t)->data; }
+int b200h_tensor_rows(void* t) { return static_cast<Tensor*>(t)->rows; }
+int b200h_tensor_cols(void* t) { return static_cast<Tensor*>(t)->cols; }
+int b200h_tensor_dtype(void* t) { return static_cast<int>(static_cast<Tensor*>(t)->dtype); }
+int b200h_tensor_to_host(void* t, void* dst) {
+    return guarded([&] { static_cast<Tensor*>(t)->copy_raw_to_host(dst); });
+}
+
+// ---- ops through the public signatures -----------------------------------------------------
+// dequant_*_to_fp16: out_dtype 1 (FP16, the reference behaviour), 0 (FP32) or 4 (BF16).
+int b200h_dequant(void* Wh, void* out_host, int out_dtype) {
+    return guarded([&] {
+        const Tensor& W = *static_cast<Tensor*>(Wh);
+        Tensor out;
+        if (out_dtype != 1) out = Tensor::empty_on(W.device, W.rows, W.cols, static_cast<Dtype>(out_dtype));
+        switch (W.dtype) {
+            case Dtype::Q4_K: dequant_q4k_to_fp16(W, out); break;
+            case Dtype::Q6_K: dequant_q6k_to_fp16(W, out); break;
+            case Dtype::Q8_0: dequant_q8_0_to_fp16(W, out); break;
+            default: throw std::runtime_error("b200h_dequant: weight is not Q4_K / Q6_K / Q8_0");
+        }
+        sync(W.device);
+        out.copy_raw_to_host(out_host);
+    });
+}
+
+// A session keeps the device-side activation and result tensors of one linear layer, so
+// a step is: host -> device copy of X, the op, device -> host copy of Y.
+void* b200h_session_create(void* Wh, int M, int x_dtype, int y_dtype, const void* bias_host) {
+    Session* s = nullptr;
+    if (guarded([&] {
+            const Tensor& W = *static_cast<Tensor*>(Wh);
+            auto up = std::make_unique<Session>();
+            up->W = &W;
+            up->M = M;
+            const Dtype xd = static_cast<Dtype>(x_dtype), yd = static_cast<Dtype>(y_dtype);
+            if (M == 1) {
+                up->x = Tensor::empty_on(W.device, W.cols, 1, xd);
+                up->y = Tensor::empty_on(W.device, W.rows, 1, yd);
+            } else {
+                up->x = Tensor::empty_on(W.device, M, W.cols, xd);
+                up->y = Tensor::empty_on(W.device, M, W.rows, yd);
+            }
+            if (bias_host) {
+                up->bias = Tensor::from_raw_bytes_on(W.device, bias_host, W.rows, 1, xd, dtype_storage_bytes(xd, W.rows));
+                up->has_bias = true;
+            }
+            s = up.release();
+        }))
+        return nullptr;
+    return s;
+}
+void b200h_session_free(void* s) { delete static_cast<Session*>(s); }
+
+int b200h_session_run(void* sh, const void* x_host, void* y_host) {
+    return guarded([&] {
+        Session& s = *static_cast<Session*>(sh);
+        const Tensor& W = *s.W;
+        // the same copies Tensor::from_raw_bytes_on / copy_to_host make, into resident tensors
+        Tensor xin = Tensor::from_raw_bytes_on(Device::CPU, x_host, s.x.rows, s.x.cols, s.x.dtype, s.x.bytes());
+        Tensor xdev = xin.to(W.device);
+        const Tensor* b = s.has_bias ? &s.bias : nullptr;
+        const bool gemv = s.M == 1;
+        switch (W.dtype) {
+            case Dtype::Q4_K: gemv ? linear_forward_q4k_fp16(W, b, xdev, s.y) : linear_forward_batched_q4k_fp16(W, b, xdev, s.y); break;
+            case Dtype::Q6_K: gemv ? linear_forward_q6k_fp16(W, b, xdev, s.y) : linear_forward_batched_q6k_fp16(W, b, xdev, s.y); break;
+            case Dtype::Q8_0: gemv ? linear_forward_q8_0_fp16(W, b, xdev, s.y) : linear_forward_batched_q8_0_fp16(W, b, xdev, s.y); break;
+            default: throw std::runtime_error("b200h_session_run: weight is not Q4_K / Q6_K / Q8_0");
+        }
+        s.y.copy_raw_to_host(y_host);
+    });
+}
+int b200h_session_y_dtype(void* sh) { return static_cast<int>(static_cast<Session*>(sh)->y.dtype); }
+
+// ---- GGUF ------------------------------------------------------------------------------------
+void* b200h_gguf_open(const char* path) {
+    gguf::File* f = nullptr;
+    if (guarded([&] { f = new gguf::File(gguf::File::open(path)); })) return nullptr;
+    return f;
+}
+void b200h_gguf_close(void* f) { delete static_cast<gguf::File*>(f); }
+int b200h_gguf_tensor_count(void* f) { return static_cast<int>(static_cast<gguf::File*>(f)->tensor_count()); }
+unsigned b200h_gguf_alignment(void* f) { return static_cast<gguf::File*>(f)->alignment(); }
+unsigned b200h_gguf_version(void* f) { return static_cast<gguf::File*>(f)->version(); }
+int b200h_gguf_meta_count(void* f) { return static_cast<int>(static_cast<gguf::File*>(f)->metadata().size()); }
+// Value of a metadata key rendered as text (scalars and strings; arrays as their length).
+int b200h_gguf_meta_text(void* fh, const char* key, char* out, int cap) {
+    return guarded([&] {
+        const gguf::Value& v = static_cast<gguf::File*>(fh)->get_meta(key);
+        std::string s;
+        using VT = gguf::ValueType;
+        switch (v.type) {
+            case VT::U8: s = std::to_string(v.scalar.u8); break;
+            case VT::I8: s = std::to_string(v.scalar.i8); break;
+            case VT::U16: s = std::to_string(v.scalar.u16); break;
+            case VT::I16: s = std::to_string(v.scalar.i16); break;
+            case VT::U32: s = std::to_string(v.scalar.u32); break;
+            case VT::I32: s = std::to_string(v.scalar.i32); break;
+            case VT::U64: s = std::to_string(v.scalar.u64); break;
+            case VT::I64: s = std::to_string(v.scalar.i64); break;
+            case VT::F32: s = std::to_string(v.scalar.f32); break;
+            case VT::F64: s = std::to_string(v.scalar.f64); break;
+            case VT::Bool: s = v.scalar.b ? "true" : "false"; break;
+            case VT::String: s = v.str; break;
+            case VT::Array: s = "array[" + std::to_string(v.array.size()) + "]"; break;
+        }
+        std::strncpy(out, s.c_str(), cap - 1);
+        out[cap - 1] = 0;
+    });
+}
+int b200h_gguf_tensor(void* fh, int i, char* name, int namelen, long long* shape8, int* ndims, unsigned* ggml_type,
+                      int* dtype, int* supported, unsigned long long* nbytes, long long* numel,
+                      unsigned long long* data_off_from_first) {
+    return guarded([&] {
+        const auto& ts = static_cast<gguf::File*>(fh)->tensors();
+        if (i < 0 || i >= static_cast<int>(ts.size())) throw std::runtime_error("gguf: tensor index out of range");
+        const gguf::TensorInfo& t = ts[i];
+        std::strncpy(name, t.name.c_str(), namelen - 1);
+        name[namelen - 1] = 0;
+        *ndims = static_cast<int>(t.shape.size());
+        for (int d = 0; d < *ndims && d < 8; ++d) shape8[d] = t.shape[d];
+        *ggml_type = t.ggml_type;
+        *dtype = static_cast<int>(t.dtype);
+        *supported = t.dtype_supported ? 1 : 0;
+        *nbytes = t.nbytes;
+        *numel = t.numel;
+        *data_off_from_first = static_cast<unsigned long long>(t.data - ts[0].data);
+    });
+}
+int b200h_shape_to_2d(const long long* shape, int n, int* rows, int* cols) {
+    return guarded([&] {
+        std::vector<std::int64_t> s(shape, shape + n);
+        auto rc = gguf::shape_to_2d(s);
+        *rows = rc.first;
+        *cols = rc.second;
+    });
+}
+// Rows [row_begin, row_end) of tensor i as (rows, cols) on `device` (< 0: host). NULL on error.
+void* b200h_gguf_upload_rows(void* fh, int i, int rows, int cols, int row_begin, int row_end, int device) {
+    Tensor* t = nullptr;
+    if (guarded([&] {
+            const auto& ts = static_cast<gguf::File*>(fh)->tensors();
+            if (i < 0 || i >= static_cast<int>(ts.size())) throw std::runtime_error("gguf: tensor index out of range");
+            auto up = std::make_unique<Tensor>();
+            gguf::upload_rows(ts[i], rows, cols, row_begin, row_end, device < 0 ? Device::CPU : Device::cuda(device), *up);
+            t = up.release();
+        }))
+        return nullptr;
+    return t;
+}
+
+}  // extern "C"

@@ -1,0 +1,224 @@
+// CUDA backend of the b200 host layer: the allocator table (stream-ordered pool
+// allocation, blocking host copies, event-ordered peer copies; brotensor
+// src/cuda/tensor.cu:56-187) and the nine quant ops. Each op validates like
+// brotensor's (src/cuda/q4k.cu:283-293, 326-420 and the q6k / q8_0 twins), resizes the
+// output, and calls the C-ABI of include/b200q.h on the thread's current stream.
+#include <cuda_runtime_api.h>
+
+#include <mutex>
+#include <stdexcept>
+#include <string>
+
+#include "b200q.h"
+#include "brotensor_b200/detail/dispatch.h"
+#include "brotensor_b200/runtime.h"
+
+namespace brotensor_b200::detail {
+
+namespace {
+
+[[noreturn]] void cuda_fail(cudaError_t e, const char* expr, const char* file, int line) {
+    (void)cudaGetLastError();
+    throw std::runtime_error("CUDA error " + std::to_string(static_cast<int>(e)) + " (" + cudaGetErrorString(e) + ") at " +
+                             file + ":" + std::to_string(line) + " in `" + expr + "`");
+}
+#define B200_CUDA_CHECK(expr)                                        \
+    do {                                                             \
+        const cudaError_t e_ = (expr);                               \
+        if (e_ != cudaSuccess) cuda_fail(e_, #expr, __FILE__, __LINE__); \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = 0;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) B200_CUDA_CHECK(cudaSetDevice(dev));
+    }
+    ~DeviceGuard() { cudaSetDevice(prev); }
+};
+
+cudaStream_t cur_stream(int dev) { return static_cast<cudaStream_t>(cuda_current_stream(dev)); }
+
+// ---- allocator table ----
+void* c_alloc(std::size_t n, int dev) {
+    if (!n) return nullptr;
+    DeviceGuard g(dev);
+    void* p = nullptr;
+    B200_CUDA_CHECK(cudaMallocAsync(&p, n, cur_stream(dev)));
+    return p;
+}
+void c_free(void* p, int dev) {
+    if (!p) return;
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(dev);
+    if (cudaFreeAsync(p, cur_stream(dev)) != cudaSuccess) (void)cudaGetLastError();
+    cudaSetDevice(prev);
+}
+void c_h2d(void* d, const void* s, std::size_t n, int dev) {
+    DeviceGuard g(dev);
+    B200_CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyHostToDevice, cur_stream(dev)));
+    B200_CUDA_CHECK(cudaStreamSynchronize(cur_stream(dev)));
+}
+void c_d2h(void* d, const void* s, std::size_t n, int dev) {
+    DeviceGuard g(dev);
+    B200_CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToHost, cur_stream(dev)));
+    B200_CUDA_CHECK(cudaStreamSynchronize(cur_stream(dev)));
+}
+void c_d2d(void* d, const void* s, std::size_t n, int dev) {
+    DeviceGuard g(dev);
+    B200_CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToDevice, cur_stream(dev)));
+}
+void c_peer(void* d, int ddev, const void* s, int sdev, std::size_t n) {
+    // ordered after the source device's stream, executed on the destination's
+    DeviceGuard g(sdev);
+    cudaEvent_t ev;
+    B200_CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    B200_CUDA_CHECK(cudaEventRecord(ev, cur_stream(sdev)));
+    B200_CUDA_CHECK(cudaSetDevice(ddev));
+    B200_CUDA_CHECK(cudaStreamWaitEvent(cur_stream(ddev), ev, 0));
+    B200_CUDA_CHECK(cudaMemcpyPeerAsync(d, ddev, s, sdev, n, cur_stream(ddev)));
+    B200_CUDA_CHECK(cudaEventDestroy(ev));
+}
+void c_zero(void* d, std::size_t n, int dev) {
+    DeviceGuard g(dev);
+    B200_CUDA_CHECK(cudaMemsetAsync(d, 0, n, cur_stream(dev)));
+}
+void c_sync(int dev) {
+    DeviceGuard g(dev);
+    B200_CUDA_CHECK(cudaDeviceSynchronize());
+}
+bool c_mem_info(std::size_t* f, std::size_t* t, int dev) {
+    DeviceGuard g(dev);
+    return cudaMemGetInfo(f, t) == cudaSuccess;
+}
+bool c_name(char* out, std::size_t cap, int dev) {
+    cudaDeviceProp p;
+    if (cudaGetDeviceProperties(&p, dev) != cudaSuccess) return false;
+    std::snprintf(out, cap, "%s", p.name);
+    return true;
+}
+
+// ---- the nine ops ----
+[[noreturn]] void op_fail(const char* op, const std::string& why) {
+    throw std::runtime_error(std::string("brotensor: ") + op + ": " + why);
+}
+bool act_dtype(Dtype d) { return d == Dtype::FP32 || d == Dtype::FP16 || d == Dtype::BF16; }
+
+void check_w(const Tensor& W, Dtype want, const char* dname, int block, const char* op) {
+    if (W.dtype != want) op_fail(op, std::string("W must be Dtype::") + dname);
+    if (W.cols % block != 0) op_fail(op, "W.cols must be a multiple of " + std::to_string(block));
+    if (W.rows <= 0 || W.cols <= 0) op_fail(op, "W has non-positive shape");
+}
+void check_status(int rc, const char* op) {
+    if (rc == B200Q_OK) return;
+    const char* msg = b200q_last_error();
+    if (rc == B200Q_ERR_CUDA) throw std::runtime_error(msg);  // already "CUDA error N (...) at file:line in `expr`"
+    op_fail(op, msg && *msg ? msg : b200q_status_str(rc));
+}
+
+// One scratch buffer per device for the tensor-core GEMM (activations in operand
+// layout). It only grows, outside any stream capture; calls on one device are ordered
+// by the stream they share.
+struct Scratch {
+    void* p = nullptr;
+    std::size_t n = 0;
+};
+Scratch g_scratch[64];
+std::mutex g_scratch_mu;
+void* scratch_for(int dev, std::size_t need) {
+    if (!need) return nullptr;
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    Scratch& s = g_scratch[dev & 63];
+    if (s.n < need) {
+        if (s.p) B200_CUDA_CHECK(cudaFree(s.p));
+        s.p = nullptr;
+        s.n = 0;
+        B200_CUDA_CHECK(cudaMalloc(&s.p, need));
+        s.n = need;
+    }
+    return s.p;
+}
+
+void dequant_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op, const Tensor& W, Tensor& out) {
+    check_w(W, wdt, dname, block, op);
+    // keep a pre-sized FP32 / BF16 destination, otherwise FP16 as in the reference
+    const bool keep = out.rows == W.rows && out.cols == W.cols && act_dtype(out.dtype) && out.data;
+    if (!keep) out.resize(W.rows, W.cols, Dtype::FP16);
+    if (W.rows == 0) return;
+    check_status(b200q_dequant(fmt, W.data, out.data, static_cast<int>(out.dtype), W.rows, W.cols,
+                               cuda_current_stream(W.device.index)), op);
+}
+
+void gemv_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op, const Tensor& W, const Tensor* bias,
+               const Tensor& x, Tensor& y) {
+    check_w(W, wdt, dname, block, op);
+    if (!act_dtype(x.dtype)) op_fail(op, "x must be FP16 (FP32 and BF16 are accepted as well)");
+    const int out = W.rows, K = W.cols;
+    if (x.rows != K || x.cols != 1) op_fail(op, "x shape must be (in, 1)");
+    if (bias) {
+        if (bias->dtype != x.dtype) op_fail(op, x.dtype == Dtype::FP16 ? "bias must be FP16" : "bias must have x's dtype");
+        if (bias->rows != out || bias->cols != 1) op_fail(op, "bias shape must be (out, 1)");
+    }
+    const bool keep = y.rows == out && y.cols == 1 && act_dtype(y.dtype) && y.data;
+    if (!keep) y.resize(out, 1, x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    if (out == 0) return;
+    const void* b = (bias && bias->size() > 0) ? bias->data : nullptr;
+    check_status(b200q_gemv(fmt, W.data, x.data, static_cast<int>(x.dtype), b, y.data, static_cast<int>(y.dtype), 1, out,
+                            K, cuda_current_stream(W.device.index)), op);
+}
+
+void batched_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op, const Tensor& W, const Tensor* bias,
+                  const Tensor& X, Tensor& Y) {
+    check_w(W, wdt, dname, block, op);
+    if (!act_dtype(X.dtype)) op_fail(op, "X must be FP16 (FP32 and BF16 are accepted as well)");
+    const int B = X.rows, K = X.cols, out = W.rows;
+    if (W.cols != K) op_fail(op, "shape mismatch (W.cols != X.cols)");
+    if (bias) {
+        if (bias->dtype != X.dtype) op_fail(op, X.dtype == Dtype::FP16 ? "bias must be FP16" : "bias must have X's dtype");
+        const bool ok = (bias->rows == out && bias->cols == 1) || (bias->rows == 1 && bias->cols == out);
+        if (!ok) op_fail(op, "bias shape must be (out,1) or (1,out)");
+    }
+    const bool keep = Y.rows == B && Y.cols == out && act_dtype(Y.dtype) && Y.data;
+    if (!keep) Y.resize(B, out, X.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    if (B == 0 || out == 0) return;
+    const void* b = (bias && bias->size() > 0) ? bias->data : nullptr;
+    const int dev = W.device.index;
+    std::size_t need = B > 8 ? b200q_gemm_workspace_bytes(fmt, static_cast<int>(X.dtype), B, out, K) : 0;
+    void* ws = scratch_for(dev, need);
+    check_status(b200q_linear(fmt, W.data, X.data, static_cast<int>(X.dtype), b, Y.data, static_cast<int>(Y.dtype), B,
+                              out, K, ws, need, cuda_current_stream(dev)), op);
+}
+
+#define B200_FMT_OPS(tag, FMT, DT, DNAME, BLOCK)                                                                 \
+    void dequant_##tag(const Tensor& W, Tensor& o) { dequant_impl(FMT, DT, DNAME, BLOCK, "dequant_" #tag "_to_fp16", W, o); } \
+    void gemv_##tag(const Tensor& W, const Tensor* b, const Tensor& x, Tensor& y) {                              \
+        gemv_impl(FMT, DT, DNAME, BLOCK, "linear_forward_" #tag "_fp16", W, b, x, y);                            \
+    }                                                                                                            \
+    void batched_##tag(const Tensor& W, const Tensor* b, const Tensor& X, Tensor& Y) {                           \
+        batched_impl(FMT, DT, DNAME, BLOCK, "linear_forward_batched_" #tag "_fp16", W, b, X, Y);                 \
+    }
+B200_FMT_OPS(q4k, B200Q_FMT_Q4_K, Dtype::Q4_K, "Q4_K", 256)
+B200_FMT_OPS(q6k, B200Q_FMT_Q6_K, Dtype::Q6_K, "Q6_K", 256)
+B200_FMT_OPS(q8_0, B200Q_FMT_Q8_0, Dtype::Q8_0, "Q8_0", 32)
+
+}  // namespace
+
+// The registration point: what brotensor does in fill_cuda_vtable_specialised
+// (src/cuda/concat.cu:359-372) for the same nine slots.
+void fill_cuda_tables(OpsVTable& ops, AllocVTable& alloc) {
+    ops.dequant_q4k_to_fp16 = dequant_q4k;
+    ops.linear_forward_q4k_fp16 = gemv_q4k;
+    ops.linear_forward_batched_q4k_fp16 = batched_q4k;
+    ops.dequant_q8_0_to_fp16 = dequant_q8_0;
+    ops.linear_forward_q8_0_fp16 = gemv_q8_0;
+    ops.linear_forward_batched_q8_0_fp16 = batched_q8_0;
+    ops.dequant_q6k_to_fp16 = dequant_q6k;
+    ops.linear_forward_q6k_fp16 = gemv_q6k;
+    ops.linear_forward_batched_q6k_fp16 = batched_q6k;
+    alloc.alloc = c_alloc; alloc.free = c_free;
+    alloc.memcpy_h2d = c_h2d; alloc.memcpy_d2h = c_d2h; alloc.memcpy_d2d = c_d2d; alloc.memcpy_peer = c_peer;
+    alloc.memset_zero = c_zero; alloc.sync = c_sync; alloc.mem_info = c_mem_info; alloc.device_name = c_name;
+}
+
+}  // namespace brotensor_b200::detail

@@ -1,0 +1,40 @@
+// Public op wrappers: resolve the device, refuse a null slot, pin an unsized output to
+// the op's device, call the backend (brotensor src/ops.cpp:2049-2125).
+#include "brotensor_b200/detail/dispatch.h"
+#include "brotensor_b200/ops/quant.h"
+
+namespace brotensor_b200 {
+
+#define B200_DEQUANT_OP(name)                                                   \
+    void name(const Tensor& W, Tensor& out) {                                   \
+        const detail::OpsVTable& v = detail::dispatch_with_opts(W, {&out});     \
+        const Device dev = W.data ? W.device : (out.data ? out.device : W.device); \
+        if (!v.name) detail::throw_not_implemented(#name, dev);                 \
+        detail::adopt_output(out, dev);                                         \
+        v.name(W, out);                                                         \
+    }
+
+#define B200_LINEAR_OP(name)                                                          \
+    void name(const Tensor& W, const Tensor* bias, const Tensor& x, Tensor& y) {      \
+        const detail::OpsVTable& v = detail::dispatch_with_opts(W, {bias, &x, &y});   \
+        Device dev = W.device;                                                        \
+        if (W.data) dev = W.device;                                                   \
+        else if (bias && bias->data) dev = bias->device;                              \
+        else if (x.data) dev = x.device;                                              \
+        else if (y.data) dev = y.device;                                              \
+        if (!v.name) detail::throw_not_implemented(#name, dev);                       \
+        detail::adopt_output(y, dev);                                                 \
+        v.name(W, bias, x, y);                                                        \
+    }
+
+B200_DEQUANT_OP(dequant_q4k_to_fp16)
+B200_LINEAR_OP(linear_forward_q4k_fp16)
+B200_LINEAR_OP(linear_forward_batched_q4k_fp16)
+B200_DEQUANT_OP(dequant_q8_0_to_fp16)
+B200_LINEAR_OP(linear_forward_q8_0_fp16)
+B200_LINEAR_OP(linear_forward_batched_q8_0_fp16)
+B200_DEQUANT_OP(dequant_q6k_to_fp16)
+B200_LINEAR_OP(linear_forward_q6k_fp16)
+B200_LINEAR_OP(linear_forward_batched_q6k_fp16)
+
+}  // namespace brotensor_b200
