@@ -256,6 +256,72 @@ def test_config2_q8_0_small_batch(M, cpu_oracle):
     assert oracle.rel_l2(got, want) < REL_L2
 
 
+# ---------------------------------------------------------------- prefill GEMM (tensor cores)
+
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("M,N,K", [(9, 64, 256), (16, 128, 512), (33, 200, 1024), (100, 1000, 2048), (256, 384, 512),
+                                   (300, 130, 768), (512, 256, 4096), (700, 77, 512)])
+def test_gemm_matches_oracle(fmt, name, M, N, K, cpu_oracle):
+    Wh = synth.make_blocks(fmt, N, K, seed=M + N + K)
+    Xh = synth.make_activations(M, K, seed=M * 3 + 1)
+    bh = synth.make_activations(1, N, seed=5)[0]
+    want = cpu_oracle.matmul(fmt, Wh, Xh, bias=bh, threads=8)
+    ops.tc_calls_consume(fmt)
+    got = ops.gemm(fmt, dev(Wh), dev(Xh), N, bias=dev(bh))
+    assert ops.tc_calls_consume(fmt) >= 1  # the tensor-core kernel ran, not the GEMV passes
+    assert got.dtype == torch.float32 and tuple(got.shape) == (M, N)
+    e = oracle.rel_l2(host_f32(got), want)
+    assert e < REL_L2, f"rel_l2={e}"
+    # 16-bit activations and outputs
+    xt, xr = as_dtype_np(Xh, "bf16")
+    want16 = cpu_oracle.matmul(fmt, Wh, xr, threads=8)
+    got16 = ops.gemm(fmt, dev(Wh), xt.cuda(), N, out_dtype=torch.float16)
+    assert oracle.rel_l2(host_f32(got16), want16) < REL_L2 + 2.0 ** -12
+
+
+def test_gemm_and_gemv_agree_on_shared_rows():
+    """tests/test_quant_prefill_parity.cpp: the prefill path against per-token decode GEMVs."""
+    fmt, N, K, M = oracle.Q4_K, 512, 2048, 24
+    W = dev(synth.make_blocks(fmt, N, K, seed=61))
+    X = dev(synth.make_activations(M, K, seed=62))
+    Y = ops.gemm(fmt, W, X, N)
+    for m0 in range(0, M, 8):
+        y = ops.gemv(fmt, W, X[m0:m0 + 8].contiguous(), N)
+        assert oracle.rel_l2(host_f32(Y[m0:m0 + 8]), host_f32(y)) < 1e-3
+
+
+def test_gemm_workspace_contract():
+    from brotensor_b200 import B200QError, _capi
+    fmt, N, K, M = oracle.Q4_K, 128, 512, 32
+    L = _capi.lib()
+    need = L.b200q_gemm_workspace_bytes(fmt, _capi.F32, M, N, K)
+    assert need == (K // 64) * 32 * 128
+    assert L.b200q_gemm_workspace_bytes(fmt, _capi.F32, 4, N, K) == 0  # decode sizes need none
+    W = dev(synth.make_blocks(fmt, N, K, seed=1))
+    X = dev(synth.make_activations(M, K, seed=1))
+    with pytest.raises(B200QError) as ei:
+        ops.gemm(fmt, W, X, N, ws=torch.empty(need - 256, dtype=torch.uint8, device="cuda"))
+    assert ei.value.status == _capi.ERR_WORKSPACE
+
+
+def test_config3_q4k_prefill_512(cpu_oracle):
+    """Config 3 at full size: 512 tokens x 14336 x 4096; a strided subset of the output
+    columns is checked against the oracle, all of them through linearity in X."""
+    fmt, N, K, M = oracle.Q4_K, 14336, 4096, 512
+    Wh = synth.make_blocks(fmt, N, K, seed=3)
+    Xh = synth.make_activations(M, K, seed=3)
+    W, X = dev(Wh), dev(Xh)
+    Y = ops.gemm(fmt, W, X, N)
+    rows = np.arange(5, N, 97)
+    Wsub = Wh.reshape(N, -1)[rows].reshape(-1)
+    want = cpu_oracle.matmul(fmt, Wsub, Xh, threads=16)
+    assert oracle.rel_l2(host_f32(Y[:, torch.from_numpy(rows).cuda()]), want) < REL_L2
+    Yb = ops.gemm(fmt, W, X.bfloat16(), N)
+    assert oracle.rel_l2(host_f32(Yb), host_f32(Y)) < 6e-3  # bf16 rounding of x alone is 2^-9 / sqrt(3)
+    Y2 = ops.gemm(fmt, W, X * 2.0, N)
+    assert oracle.rel_l2(host_f32(Y2), 2.0 * host_f32(Y)) < 1e-6
+
+
 # ---------------------------------------------------------------- error behaviour
 
 def test_bad_arguments_raise():
