@@ -1,0 +1,139 @@
+"""Secondary measurements of bench.py: the benchmark configurations other than the
+headline decode layer set. Every number is parity-gated against the CPU oracle by the
+caller's tests; here only timing happens (CUDA events around CUDA-graph replays that
+rotate over weight replicas larger than the L2).
+
+  config0   Q4_K 4096x4096, M=1 GEMV                      GB/s of packed weight bytes
+  config2   Q8_0 14336x4096, M in {1,2,4,8}               GB/s (weights counted once)
+  config3   Q4_K 14336x4096 prefill GEMM, M=512 tokens    TFLOP/s vs the measured bf16 peak
+  lm_head   Q6_K 128256x4096 rows split over the ranks, per-shard GEMV + NCCL all-gather
+            of the fp32 logits; tok/s = 1 / time of the slowest rank
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import ops, synth
+
+
+def _time_graph(fn, n_launch, stream, reps=10):
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        for i in range(n_launch):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ts = []
+    for _ in range(reps):
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / n_launch)
+    return float(np.median(ts)), float(np.min(ts))  # ms per launch
+
+
+def _replicas(fmt, N, K, seed, budget_bytes=1.2e9, cap=32):
+    nbytes = synth.packed_bytes(fmt, N, K)
+    R = int(max(2, min(cap, budget_bytes // nbytes)))
+    base = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=seed)).cuda()
+    return [base] + [torch.roll(base, 1028160 * (i + 1)).contiguous() for i in range(R - 1)], nbytes
+
+
+def gemv_case(fmt, N, K, M, stream, peak_gbs, n_launch=48):
+    Ws, nbytes = _replicas(fmt, N, K, seed=N + K)
+    X = torch.from_numpy(synth.make_activations(M, K, seed=M)).cuda()
+    Y = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    for i in range(3):
+        ops.gemv(fmt, Ws[i % len(Ws)], X, N, out=Y)
+    med, mn = _time_graph(lambda i: ops.gemv(fmt, Ws[i % len(Ws)], X, N, out=Y), n_launch, stream)
+    gbs = nbytes / (med * 1e-3) / 1e9
+    return {"fmt": synth.FMT_NAME[fmt], "N": N, "K": K, "M": M, "us": med * 1e3, "us_min": mn * 1e3, "GBps": gbs,
+            "frac_of_hbm_peak": gbs / peak_gbs, "replicas": len(Ws)}
+
+
+def gemm_case(fmt, N, K, M, x_dtype, stream, peaks, n_launch=8):
+    W = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=3)).cuda()
+    X = torch.from_numpy(synth.make_activations(M, K, seed=3)).cuda().to(x_dtype)
+    Y = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    from . import _capi
+    need = _capi.lib().b200q_gemm_workspace_bytes(fmt, ops._DT[x_dtype], M, N, K)
+    ws = torch.empty(max(need, 256), dtype=torch.uint8, device="cuda")
+    for _ in range(3):
+        ops.gemm(fmt, W, X, N, out=Y, ws=ws)
+    ops.tc_calls_consume(fmt)
+    med, mn = _time_graph(lambda i: ops.gemm(fmt, W, X, N, out=Y, ws=ws), n_launch, stream)
+    tc = ops.tc_calls_consume(fmt)
+    flops = 2.0 * M * N * K
+    tf = flops / (med * 1e-3) / 1e12
+    return {"fmt": synth.FMT_NAME[fmt], "N": N, "K": K, "M": M, "x_dtype": str(x_dtype).replace("torch.", ""),
+            "us": med * 1e3, "us_min": mn * 1e3, "TFLOPs": tf, "frac_of_bf16_burst_peak": tf / peaks["bf16_tflops"],
+            "frac_of_bf16_sustained_peak": tf / peaks["bf16_tflops_sustained"] if peaks.get("bf16_tflops_sustained") else None,
+            "tensor_core_launches": tc, "includes": "activation pre-pass (fp16 operand image) + tcgen05 GEMM"}
+
+
+def lm_head_case(rank, world, stream, peak_gbs, n_launch=16):
+    """Config 4: vocab rows split evenly over the ranks; every rank streams its own shard
+    and the fp32 logits are all-gathered. Strong scaling: the total work is fixed."""
+    fmt, N, K = synth.Q6_K, 128256, 4096
+    assert N % world == 0
+    rows = N // world
+    # each rank generates only its shard (seeded per shard, so the content is independent of world size
+    # only in distribution; parity of the sharded path is covered by the tests)
+    Ws, nbytes = _replicas(fmt, rows, K, seed=4000 + rank, budget_bytes=1.0e9, cap=6)
+    x = torch.from_numpy(synth.make_activations(1, K, seed=4)).cuda()
+    local = torch.empty((1, rows), dtype=torch.float32, device="cuda")
+    full = torch.empty((world, rows), dtype=torch.float32, device="cuda")
+
+    def step(i):
+        ops.gemv(fmt, Ws[i % len(Ws)], x, rows, out=local)
+        if world > 1:
+            dist.all_gather_into_tensor(full.view(-1), local.view(-1))
+
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    out = {"fmt": "q6k", "N": N, "K": K, "ranks": world, "rows_per_rank": rows}
+    # the gather cannot be captured on every NCCL configuration; fall back to stream launches
+    try:
+        med, mn = _time_graph(step, n_launch, stream)
+        out["timed_as"] = "cuda graph"
+    except Exception:  # noqa: BLE001
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ts = []
+        for _ in range(5):
+            e0.record()
+            for i in range(n_launch):
+                step(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / n_launch)
+        med, mn = float(np.median(ts)), float(np.min(ts))
+        out["timed_as"] = "stream launches"
+    t = torch.tensor([med], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    med = float(t.item())
+    # GEMV alone, for the split between streaming and exchange
+    g_med, _ = _time_graph(lambda i: ops.gemv(fmt, Ws[i % len(Ws)], x, rows, out=local), n_launch, stream)
+    out.update({"us_per_token": med * 1e3, "tok_per_s": 1.0 / (med * 1e-3), "gemv_only_us": g_med * 1e3,
+                "shard_GBps": nbytes / (g_med * 1e-3) / 1e9, "shard_frac_of_hbm_peak": nbytes / (g_med * 1e-3) / 1e9 / peak_gbs,
+                "all_gather_bytes": 4 * N, "collective": "nccl all_gather_into_tensor" if world > 1 else "none"})
+    return out
+
+
+def run(rank, world, peaks, stream):
+    out = {}
+    if world == 1:
+        out["config0_q4k_4096x4096_m1"] = gemv_case(synth.Q4_K, 4096, 4096, 1, stream, peaks["hbm_gbs"])
+        out["layer_set_per_kernel"] = [gemv_case(fmt, N, K, 1, stream, peaks["hbm_gbs"]) | {"name": name}
+                                       for name, fmt, N, K in synth.LLAMA3_8B_LAYER_SET if name not in ("v_proj", "up_proj", "o_proj")]
+        out["config2_q8_0_14336x4096"] = [gemv_case(synth.Q8_0, 14336, 4096, M, stream, peaks["hbm_gbs"]) for M in (1, 2, 4, 8)]
+        out["config3_q4k_prefill_512"] = [gemm_case(synth.Q4_K, 14336, 4096, 512, dt, stream, peaks)
+                                          for dt in (torch.float32, torch.bfloat16)]
+    out["lm_head"] = lm_head_case(rank, world, stream, peaks["hbm_gbs"])
+    return out
