@@ -283,15 +283,17 @@ static void run_fmt(const FmtCase& c) {
         CHECK(y.dtype == Dtype::FP16 && y.rows == OUT && y.cols == 1);
         bt::sync_all();
         std::vector<uint16_t> got = y.to_host_vector_fp16();
-        float max_abs = 0;
-        for (int r = 0; r < OUT; ++r) max_abs = std::fmax(max_abs, std::fabs(bt::fp16_bits_to_fp32(got[r]) - y_ref[r]));
-        CHECK(max_abs < 5e-2f);
+        bool within = true;
+        for (int r = 0; r < OUT; ++r)
+            if (std::fabs(bt::fp16_bits_to_fp32(got[r]) - y_ref[r]) > 3e-2f + 5e-2f * std::fabs(y_ref[r])) within = false;
+        CHECK(within);
         Tensor bias = Tensor::from_host_fp16_on(dev, bh.data(), OUT, 1), yb;
         c.gemv(W, &bias, x, yb);
         got = yb.to_host_vector_fp16();
-        max_abs = 0;
-        for (int r = 0; r < OUT; ++r) max_abs = std::fmax(max_abs, std::fabs(bt::fp16_bits_to_fp32(got[r]) - yb_ref[r]));
-        CHECK(max_abs < 5e-2f);
+        within = true;
+        for (int r = 0; r < OUT; ++r)
+            if (std::fabs(bt::fp16_bits_to_fp32(got[r]) - yb_ref[r]) > 3e-2f + 5e-2f * std::fabs(yb_ref[r])) within = false;
+        CHECK(within);
         // FP32 activations -> FP32 output, tight bound
         Tensor x32 = Tensor::from_host_on(dev, xf.data(), IN, 1), y32;
         c.gemv(W, nullptr, x32, y32);
@@ -326,10 +328,17 @@ static void run_fmt(const FmtCase& c) {
         bt::sync_all();
         const unsigned long long calls = c.tc_calls();
         std::vector<uint16_t> got = Y.to_host_vector_fp16();
+        // random scale bytes make large outputs, so the bound is the mixed one of the reference's
+        // prefill test (tests/test_quant_prefill_parity.cpp:133-145): |e| <= 3e-2 + 5e-2 * |ref|
         float max_abs = 0;
-        for (size_t i = 0; i < got.size(); ++i) max_abs = std::fmax(max_abs, std::fabs(bt::fp16_bits_to_fp32(got[i]) - Yref[i]));
+        bool within = true;
+        for (size_t i = 0; i < got.size(); ++i) {
+            const float e = std::fabs(bt::fp16_bits_to_fp32(got[i]) - Yref[i]);
+            max_abs = std::fmax(max_abs, e);
+            if (e > 3e-2f + 5e-2f * std::fabs(Yref[i])) within = false;
+        }
         std::printf("  batched B=%d tc_calls=%llu max_abs=%g\n", B, calls, max_abs);
-        CHECK(max_abs < (B >= 32 ? 1e-1f : 5e-2f));
+        CHECK(within);
         if (B <= 8) CHECK(calls == 0);  // small batches stream the weight once through the decode GEMV
         else CHECK(calls > 0);          // prefill batches run on the tensor cores
         Tensor bias_row = Tensor::zeros_on(dev, 1, OUT, Dtype::FP16), Yb;  // (1,out) bias is accepted for batched
