@@ -50,10 +50,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded mbarrier wait with an abort flag shared by the CTA. Returns false when
 // the wait was abandoned (by this thread's timeout or because another thread of
 // the CTA already gave up).
+template <bool kSpinFirst = false>
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                               int code) {
-    for (int i = 0; i < 128; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+    // Optional fast path for a single latency-critical thread: non-blocking probes, so a
+    // phase that completes soon is seen at once instead of after a parked time slice. Whole
+    // warps must not use it: their probes fill the shared-memory pipeline the other warps need.
+    if constexpr (kSpinFirst) {
+        for (int i = 0; i < 256; ++i)
+            if (mbar_test_wait(bar, parity)) return true;
+    }
     const uint64_t t0 = global_timer_ns();
     for (;;) {
         for (int i = 0; i < 64; ++i)
