@@ -29,6 +29,8 @@ SYMBOLS = [
     ("b200q_gemv", _i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     ("b200q_gemm_workspace_bytes", _sz, [_i, _i, _i, _i, _i]),
     ("b200q_gemm", _i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
+    ("b200q_gemm_static_max_bytes", _sz, []),
+    ("b200q_gemm_static", _i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     ("b200q_linear", _i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     ("b200q_tc_calls_consume", C.c_ulonglong, [_i]),
     ("brotensor_q4k_wmma_calls_consume", C.c_ulonglong, []),

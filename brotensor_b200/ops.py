@@ -51,8 +51,9 @@ def _linear(entry: str, fmt, W, X, N, bias, out, out_dtype, ws):
     L = capi.lib()
     bptr = bias.data_ptr() if bias is not None else None
     with torch.cuda.device(W.device):
-        if entry == "gemv":
-            rc = L.b200q_gemv(fmt, W.data_ptr(), X.data_ptr(), _DT[X.dtype], bptr, out.data_ptr(), _DT[out.dtype],
+        if entry in ("gemv", "gemm_static"):
+            f = L.b200q_gemv if entry == "gemv" else L.b200q_gemm_static
+            rc = f(fmt, W.data_ptr(), X.data_ptr(), _DT[X.dtype], bptr, out.data_ptr(), _DT[out.dtype],
                               M, N, K, _stream())
         else:
             need = L.b200q_gemm_workspace_bytes(fmt, _DT[X.dtype], M, N, K)
@@ -73,6 +74,11 @@ def gemv(fmt, W, X, N, bias=None, out=None, out_dtype=None):
 def gemm(fmt, W, X, N, bias=None, out=None, out_dtype=None, ws=None):
     """Prefill GEMM on the tensor cores, any M."""
     return _linear("gemm", fmt, W, X, N, bias, out, out_dtype, ws)
+
+
+def gemm_static(fmt, W, X, N, bias=None, out=None, out_dtype=None):
+    """The GEMM with its scratch in the library's fixed device array: makes no allocation."""
+    return _linear("gemm_static", fmt, W, X, N, bias, out, out_dtype, None)
 
 
 def linear(fmt, W, X, N, bias=None, out=None, out_dtype=None, ws=None):

@@ -94,6 +94,27 @@ int b200q_gemm(int fmt, const void* W, const void* X, int x_dtype, const void* b
                int M, int N, int K, void* ws, size_t ws_bytes, void* stream);
 
 /*
+ * b200q_gemm without a workspace argument and without any allocation: the
+ * activation operand image goes to a fixed array in the library's own device
+ * memory (b200q_gemm_static_max_bytes() bytes per device, 8 MiB: 512 tokens
+ * at K = 8192, 1024 at K = 4096). For callers that cannot allocate: inside a
+ * stream capture, under a fixed-footprint promise, or behind a plugin slot
+ * that carries no workspace pointer. Problems whose
+ * b200q_gemm_workspace_bytes() exceeds the array fail with
+ * B200Q_ERR_WORKSPACE and nothing is launched.
+ * All calls on one device share the one array: calls on the same stream are
+ * ordered and safe; calls on different streams (or threads) that can overlap
+ * race on it and must be ordered by the caller. Nothing in the array has to
+ * be cleared between calls: every byte the GEMM reads is rewritten first.
+ * The first call on a device does one-time set-up (symbol address lookup,
+ * kernel attributes), so make one call before beginning a stream capture.
+ * No counterpart in brotensor, whose batched ops allocate per call.
+ */
+size_t b200q_gemm_static_max_bytes(void);
+int b200q_gemm_static(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
+                      int M, int N, int K, void* stream);
+
+/*
  * Routing used by the batched ops: M <= 8 goes to b200q_gemv, larger M to
  * b200q_gemm (brotensor routes B >= 4 to its WMMA kernel, q4k_wmma.cu:320-326).
  */
