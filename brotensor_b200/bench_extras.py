@@ -15,7 +15,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-from . import ops, synth
+from . import ops, shard, synth
 
 
 def _time_graph(fn, n_launch, stream, reps=10):
@@ -79,8 +79,9 @@ def lm_head_case(rank, world, stream, peak_gbs, n_launch=16):
     """Config 4: vocab rows split evenly over the ranks; every rank streams its own shard
     and the fp32 logits are all-gathered. Strong scaling: the total work is fixed."""
     fmt, N, K = synth.Q6_K, 128256, 4096
-    assert N % world == 0
-    rows = N // world
+    b, e = shard.row_range(N, world, rank, align=16)
+    rows = e - b
+    assert rows * world == N, "the LM-head benchmark wants equal shards"
     # each rank generates only its shard (seeded per shard, so the content is independent of world size
     # only in distribution; parity of the sharded path is covered by the tests)
     Ws, nbytes = _replicas(fmt, rows, K, seed=4000 + rank, budget_bytes=1.0e9, cap=6)
@@ -90,7 +91,7 @@ def lm_head_case(rank, world, stream, peak_gbs, n_launch=16):
 
     def step(i):
         ops.gemv(fmt, Ws[i % len(Ws)], x, rows, out=local)
-        if world > 1:
+        if world > 1:  # shard.all_gather_rows's equal-shard case, with the output preallocated
             dist.all_gather_into_tensor(full.view(-1), local.view(-1))
 
     for i in range(3):
