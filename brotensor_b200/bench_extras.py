@@ -121,10 +121,57 @@ def lm_head_case(rank, world, stream, peak_gbs, n_launch=16):
     med = float(t.item())
     # GEMV alone, for the split between streaming and exchange
     g_med, _ = _time_graph(lambda i: ops.gemv(fmt, Ws[i % len(Ws)], x, rows, out=local), n_launch, stream)
+    step(0)  # the gathered form on replica 0: the fused form must reproduce it
+    torch.cuda.synchronize()
+    out["fused"] = _fused_head(fmt, rows, K, b, N, rank, world, Ws, x, stream, n_launch, full if world > 1 else local)
     out.update({"us_per_token": med * 1e3, "tok_per_s": 1.0 / (med * 1e-3), "gemv_only_us": g_med * 1e3,
                 "shard_GBps": nbytes / (g_med * 1e-3) / 1e9, "shard_frac_of_hbm_peak": nbytes / (g_med * 1e-3) / 1e9 / peak_gbs,
                 "all_gather_bytes": 4 * N, "collective": "nccl all_gather_into_tensor" if world > 1 else "none"})
     return out
+
+
+def _fused_head(fmt, rows, K, row0, N, rank, world, Ws, x, stream, n_launch, ref_full):
+    """The one-kernel form: the shard GEMV stores its rows into every rank's result vector over
+    NVLink and signals arrival itself (brotensor_b200::ShardedHead); no collective call."""
+    from . import hostapi
+    try:
+        hostapi.init()
+        dev = torch.cuda.current_device()
+        # the head's weights are Tensors of the host layer; they alias the replicas already on the device
+        weights = [hostapi.Weight.view(fmt, w.data_ptr(), rows, K, dev) for w in Ws]
+
+        def exchange(h):
+            outl = [None] * world
+            dist.all_gather_object(outl, h)
+            return outl
+
+        head = hostapi.ShardedHead(weights[0], row0, N, rank, world, exchange if world > 1 else None)
+        hostapi.set_stream(torch.cuda.current_stream().cuda_stream, dev)
+        # parity with the gathered form first: same kernel arithmetic, so bitwise
+        head.run(x.data_ptr(), K, 0, weights[0])
+        same = bool(np.array_equal(head.logits(), ref_full.reshape(-1).cpu().numpy()))
+        if world > 1:
+            dist.barrier()
+
+        def step(i):
+            head.run(x.data_ptr(), K, 0, weights[i % len(weights)])
+
+        hostapi.set_stream(stream.cuda_stream, dev)
+        med, mn = _time_graph(step, n_launch, stream)
+        hostapi.set_stream(torch.cuda.current_stream().cuda_stream, dev)
+        t = torch.tensor([med], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        med = float(t.item())
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        status = ops.device_status()
+        head.close()
+        return {"us_per_token": med * 1e3, "tok_per_s": 1.0 / (med * 1e-3), "matches_gathered_bitwise": same,
+                "device_status": status, "exchange": "peer stores + arrival words inside the GEMV kernel (CUDA IPC memory)"}
+    except Exception as ex:  # noqa: BLE001
+        return {"error": repr(ex)}
 
 
 def run(rank, world, peaks, stream):

@@ -17,7 +17,7 @@ int launch_gemv_simple(int fmt, const void* W, const void* X, int x_dtype, const
 int launch_gemv_stream(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
                        int M, int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken);
 int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
-                   int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken);
+                   int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh);
 void stream_set_option(int which, int value);
 void dp_set_groups(int v);
 int dp_get_groups();
@@ -161,7 +161,7 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
     // 0 = automatic, 1 = plain-load kernel, 2 = warp-MMA streaming kernel, 3 = integer-dot streaming kernel
     if (g_opt_gemv_path == 0 || g_opt_gemv_path == 3) {
         bool taken = false;
-        if (int rc = launch_gemv_dp(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->smem_optin - 1024, d->status, st, &taken))
+        if (int rc = launch_gemv_dp(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->smem_optin - 1024, d->status, st, &taken, nullptr))
             return rc;
         if (taken) return B200Q_OK;
         if (g_opt_gemv_path == 3)
@@ -176,6 +176,38 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
             return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the streaming kernel", M, N, K, fmt);
     }
     return launch_gemv_simple(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
+}
+
+int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
+                     int row_offset, int total_rows, int rank, int world, void* const* peer_out,
+                     void* const* peer_flags, void* state, void* stream) {
+    static float dummy_y;  // check_linear_args wants a non-null result pointer; the sharded form has none
+    if (int rc = check_linear_args("gemv_shard", fmt, W_shard, x, x_dtype, &dummy_y, B200Q_DT_F32, 1, rows, K)) return rc;
+    if (world < 1 || world > kMaxShardRanks || rank < 0 || rank >= world)
+        return fail(B200Q_ERR_BAD_ARG, "gemv_shard: rank %d of %d (at most %d ranks)", rank, world, kMaxShardRanks);
+    if (row_offset < 0 || total_rows <= 0 || (long long)row_offset + rows > total_rows)
+        return fail(B200Q_ERR_BAD_ARG, "gemv_shard: rows [%d, %d) do not lie in [0, %d)", row_offset, row_offset + rows, total_rows);
+    if (!peer_out || !peer_flags || !state) return fail(B200Q_ERR_BAD_ARG, "gemv_shard: null peer table or state");
+    for (int q = 0; q < world; ++q)
+        if (!peer_out[q] || !peer_flags[q]) return fail(B200Q_ERR_BAD_ARG, "gemv_shard: null pointer for rank %d", q);
+    if (rows == 0) return fail(B200Q_ERR_UNSUPPORTED, "gemv_shard: an empty shard cannot signal its arrival");
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    ShardOut sh;
+    sh.world = world;
+    sh.rank = rank;
+    sh.row_offset = row_offset;
+    sh.total_rows = total_rows;
+    sh.out = reinterpret_cast<float* const*>(peer_out);
+    sh.flags = reinterpret_cast<unsigned int* const*>(peer_flags);
+    sh.state = static_cast<unsigned int*>(state);
+    bool taken = false;
+    if (int rc = launch_gemv_dp(fmt, W_shard, x, x_dtype, bias_shard, nullptr, B200Q_DT_F32, 1, rows, K, d->sms,
+                                d->smem_optin - 1024, d->status, static_cast<cudaStream_t>(stream), &taken, &sh))
+        return rc;
+    if (!taken)
+        return fail(B200Q_ERR_UNSUPPORTED, "gemv_shard: shape (rows %d, K %d, fmt %d) or weight alignment is outside the streaming kernel", rows, K, fmt);
+    return B200Q_OK;
 }
 
 size_t b200q_gemm_workspace_bytes(int fmt, int x_dtype, int M, int N, int K) {

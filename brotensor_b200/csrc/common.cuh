@@ -26,6 +26,7 @@ constexpr int kDevTimeoutFull = 101;   // consumer gave up waiting for a filled 
 constexpr int kDevTimeoutEmpty = 102;  // producer gave up waiting for a free stage
 constexpr int kDevTimeoutMma = 103;    // epilogue gave up waiting for the tensor core
 constexpr int kDevTimeoutTmem = 104;
+constexpr int kDevTimeoutPeer = 105;   // sharded GEMV gave up waiting for a peer rank's arrival flag
 
 template <int FMT>
 struct Blk;
@@ -49,6 +50,15 @@ struct Blk<kQ8_0> {
 // ---- host-side error plumbing ------------------------------------------------
 void set_error(const char* fmt, ...);
 int fail(int code, const char* fmt, ...);
+
+constexpr int kMaxShardRanks = 8;
+// Host-side description of a row-sharded GEMV output (StreamParams::sh_* on the device side).
+struct ShardOut {
+    int world, rank, row_offset, total_rows;
+    float* const* out;
+    unsigned int* const* flags;
+    unsigned int* state;
+};
 int* device_status_word(int dev);  // device pointer to this device's status word, or nullptr
 
 #define B200Q_CUDA_TRY(expr)                                                                          \

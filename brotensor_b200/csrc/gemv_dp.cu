@@ -457,6 +457,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
 
     // ---- consumers
     grid_dep_wait();  // activations (and Y) belong to the stream-ordered predecessor
+    // launch counter of the sharded form: stable while this launch runs (only its last CTA bumps it)
+    const unsigned int sh_epoch = p.sh_world > 0 ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
+    const unsigned int sh_buf = (sh_epoch + 1u) & 1u;
     if (p.x_dtype == B200Q_DT_F32) stage_x16<FMT, float>(p, sbase, tid, kConsumers * 32);
     else if (p.x_dtype == B200Q_DT_F16) stage_x16<FMT, __half>(p, sbase, tid, kConsumers * 32);
     else stage_x16<FMT, __nv_bfloat16>(p, sbase, tid, kConsumers * 32);
@@ -522,9 +525,48 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                     else s += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
                 }
                 const size_t o = (size_t)m * p.N + n;
-                if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
+                if (p.sh_world > 0) {
+                    // sharded output: the row goes to every rank's result vector (own included) with
+                    // plain peer stores over NVLink; which of the two vectors is this launch's parity
+                    const size_t go = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n);
+                    for (int q = 0; q < p.sh_world; ++q) p.sh_out[q][go] = s;
+                } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
                 else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(s);
                 else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(s);
+            }
+        }
+    }
+    if (p.sh_world > 0) {
+        // Every consumer warp gets here (aborted ones too). When the whole grid has stored its
+        // rows, the last CTA publishes this rank's arrival to all ranks and waits - bounded -
+        // until every rank has arrived at this one, so that on return from the kernel the
+        // full result vector of this launch is complete in this rank's memory.
+        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+        if (tid == 0) {
+            __threadfence_system();  // this CTA's peer stores before its arrival
+            const unsigned int done = atomicAdd(&p.sh_state[0], 1u);
+            if (done == gridDim.x - 1) {
+                p.sh_state[0] = 0;
+                const unsigned int epoch = sh_epoch + 1u;
+                __threadfence_system();
+                for (int q = 0; q < p.sh_world; ++q)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[q] + p.sh_rank), "r"(epoch) : "memory");
+                const uint64_t t0 = global_timer_ns();
+                bool ok = true;
+                for (int q = 0; q < p.sh_world && ok; ++q) {
+                    for (;;) {
+                        unsigned int v;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
+                        if ((int)(v - epoch) >= 0) break;
+                        if (global_timer_ns() - t0 > 1000000000ull) {  // one second: a peer never arrived
+                            if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                *(volatile unsigned int*)&p.sh_state[1] = epoch;
+                __threadfence();
             }
         }
     }
@@ -626,7 +668,7 @@ static int launch_dp_g(const StreamParams& p, int ng, int grid, size_t smem, cud
 
 template <int FMT>
 static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N,
-                       int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken) {
+                       int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh) {
     StreamParams p = {};
     int grid = 0;
     size_t smem = 0;
@@ -644,6 +686,17 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
     p.status = status;
     p.x_dtype = x_dtype;
     p.y_dtype = y_dtype;
+    if (sh) {
+        p.sh_world = sh->world;
+        p.sh_rank = sh->rank;
+        p.sh_row_offset = sh->row_offset;
+        p.sh_total = sh->total_rows;
+        for (int q = 0; q < sh->world; ++q) {
+            p.sh_out[q] = sh->out[q];
+            p.sh_flags[q] = sh->flags[q];
+        }
+        p.sh_state = sh->state;
+    }
     switch (M) {
         case 1: return launch_dp_g<FMT, 1>(p, ng, grid, smem, st);
         case 2: return launch_dp_g<FMT, 2>(p, ng, grid, smem, st);
@@ -654,13 +707,13 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
 
 // Launches the integer-dot-product kernel when the shape qualifies (*taken = true).
 int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
-                   int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken) {
+                   int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh) {
     *taken = false;
     if ((reinterpret_cast<uintptr_t>(W) & 15) != 0) return B200Q_OK;  // bulk copies need 16-byte aligned rows
     switch (fmt) {
-        case kQ4_K: return launch_dp_f<kQ4_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken);
-        case kQ6_K: return launch_dp_f<kQ6_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken);
-        case kQ8_0: return launch_dp_f<kQ8_0>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken);
+        case kQ4_K: return launch_dp_f<kQ4_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
+        case kQ6_K: return launch_dp_f<kQ6_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
+        case kQ8_0: return launch_dp_f<kQ8_0>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
     }
     return fail(B200Q_ERR_BAD_ARG, "gemv: unknown block format %d", fmt);
 }

@@ -30,6 +30,13 @@ struct StreamParams {
     int n_stages;        // ring depth
     // shared-memory offsets (bytes from the 128-byte aligned base)
     int off_xhi, off_xlo, off_sxhi, off_sxlo, off_red, off_stage;
+    // Row-sharded output (world > 0): instead of Y, every finished row goes to all ranks'
+    // result vectors through peer pointers, followed by an arrival flag per rank.
+    int sh_world, sh_rank;       // sh_world == 0: plain GEMV
+    int sh_row_offset, sh_total; // first global row of this shard; rows of the whole matrix
+    float* sh_out[kMaxShardRanks];         // rank q's result buffers: two vectors of sh_total floats, used alternately
+    unsigned int* sh_flags[kMaxShardRanks]; // rank q's arrival words, one per writing rank
+    unsigned int* sh_state;      // this rank: [0] CTAs finished in this launch, [1] completed launches (epoch)
 };
 
 template <int FMT>

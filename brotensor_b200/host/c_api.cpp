@@ -11,6 +11,7 @@
 #include "brotensor_b200/gguf.h"
 #include "brotensor_b200/ops/quant.h"
 #include "brotensor_b200/runtime.h"
+#include "brotensor_b200/sharded_head.h"
 
 using namespace brotensor_b200;
 
@@ -46,6 +47,9 @@ int b200h_init() {
     return cuda_device_count();
 }
 
+// The calling thread's stream for ops on device `dev` (a cudaStream_t; NULL = legacy default stream).
+void b200h_set_stream(void* stream, int dev) { cuda_set_stream(stream, dev); }
+
 // ---- weights -----------------------------------------------------------------------------
 // `device` < 0 keeps the tensor on the host. Returns an owning handle or NULL.
 void* b200h_weight_from_host(int fmt, const void* bytes, int rows, int cols, int device) {
@@ -57,6 +61,12 @@ void* b200h_weight_from_host(int fmt, const void* bytes, int rows, int cols, int
                                                      dtype_storage_bytes(dt, static_cast<std::int64_t>(rows) * cols)));
         }))
         return nullptr;
+    return t;
+}
+// Non-owning Tensor over quantized blocks already resident on `device` (freed by its owner).
+void* b200h_weight_view(int fmt, void* dev_bytes, int rows, int cols, int device) {
+    Tensor* t = nullptr;
+    if (guarded([&] { t = new Tensor(Tensor::view(Device::cuda(device), dev_bytes, rows, cols, fmt_dtype(fmt))); })) return nullptr;
     return t;
 }
 void b200h_tensor_free(void* t) { delete static_cast<Tensor*>(t); }
@@ -133,6 +143,48 @@ int b200h_session_run(void* sh, const void* x_host, void* y_host) {
     });
 }
 int b200h_session_y_dtype(void* sh) { return static_cast<int>(static_cast<Session*>(sh)->y.dtype); }
+
+// ---- row-sharded LM head -----------------------------------------------------------------------
+// create -> exchange the 64-byte handles between the ranks -> connect -> run ... -> free
+void* b200h_head_create(void* W_shard, int row_offset, int total_rows, int rank, int world, unsigned char* handle64) {
+    ShardedHead* h = nullptr;
+    if (guarded([&] {
+            h = new ShardedHead(*static_cast<Tensor*>(W_shard), row_offset, total_rows, rank, world);
+            const IpcHandle hd = h->local_handle();
+            std::memcpy(handle64, hd.data(), 64);
+        }))
+        return nullptr;
+    return h;
+}
+int b200h_head_connect(void* hh, const unsigned char* handles, int world) {
+    return guarded([&] {
+        std::vector<IpcHandle> v(world);
+        for (int q = 0; q < world; ++q) std::memcpy(v[q].data(), handles + 64 * q, 64);
+        static_cast<ShardedHead*>(hh)->connect(v);
+    });
+}
+// x_dev: device pointer to `in` values of x_dtype on the head's device (already resident: the
+// decode loop keeps activations on the device between layers).
+int b200h_head_run(void* hh, void* W_or_null, void* x_dev, int in, int x_dtype) {
+    return guarded([&] {
+        ShardedHead& h = *static_cast<ShardedHead*>(hh);
+        const Tensor x = Tensor::view(h.device(), x_dev, in, 1, static_cast<Dtype>(x_dtype));
+        if (W_or_null) h.forward_with(*static_cast<Tensor*>(W_or_null), x);
+        else h.forward(x);
+    });
+}
+// Waits for the head's device, then copies the latest full result vector to `dst` (total_rows floats).
+int b200h_head_logits_to_host(void* hh, float* dst) {
+    return guarded([&] {
+        ShardedHead& h = *static_cast<ShardedHead*>(hh);
+        sync(h.device());
+        const Tensor v = Tensor::view(h.device(), const_cast<float*>(h.logits()), h.total_rows(), 1, Dtype::FP32);
+        v.copy_to_host(dst);
+    });
+}
+const void* b200h_head_logits(void* hh) { return static_cast<ShardedHead*>(hh)->logits(); }
+unsigned long long b200h_head_calls(void* hh) { return static_cast<ShardedHead*>(hh)->calls(); }
+void b200h_head_free(void* hh) { delete static_cast<ShardedHead*>(hh); }
 
 // ---- GGUF ------------------------------------------------------------------------------------
 void* b200h_gguf_open(const char* path) {

@@ -26,6 +26,8 @@ def lib() -> C.CDLL:
         L.b200h_weight_from_host.restype = C.c_void_p
         L.b200h_weight_from_host.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int]
         L.b200h_tensor_free.argtypes = [C.c_void_p]
+        L.b200h_weight_view.restype = C.c_void_p
+        L.b200h_weight_view.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int]
         L.b200h_tensor_data.restype = C.c_void_p
         L.b200h_tensor_data.argtypes = [C.c_void_p]
         L.b200h_dequant.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
@@ -33,6 +35,18 @@ def lib() -> C.CDLL:
         L.b200h_session_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.b200h_session_free.argtypes = [C.c_void_p]
         L.b200h_session_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.b200h_head_create.restype = C.c_void_p
+        L.b200h_head_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.b200h_head_connect.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.b200h_head_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        L.b200h_head_logits.restype = C.c_void_p
+        L.b200h_head_logits.argtypes = [C.c_void_p]
+        L.b200h_head_calls.restype = C.c_ulonglong
+        L.b200h_head_calls.argtypes = [C.c_void_p]
+        L.b200h_head_free.argtypes = [C.c_void_p]
+        L.b200h_head_logits_to_host.argtypes = [C.c_void_p, C.c_void_p]
+        L.b200h_set_stream.argtypes = [C.c_void_p, C.c_int]
+        L.b200h_set_stream.restype = None
         _lib = L
     return _lib
 
@@ -48,12 +62,27 @@ def init() -> int:
     return n
 
 
+def set_stream(stream_ptr: int, device: int = -1) -> None:
+    """Makes `stream_ptr` (a cudaStream_t as an int, 0 = legacy default) the calling thread's stream."""
+    lib().b200h_set_stream(stream_ptr, device)
+
+
 class Weight:
     def __init__(self, fmt: int, blocks: np.ndarray, rows: int, cols: int, device: int = 0):
         blocks = np.ascontiguousarray(blocks, np.uint8)
         self.h = lib().b200h_weight_from_host(fmt, blocks.ctypes.data, rows, cols, device)
         _check(bool(self.h))
         self.fmt, self.rows, self.cols = fmt, rows, cols
+
+    @classmethod
+    def view(cls, fmt: int, dev_ptr: int, rows: int, cols: int, device: int = 0) -> "Weight":
+        """A Tensor of the host layer over quantized blocks that already live on the device
+        (the caller keeps them alive)."""
+        self = cls.__new__(cls)
+        self.h = lib().b200h_weight_view(fmt, dev_ptr, rows, cols, device)
+        _check(bool(self.h))
+        self.fmt, self.rows, self.cols = fmt, rows, cols
+        return self
 
     def dequant(self, out_dtype: int = 1) -> np.ndarray:
         out = np.empty((self.rows, self.cols), _NP[out_dtype])
@@ -84,3 +113,47 @@ class Session:
         if self.h:
             lib().b200h_session_free(self.h)
             self.h = None
+
+
+class ShardedHead:
+    """One rank of the row-sharded LM head (brotensor_b200::ShardedHead). `exchange` moves the
+    64-byte IPC handles between the ranks: a callable taking this rank's handle (bytes) and
+    returning all ranks' handles in rank order; None for a single rank."""
+
+    def __init__(self, weight: "Weight", row_offset: int, total_rows: int, rank: int, world: int, exchange=None):
+        hb = (C.c_ubyte * 64)()
+        self.h = lib().b200h_head_create(weight.h, row_offset, total_rows, rank, world, hb)
+        _check(bool(self.h))
+        self.weight, self.total_rows, self.rank, self.world = weight, total_rows, rank, world
+        if world > 1:
+            allh = exchange(bytes(hb))
+            assert len(allh) == world and all(len(x) == 64 for x in allh)
+            buf = (C.c_ubyte * (64 * world)).from_buffer_copy(b"".join(allh))
+            _check(lib().b200h_head_connect(self.h, buf, world) == 0)
+
+    def run(self, x_dev_ptr: int, in_features: int, x_dtype: int = 0, weight: "Weight | None" = None) -> None:
+        """Enqueues one forward; `weight` substitutes another tensor of the shard's shape."""
+        _check(lib().b200h_head_run(self.h, weight.h if weight is not None else None, x_dev_ptr, in_features, x_dtype) == 0)
+
+    def logits_ptr(self) -> int:
+        return int(lib().b200h_head_logits(self.h))
+
+    def calls(self) -> int:
+        return int(lib().b200h_head_calls(self.h))
+
+    def logits(self) -> np.ndarray:
+        """Synchronises the device and returns the latest full result vector."""
+        out = np.empty(self.total_rows, np.float32)
+        _check(lib().b200h_head_logits_to_host(self.h, out.ctypes.data) == 0)
+        return out
+
+    def close(self):
+        if self.h:
+            lib().b200h_head_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass

@@ -79,6 +79,31 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
                int M, int N, int K, void* stream);
 
 /*
+ * Row-sharded decode GEMV for one rank of a multi-GPU LM head (M = 1):
+ * this rank owns rows [row_offset, row_offset + rows) of a matrix of total_rows
+ * rows; W_shard is the byte range of those rows, x is replicated. The kernel
+ * writes every finished row straight into ALL ranks' result vectors through
+ * peer pointers (NVLink stores), then sets its arrival word at every rank and
+ * waits - at most one second - for all ranks' arrival words at its own, so when
+ * the kernel has completed, this rank holds the whole result vector. There is
+ * no separate collective.
+ *   peer_out[q]   rank q's result memory: TWO vectors of total_rows FP32, used
+ *                 alternately; after the n-th call on this state the result is
+ *                 vector (n & 1). Must be zero-initialised device memory
+ *                 mapped into this process (e.g. CUDA IPC).
+ *   peer_flags[q] rank q's arrival words, `world` x uint32, zero-initialised.
+ *   state         this rank's own two uint32 (CTA counter, call counter), zero-
+ *                 initialised; its second word is the call count n.
+ * All ranks must make the same sequence of calls. A rank that never arrives
+ * makes the others report B200Q_ERR_TIMEOUT through b200q_device_status().
+ * brotensor has no sharded form; the closest is its P2P bring-up
+ * (src/cuda/register.cu:90-103).
+ */
+int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
+                     int row_offset, int total_rows, int rank, int world, void* const* peer_out,
+                     void* const* peer_flags, void* state, void* stream);
+
+/*
  * Prefill GEMM on the tensor cores, any M >= 1:
  *   Y(M,N) = X(M,K) * decode(W(N,K))^T (+ bias(N)),   FP16 operands, FP32 accumulation.
  * `ws` is caller-owned scratch of at least b200q_gemm_workspace_bytes() bytes,

@@ -1,0 +1,65 @@
+// Row-sharded LM head over the GPUs of one node, one process per GPU.
+//
+// Each rank owns a contiguous row range of a quantized (out, in) matrix and a block of
+// "exchange memory": two result vectors of `out` floats plus one arrival word per rank.
+// The ranks exchange CUDA IPC handles of these blocks once (the caller moves the 64-byte
+// handles between processes with whatever it has: torch.distributed, MPI, a file), map each
+// other's blocks, and from then on a forward is ONE kernel per rank: the decode GEMV of the
+// shard whose epilogue stores every row into all ranks' result vectors over NVLink and
+// then signals / awaits arrival (b200q_gemv_shard). No collective library on the data path.
+//
+// brotensor has no sharded form of this op; it only brings up peer access
+// (src/cuda/register.cu:90-103).
+#pragma once
+
+#include <array>
+#include <cstdint>
+#include <vector>
+
+#include "brotensor_b200/tensor.h"
+
+namespace brotensor_b200 {
+
+using IpcHandle = std::array<unsigned char, 64>;
+
+class ShardedHead {
+public:
+    // W_shard: this rank's rows (row_offset .. row_offset + W_shard.rows) of a matrix with
+    // total_rows rows; lives on the CUDA device that is current for this rank.
+    ShardedHead(const Tensor& W_shard, int row_offset, int total_rows, int rank, int world);
+    ~ShardedHead();
+    ShardedHead(const ShardedHead&) = delete;
+    ShardedHead& operator=(const ShardedHead&) = delete;
+
+    // Handle of this rank's exchange memory, to be sent to every other rank.
+    IpcHandle local_handle() const { return handle_; }
+    // All ranks' handles, indexed by rank (the own entry is ignored). Call once, on every rank.
+    void connect(const std::vector<IpcHandle>& handles);
+
+    // x: (in, 1) activations on this device (FP32 / FP16 / BF16). Enqueues the kernel on the
+    // current stream. Every rank must call forward the same number of times.
+    void forward(const Tensor& x, const Tensor* bias_shard = nullptr);
+    // The same with another weight tensor of the shard's shape, dtype and device (e.g. the
+    // benchmark's rotation over weight replicas that keeps the L2 cold).
+    void forward_with(const Tensor& W_shard, const Tensor& x, const Tensor* bias_shard = nullptr);
+    // Device pointer to the full result vector of the most recent forward (total_rows floats),
+    // valid once that forward's kernel has completed on the stream.
+    const float* logits() const;
+    std::uint64_t calls() const { return calls_; }
+    int total_rows() const { return total_rows_; }
+    Device device() const { return W_->device; }
+
+private:
+    const Tensor* W_;
+    int row_offset_, total_rows_, rank_, world_;
+    void* local_ = nullptr;                  // exchange memory of this rank
+    std::vector<void*> peer_base_;           // mapped exchange memory of every rank (own = local_)
+    std::vector<void*> peer_out_, peer_flags_;
+    void* state_ = nullptr;
+    IpcHandle handle_{};
+    std::uint64_t calls_ = 0;
+    bool connected_ = false;
+    std::size_t out_bytes() const { return 2u * sizeof(float) * static_cast<std::size_t>(total_rows_); }
+};
+
+}  // namespace brotensor_b200
