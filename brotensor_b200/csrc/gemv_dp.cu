@@ -543,20 +543,25 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         // full result vector of this launch is complete in this rank's memory.
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
         if (tid == 0) {
-            __threadfence_system();  // this CTA's peer stores before its arrival
-            const unsigned int done = atomicAdd(&p.sh_state[0], 1u);
+            // Release chain with one system-scope fence on the critical path: each CTA's arrival
+            // is a gpu-scope release (its rows, seen through the barrier above, come before it);
+            // the last CTA acquires those, then one system-scope fence orders the whole grid's
+            // peer stores before the arrival words (release cumulativity).
+            unsigned int done;
+            asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
             if (done == gridDim.x - 1) {
+                asm volatile("fence.acq_rel.gpu;" ::: "memory");
                 p.sh_state[0] = 0;
                 const unsigned int epoch = sh_epoch + 1u;
-                __threadfence_system();
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
                 for (int q = 0; q < p.sh_world; ++q)
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[q] + p.sh_rank), "r"(epoch) : "memory");
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[q] + p.sh_rank), "r"(epoch) : "memory");
                 const uint64_t t0 = global_timer_ns();
                 bool ok = true;
                 for (int q = 0; q < p.sh_world && ok; ++q) {
                     for (;;) {
                         unsigned int v;
-                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
+                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
                         if ((int)(v - epoch) >= 0) break;
                         if (global_timer_ns() - t0 > 1000000000ull) {  // one second: a peer never arrived
                             if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
@@ -565,8 +570,10 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                         }
                     }
                 }
+                // acquire side for the peers' rows (they sit in this GPU's L2 already: a peer's rows
+                // are performed before its arrival word); needed only when there are peers
+                if (p.sh_world > 1) asm volatile("fence.acq_rel.sys;" ::: "memory");
                 *(volatile unsigned int*)&p.sh_state[1] = epoch;
-                __threadfence();
             }
         }
     }
