@@ -19,6 +19,8 @@ int launch_gemv_stream(int fmt, const void* W, const void* X, int x_dtype, const
 int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
                    int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh);
 void stream_set_option(int which, int value);
+void gemm_set_pair(int v);
+int gemm_get_pair();
 void dp_set_groups(int v);
 int dp_get_groups();
 int stream_get_option(int which);
@@ -285,6 +287,7 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "gemv_stage_kb")) stream_set_option(2, value);
     else if (!strcmp(key, "gemv_grid")) stream_set_option(3, value);
     else if (!strcmp(key, "gemv_groups")) dp_set_groups(value);
+    else if (!strcmp(key, "gemm_pair")) gemm_set_pair(value);
     else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
     return B200Q_OK;
 }
@@ -297,6 +300,7 @@ int b200q_get_option(const char* key, int* out) {
     else if (!strcmp(key, "gemv_stage_kb")) *out = stream_get_option(2);
     else if (!strcmp(key, "gemv_grid")) *out = stream_get_option(3);
     else if (!strcmp(key, "gemv_groups")) *out = dp_get_groups();
+    else if (!strcmp(key, "gemm_pair")) *out = gemm_get_pair();
     else return fail(B200Q_ERR_BAD_ARG, "get_option: unknown key '%s'", key);
     return B200Q_OK;
 }

@@ -1,0 +1,427 @@
+// Prefill GEMM on a CTA pair (thread-block cluster of two, tcgen05 cta_group::2):
+//   Y(M,N) = X(M,K) * decode(W(N,K))^T (+bias), FP16 operands, FP32 accumulation in TMEM.
+//
+// Why a pair. With one CTA per 128 weight rows the activation operand of 512 tokens is
+// re-streamed from L2 by every CTA at 64 KB per 64-k stage - at the MMA rate that is the
+// whole L2->SM bandwidth of an SM, and only two such stages fit in shared memory, so the
+// tensor pipe waits for operand data about half of the time. A pair of CTAs on two SMs runs
+// ONE MMA of 256 weight rows (128 per CTA, each from its own shared memory and into its own
+// TMEM) whose token operand is split between the two shared memories: each CTA fetches
+// only half of the tokens (32 KB per stage), the slab ring becomes four stages deep, and
+// every weight block is still decoded exactly once.
+//
+// Roles, identical in both CTAs unless noted:
+//   warp 0   loader: bulk async copies of this CTA's half of the activation slabs;
+//   warp 1   TMEM allocation; in the leader CTA (cluster rank 0) one thread of warp 1 and one
+//            of warp 3 issue the MMAs of alternate stages and commit them to the stage
+//            barriers of both CTAs;
+//   warp 2   relay: tells the leader when this CTA's slab has landed (a bulk copy can only
+//            signal a barrier of the CTA it writes to);
+//   warps 4..11  decode this CTA's 128 weight rows into the A-operand ring (two threads per
+//            row) and arrive on the LEADER's "A ready" barrier; afterwards the epilogue.
+// All waits are bounded; on a timeout the CTA records a status code, stops working, still
+// takes part in the cluster barriers, frees its TMEM and returns.
+//
+// Takes the place of brotensor's fused-dequant WMMA kernels (src/cuda/q4k_wmma.cu:56-310,
+// q6k_wmma.cu:62-356, q8_0_wmma.cu:54-288).
+#include <cstdlib>
+
+#include "gemm_common.cuh"
+
+namespace b200q {
+
+constexpr int kPairCtrlWarps = 4;
+constexpr int kPairProducerWarps = 8;
+constexpr int kPairThreads = 32 * (kPairCtrlWarps + kPairProducerWarps);
+constexpr int kPairMaxStages = 8;
+
+struct PairParams {
+    const uint8_t* W;
+    const uint8_t* Xp;   // prepared activations of this pass: [K/64][tok_stride][64] FP16, swizzled rows
+    const void* bias;
+    void* Y;
+    int* status;
+    int tokens, tok_pad, xp_tok_stride;
+    int N, K, row_bytes;
+    int bias_dtype, y_dtype;
+    int n_a, n_b;        // ring depths in k-blocks: decoded weights (16 KB slots) and slabs; n_b <= n_a
+    int g_bytes;         // bytes of one token group's half in a slab slot: (min(tok_pad, 256) / 2) * 128
+    int b_bytes;         // one slab slot of this CTA: g_bytes * groups
+    int debug;
+};
+
+// ---- cluster / cta_group::2 wrappers ----------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of `saddr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on the barrier at shared::cluster address `bar` once all MMAs issued so far have retired
+__device__ __forceinline__ void umma2_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// kind::f16 instruction descriptor of the pair MMA: D = F32, A = B = F16, K-major, M = 256, N = n
+__device__ __forceinline__ uint32_t instr_desc_pair(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+// Pair P of a Q4_K block held in registers: low nibbles are sub-block 2P (k 0..31 of the
+// stage), high nibbles sub-block 2P+1 (k 32..63). Thread half H = 0 writes the low-nibble
+// sub-block (16-byte chunks 0..3 of the row), H = 1 the high-nibble one (chunks 4..7).
+template <int P>
+__device__ __forceinline__ void q4k_half_to_smem(const uint4 (&blk)[9], uint32_t rowaddr, uint32_t r7, int H) {
+    const uint4 h = blk[0];
+    uint32_t sc, m;
+    if constexpr (P < 2) {
+        sc = (h.y >> (16 * P + 8 * H)) & 63u;
+        m = (h.z >> (16 * P + 8 * H)) & 63u;
+    } else {
+        const int J = 2 * (P - 2) + H;
+        sc = ((h.w >> (8 * J)) & 0xFu) | (((h.y >> (8 * J + 6)) & 3u) << 4);
+        m = ((h.w >> (8 * J + 4)) & 0xFu) | (((h.z >> (8 * J + 6)) & 3u) << 4);
+    }
+    const float ds = h2f(h.x & 0xFFFFu) * (float)sc, dm = h2f(h.x >> 16) * (float)m;
+    const uint4 qa = blk[1 + 2 * P], qb = blk[2 + 2 * P];
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const uint32_t sh = 4u * (uint32_t)H;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint4 o;
+        nib4_to_h2((w[2 * c] >> sh) & 0x0F0F0F0Fu, ds, dm, o.x, o.y);
+        nib4_to_h2((w[2 * c + 1] >> sh) & 0x0F0F0F0Fu, ds, dm, o.z, o.w);
+        sts128(rowaddr + (((uint32_t)(c + 4 * H) ^ r7) << 4), o);
+    }
+}
+// Any format straight from global memory: four chunks of eight weights through the exact scalar decode.
+template <int FMT>
+__device__ __forceinline__ void generic_half_to_smem(const uint8_t* row, int kb, int H, uint32_t rowaddr, uint32_t r7) {
+#pragma unroll 2
+    for (int c = 4 * H; c < 4 * H + 4; ++c) {
+        float w[8];
+        decode8<FMT>(row, kb * 8 + c, w);
+        uint4 o;
+        o.x = pack_h2(w[0], w[1]); o.y = pack_h2(w[2], w[3]); o.z = pack_h2(w[4], w[5]); o.w = pack_h2(w[6], w[7]);
+        sts128(rowaddr + (((uint32_t)c ^ r7) << 4), o);
+    }
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+template <int FMT>
+__global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;  // operand tiles need 1024-byte alignment
+    __shared__ uint64_t bar_ready[kPairMaxStages];    // leader: the k-block's operands are complete: both CTAs' producer
+                                                      // warps have written their A slot and both slab halves have landed
+    __shared__ uint64_t bar_a_empty[kPairMaxStages];  // the pair's MMAs on the k-block retired (commit from the leader)
+    __shared__ uint64_t bar_b_full[kPairMaxStages];   // this CTA's half of the slab landed (tx)
+    __shared__ uint64_t bar_turn[2];                  // leader: issuer q may queue its next stage (strict alternation)
+    __shared__ uint64_t bar_accum;                    // all MMAs retired
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t crank = cluster_ctarank();         // 0 = leader
+    const int row0 = blockIdx.x * kGemmRows;          // the pair's CTAs own consecutive row tiles
+    const int n_kb = p.K / kBK;
+    const uint32_t tmem_cols = p.tok_pad <= 32 ? 32u : p.tok_pad <= 64 ? 64u : p.tok_pad <= 128 ? 128u : p.tok_pad <= 256 ? 256u : 512u;
+    // token groups of up to 256: group g is one MMA of N = ng tokens into accumulator columns 256 g ..;
+    // this CTA holds tokens [256 g + crank * ng / 2, + ng / 2) of it
+    const int n0 = min(p.tok_pad, 256), n1 = p.tok_pad - n0;
+    const int groups = n1 > 0 ? 2 : 1;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.n_a; ++s) {
+            mbar_init(smem_u32(&bar_ready[s]), 2 * kPairProducerWarps + 2);
+            mbar_init(smem_u32(&bar_a_empty[s]), 1);
+        }
+        for (int s = 0; s < p.n_b; ++s) mbar_init(smem_u32(&bar_b_full[s]), 1);
+        mbar_init(smem_u32(&bar_turn[0]), 1);
+        mbar_init(smem_u32(&bar_turn[1]), 1);
+        mbar_init(smem_u32(&bar_accum), 2);
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc2(smem_u32(&tmem_base_slot), tmem_cols);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    const uint32_t b_base = sbase + (uint32_t)(p.n_a * kGemmRows * 128);  // A ring first, then the slab ring
+
+    if (warp == 0) {
+        // ---- loader. The slab slot of k-block kb is free once the MMAs of k-block kb - n_b have
+        // retired, which is what that k-block's A-slot barrier says (n_b <= n_a).
+        if (lane == 0) {
+            int bs = 0, sa = 0;
+            uint32_t pa = 0;
+            for (int kb = 0; kb < n_kb; ++kb) {
+                if (kb >= p.n_b) {
+                    if (!wait_or_abort<true>(smem_u32(&bar_a_empty[sa]), pa, &abort_flag, p.status, kDevTimeoutEmpty)) break;
+                    if (++sa == p.n_a) { sa = 0; pa ^= 1; }
+                }
+                const uint32_t full = smem_u32(&bar_b_full[bs]);
+                const uint32_t h0 = (uint32_t)(n0 / 2) * 128u, h1 = (uint32_t)(n1 / 2) * 128u;
+                if (p.debug & 4) { mbar_arrive(full); if (++bs == p.n_b) bs = 0; continue; }
+                mbar_arrive_expect_tx(full, h0 + h1);
+                const uint8_t* src = p.Xp + (size_t)kb * p.xp_tok_stride * 128u;
+                const uint32_t dst = b_base + bs * p.b_bytes;
+                bulk_g2s(dst, src + (size_t)crank * h0, h0, full);
+                if (groups == 2) bulk_g2s(dst + p.g_bytes, src + 256u * 128u + (size_t)crank * h1, h1, full);
+                if (++bs == p.n_b) bs = 0;
+            }
+        }
+    } else if (warp == 2) {
+        // ---- relay: this CTA's half has landed -> one arrival on the leader's "ready" barrier of the k-block
+        if (lane == 0) {
+            int bs = 0, sa = 0;
+            uint32_t pb = 0;
+            for (int kb = 0; kb < n_kb; ++kb) {
+                if (!wait_or_abort<true>(smem_u32(&bar_b_full[bs]), pb, &abort_flag, p.status, kDevTimeoutFull)) break;
+                mbar_arrive_remote(map_to_rank(smem_u32(&bar_ready[sa]), 0));
+                if (++bs == p.n_b) { bs = 0; pb ^= 1; }
+                if (++sa == p.n_a) sa = 0;
+            }
+        }
+    } else if (warp == 1 || warp == 3) {
+        // ---- MMA issuers (leader CTA only). One thread cannot keep the tensor pipe fed: issuing
+        // blocks while the pipe's short queue is full, and the wait / fence / commits between two
+        // stages would then leave it idle. Two threads in different warps take alternate stages:
+        // while one is blocked behind its own MMAs, the other has done the next stage's wait and
+        // queues up right behind it. A turn barrier keeps the queueing order kb = 0, 1, 2, ...
+        // so the accumulation order, and with it the result, is the same on every run.
+        if (lane == 0 && crank == 0) {
+            const int q = warp == 1 ? 0 : 1;
+            int sa = q % p.n_a, bs = q % p.n_b;
+            uint32_t pa = (uint32_t)(q / p.n_a) & 1u, pt = 0;
+            const uint32_t idesc0 = instr_desc_pair(n0), idesc1 = instr_desc_pair(n1 > 0 ? n1 : 16);
+            for (int kb = q; kb < n_kb; kb += 2) {
+                if (!wait_or_abort<true>(smem_u32(&bar_ready[sa]), pa, &abort_flag, p.status, kDevTimeoutFull)) break;
+                if (kb > 0) {  // my turn: the other issuer has queued stage kb - 1
+                    if (!wait_or_abort<true>(smem_u32(&bar_turn[q]), pt, &abort_flag, p.status, kDevTimeoutFull)) break;
+                    pt ^= 1;
+                }
+                tc_fence_after();
+                const uint32_t a_s = sbase + sa * (kGemmRows * 128), b_s = b_base + bs * p.b_bytes;
+#pragma unroll
+                for (int k = 0; k < kBK / 16 && !(p.debug & 1); ++k) {
+                    const uint64_t adesc = smem_desc_sw128(a_s + k * 32);
+                    umma2_f16(tmem_base, adesc, smem_desc_sw128(b_s + k * 32), idesc0, (kb | k) != 0);
+                    if (groups == 2) umma2_f16(tmem_base + 256, adesc, smem_desc_sw128(b_s + p.g_bytes + k * 32), idesc1, (kb | k) != 0);
+                }
+                mbar_arrive(smem_u32(&bar_turn[q ^ 1]));
+                // the k-block's A slots (and, n_b k-blocks on, its slabs) are free in both CTAs once these have retired
+                umma2_commit(smem_u32(&bar_a_empty[sa]));
+                umma2_commit(map_to_rank(smem_u32(&bar_a_empty[sa]), 1));
+                sa += 2;
+                if (sa >= p.n_a) { sa -= p.n_a; pa ^= 1; }
+                bs += 2;
+                if (bs >= p.n_b) bs -= p.n_b;
+            }
+            umma2_commit(smem_u32(&bar_accum));
+            umma2_commit(map_to_rank(smem_u32(&bar_accum), 1));
+        }
+    } else if (warp >= kPairCtrlWarps) {
+        // ---- A producers (two threads per weight row: k 0..31 and k 32..63 of the stage), then the epilogue
+        const int H = (warp - kPairCtrlWarps) >> 2;
+        const int pt = (warp & 3) * 32 + lane;                   // tile row = TMEM lane of this thread
+        const int wrow = min(row0 + pt, p.N - 1);                // rows past N decode row N-1, never stored
+        const uint8_t* rowp = p.W + (size_t)wrow * p.row_bytes;
+        const uint32_t r7 = (uint32_t)(pt & 7);
+        const uint32_t row_off = (uint32_t)((pt >> 3) * 1024 + (pt & 7) * 128);
+        const int n_blk = p.K / 256;
+        int slot = 0;
+        uint32_t phase = 0;
+        bool live = true;
+        // The row's Q4_K block for the next four stages is loaded into registers one block ahead
+        // of its use, so its latency (an L2 or DRAM round trip) hides behind four stages of decode.
+        uint4 cur[9], nxt[9];
+#pragma unroll
+        for (int i = 0; i < 9; ++i) cur[i] = nxt[i] = make_uint4(0, 0, 0, 0);
+        if constexpr (FMT == kQ4_K) {
+#pragma unroll
+            for (int i = 0; i < 9; ++i) nxt[i] = __ldg(reinterpret_cast<const uint4*>(rowp) + i);
+        }
+        for (int kb = 0; kb < n_kb; ++kb) {
+            if constexpr (FMT == kQ4_K) {
+                if ((kb & 3) == 0) {
+                    const int b = kb >> 2;
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
+                    if (b + 1 < n_blk) {
+#pragma unroll
+                        for (int i = 0; i < 9; ++i) nxt[i] = __ldg(reinterpret_cast<const uint4*>(rowp + (size_t)(b + 1) * 144) + i);
+                    }
+                }
+            }
+            if (live) {
+                const bool ok = gemm_wait(smem_u32(&bar_a_empty[slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty);
+                live = __all_sync(0xffffffffu, ok);
+            }
+            if (live) {
+                const uint32_t rowaddr = sbase + slot * (kGemmRows * 128) + row_off;
+                if (p.debug & 2) {
+                } else if constexpr (FMT == kQ4_K) {
+                    switch (kb & 3) {
+                        case 0: q4k_half_to_smem<0>(cur, rowaddr, r7, H); break;
+                        case 1: q4k_half_to_smem<1>(cur, rowaddr, r7, H); break;
+                        case 2: q4k_half_to_smem<2>(cur, rowaddr, r7, H); break;
+                        default: q4k_half_to_smem<3>(cur, rowaddr, r7, H); break;
+                    }
+                } else {
+                    generic_half_to_smem<FMT>(rowp, kb, H, rowaddr, r7);
+                }
+                if (!(p.debug & 8)) fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor cores of the pair
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&bar_ready[slot]), 0));
+            if (++slot == p.n_a) { slot = 0; phase ^= 1; }
+        }
+        // ---- epilogue: this CTA's accumulator rows are its own 128 weight rows; a warp may only
+        // touch TMEM lanes 32*(warp%4)..+31, and the two warps sharing a lane quarter split the tokens
+        if (live) {
+            const bool ok = gemm_wait(smem_u32(&bar_accum), 0, &abort_flag, p.status, kDevTimeoutMma);
+            live = __all_sync(0xffffffffu, ok);
+        }
+        if (live) {
+            tc_fence_after();
+            const int n = row0 + pt;
+            float bv = 0.f;
+            if (p.bias && n < p.N) {
+                if (p.bias_dtype == B200Q_DT_F32) bv = static_cast<const float*>(p.bias)[n];
+                else if (p.bias_dtype == B200Q_DT_F16) bv = __half2float(static_cast<const __half*>(p.bias)[n]);
+                else bv = __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+            }
+            const uint32_t tlane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            const int share = ((p.tok_pad / 16 + 1) / 2) * 16;
+            const int cbeg = H * share, cend = min(cbeg + share, p.tok_pad);
+            for (int c0 = cbeg; c0 < cend; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(tlane + (uint32_t)c0, r);
+                tmem_ld_wait();
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = c0 + j;
+                        if (t < p.tokens) {
+                            const float v = __uint_as_float(r[j]) + bv;
+                            const size_t o = (size_t)t * p.N + n;
+                            if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = v;
+                            else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(v);
+                            else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // Nobody leaves (or frees TMEM) while the other CTA may still read this one's shared memory,
+    // arrive on its barriers or have MMAs of the pair in flight.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc2(tmem_base, tmem_cols);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+template <int FMT>
+static int launch_pair_fmt(const PairParams& p, size_t smem, cudaStream_t st) {
+    auto kern = gemm_tc2_kernel<FMT>;
+    static bool configured[64] = {};
+    int dev = 0;
+    B200Q_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    const unsigned tiles = (unsigned)((p.N + kGemmRows - 1) / kGemmRows);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((tiles + 1u) & ~1u);  // whole pairs; a CTA past the last row tile decodes row N-1 and stores nothing
+    cfg.blockDim = dim3(kPairThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+    return B200Q_OK;
+}
+
+// One pass (<= 512 tokens) of the prefill GEMM on CTA pairs. The caller has run the activation
+// pre-pass; Xp points at this pass's first token row inside the workspace.
+int launch_gemm_pair_pass(int fmt, const void* W, const uint8_t* Xp, int tok_stride, const void* bias, int bias_dtype,
+                          void* Y, int y_dtype, int tokens, int N, int K, int* status, cudaStream_t st) {
+    PairParams p = {};
+    p.W = static_cast<const uint8_t*>(W);
+    p.Xp = Xp;
+    p.bias = bias;
+    p.Y = Y;
+    p.status = status;
+    p.tokens = tokens;
+    p.tok_pad = (tokens + 15) & ~15;
+    p.xp_tok_stride = tok_stride;
+    p.N = N;
+    p.K = K;
+    p.row_bytes = (K / b200q_block_elems(fmt)) * b200q_block_bytes(fmt);
+    p.bias_dtype = bias_dtype;
+    p.y_dtype = y_dtype;
+    { const char* e = getenv("B200Q_GEMM_DEBUG"); p.debug = e ? atoi(e) : 0; }
+    const int n0 = p.tok_pad < 256 ? p.tok_pad : 256;
+    const int groups = p.tok_pad > 256 ? 2 : 1;
+    p.g_bytes = (n0 / 2) * 128;
+    p.b_bytes = p.g_bytes * groups;
+    // Ring depths: slabs four k-blocks ahead (they come from L2 with about a microsecond of
+    // latency), decoded weights in the rest so the producers can hide their block loads.
+    const unsigned budget = 227u * 1024u - 2048u;
+    const unsigned kb_a = kGemmRows * 128;
+    p.n_b = 4;
+    p.n_a = (int)((budget - (unsigned)p.n_b * (unsigned)p.b_bytes) / kb_a);
+    if (p.n_a > kPairMaxStages) p.n_a = kPairMaxStages;
+    if (p.n_a < p.n_b) return fail(B200Q_ERR_UNSUPPORTED, "gemm: pair rings do not fit (%d weight slots, %d slab stages)", p.n_a, p.n_b);
+    const size_t smem = (size_t)p.n_a * kb_a + (size_t)p.n_b * p.b_bytes + 1024;
+    if (fmt == kQ4_K) return launch_pair_fmt<kQ4_K>(p, smem, st);
+    if (fmt == kQ6_K) return launch_pair_fmt<kQ6_K>(p, smem, st);
+    return launch_pair_fmt<kQ8_0>(p, smem, st);
+}
+
+}  // namespace b200q

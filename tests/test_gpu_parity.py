@@ -333,3 +333,30 @@ def test_bad_arguments_raise():
     with pytest.raises(ValueError):
         ops.gemv(oracle.Q4_K, W, x[:1, :128].contiguous(), 4)  # K not a block multiple
     assert ops.gemv(oracle.Q4_K, W[:0], x[:1], 0).shape == (1, 0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,N,K,M", [(synth.Q4_K, 256, 256, 16), (synth.Q4_K, 384, 512, 48), (synth.Q4_K, 1024, 1024, 272),
+                                       (synth.Q4_K, 1000, 768, 700), (synth.Q6_K, 256, 512, 33), (synth.Q8_0, 384, 512, 130),
+                                       (synth.Q4_K, 2048, 2048, 512)])
+def test_gemm_cta_pair_equals_single_cta(fmt, N, K, M, cpu_oracle):
+    """The CTA-pair kernel (cta_group::2, two alternating issuers) queues its MMAs in the same
+    k order as the one-CTA kernel, so the two agree bit for bit; both agree with the oracle."""
+    import torch
+    import oracle
+    Wh = synth.make_blocks(fmt, N, K, seed=N + M)
+    xh = synth.make_activations(M, K, seed=M)
+    W, X = torch.from_numpy(Wh).cuda(), torch.from_numpy(xh).cuda()
+    try:
+        ops.set_option("gemm_pair", 0)
+        y0 = ops.gemm(fmt, W, X, N)
+        ops.set_option("gemm_pair", 1)
+        y1 = ops.gemm(fmt, W, X, N)
+        y2 = ops.gemm(fmt, W, X, N)
+    finally:
+        ops.set_option("gemm_pair", -1)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)  # same on every run
+    assert torch.equal(y0, y1)
+    assert oracle.rel_l2(y1.cpu().numpy(), cpu_oracle.matmul(fmt, Wh, xh, threads=8)) < 2e-3
+    assert ops.device_status() == 0
