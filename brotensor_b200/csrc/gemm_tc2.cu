@@ -24,8 +24,6 @@
 //
 // Takes the place of brotensor's fused-dequant WMMA kernels (src/cuda/q4k_wmma.cu:56-310,
 // q6k_wmma.cu:62-356, q8_0_wmma.cu:54-288).
-#include <cstdlib>
-
 #include "gemm_common.cuh"
 
 namespace b200q {
@@ -47,7 +45,6 @@ struct PairParams {
     int n_a, n_b;        // ring depths in k-blocks: decoded weights (16 KB slots) and slabs; n_b <= n_a
     int g_bytes;         // bytes of one token group's half in a slab slot: (min(tok_pad, 256) / 2) * 128
     int b_bytes;         // one slab slot of this CTA: g_bytes * groups
-    int debug;
 };
 
 // ---- cluster / cta_group::2 wrappers ----------------------------------------------------------
@@ -65,6 +62,10 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival on a barrier of another CTA of the cluster. Default (CTA-scope release) semantics on
+// purpose: what has to be ordered before it is this CTA's own shared-memory image, which the
+// proxy fence has already made visible to the tensor cores; a cluster-scope release here is a
+// full memory barrier per producer warp and stage and cost a third of the kernel's time.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
@@ -194,7 +195,6 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                 }
                 const uint32_t full = smem_u32(&bar_b_full[bs]);
                 const uint32_t h0 = (uint32_t)(n0 / 2) * 128u, h1 = (uint32_t)(n1 / 2) * 128u;
-                if (p.debug & 4) { mbar_arrive(full); if (++bs == p.n_b) bs = 0; continue; }
                 mbar_arrive_expect_tx(full, h0 + h1);
                 const uint8_t* src = p.Xp + (size_t)kb * p.xp_tok_stride * 128u;
                 const uint32_t dst = b_base + bs * p.b_bytes;
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                 tc_fence_after();
                 const uint32_t a_s = sbase + sa * (kGemmRows * 128), b_s = b_base + bs * p.b_bytes;
 #pragma unroll
-                for (int k = 0; k < kBK / 16 && !(p.debug & 1); ++k) {
+                for (int k = 0; k < kBK / 16; ++k) {
                     const uint64_t adesc = smem_desc_sw128(a_s + k * 32);
                     umma2_f16(tmem_base, adesc, smem_desc_sw128(b_s + k * 32), idesc0, (kb | k) != 0);
                     if (groups == 2) umma2_f16(tmem_base + 256, adesc, smem_desc_sw128(b_s + p.g_bytes + k * 32), idesc1, (kb | k) != 0);
@@ -292,8 +292,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
             }
             if (live) {
                 const uint32_t rowaddr = sbase + slot * (kGemmRows * 128) + row_off;
-                if (p.debug & 2) {
-                } else if constexpr (FMT == kQ4_K) {
+                if constexpr (FMT == kQ4_K) {
                     switch (kb & 3) {
                         case 0: q4k_half_to_smem<0>(cur, rowaddr, r7, H); break;
                         case 1: q4k_half_to_smem<1>(cur, rowaddr, r7, H); break;
@@ -303,7 +302,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                 } else {
                     generic_half_to_smem<FMT>(rowp, kb, H, rowaddr, r7);
                 }
-                if (!(p.debug & 8)) fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor cores of the pair
+                fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor cores of the pair
             }
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(map_to_rank(smem_u32(&bar_ready[slot]), 0));
@@ -405,7 +404,6 @@ int launch_gemm_pair_pass(int fmt, const void* W, const uint8_t* Xp, int tok_str
     p.row_bytes = (K / b200q_block_elems(fmt)) * b200q_block_bytes(fmt);
     p.bias_dtype = bias_dtype;
     p.y_dtype = y_dtype;
-    { const char* e = getenv("B200Q_GEMM_DEBUG"); p.debug = e ? atoi(e) : 0; }
     const int n0 = p.tok_pad < 256 ? p.tok_pad : 256;
     const int groups = p.tok_pad > 256 ? 2 : 1;
     p.g_bytes = (n0 / 2) * 128;
