@@ -8,6 +8,7 @@
 #include <string>
 #include <vector>
 
+#include "brotensor_b200/cuda_graph.h"
 #include "brotensor_b200/gguf.h"
 #include "brotensor_b200/ops/quant.h"
 #include "brotensor_b200/runtime.h"
@@ -141,6 +142,115 @@ int b200h_session_run(void* sh, const void* x_host, void* y_host) {
         }
         s.y.copy_raw_to_host(y_host);
     });
+}
+// The same step without blocking: x_pinned and y_pinned are page-locked host buffers; the copy
+// in, the op and the copy out are enqueued on the calling thread's stream. b200h_sync() makes
+// y_pinned valid. Several sessions may be enqueued before one sync.
+int b200h_session_enqueue(void* sh, const void* x_pinned, void* y_pinned) {
+    return guarded([&] {
+        Session& s = *static_cast<Session*>(sh);
+        const Tensor& W = *s.W;
+        s.x.copy_raw_from_host_async(x_pinned);
+        const Tensor* b = s.has_bias ? &s.bias : nullptr;
+        const bool gemv = s.M == 1;
+        switch (W.dtype) {
+            case Dtype::Q4_K: gemv ? linear_forward_q4k_fp16(W, b, s.x, s.y) : linear_forward_batched_q4k_fp16(W, b, s.x, s.y); break;
+            case Dtype::Q6_K: gemv ? linear_forward_q6k_fp16(W, b, s.x, s.y) : linear_forward_batched_q6k_fp16(W, b, s.x, s.y); break;
+            case Dtype::Q8_0: gemv ? linear_forward_q8_0_fp16(W, b, s.x, s.y) : linear_forward_batched_q8_0_fp16(W, b, s.x, s.y); break;
+            default: throw std::runtime_error("b200h_session_enqueue: weight is not Q4_K / Q6_K / Q8_0");
+        }
+        s.y.copy_raw_to_host_async(y_pinned);
+    });
+}
+// ---- a set of GEMV layers whose activations and results live in one device arena each, so a
+// step's host round trip is ONE copy in and ONE copy out around the ops (what a decode loop
+// does: a layer's activations sit in one buffer). x/y of op i are views into the arenas.
+struct LayerSet {
+    std::vector<const Tensor*> W;
+    Tensor X_all, Y_all;
+    std::vector<Tensor> x, y;
+    std::vector<unsigned long long> x_off, y_off;
+    unsigned long long x_bytes = 0, y_bytes = 0;
+};
+void* b200h_layer_create(void* const* weights, int n, int x_dtype, int y_dtype) {
+    LayerSet* L = nullptr;
+    if (guarded([&] {
+            auto up = std::make_unique<LayerSet>();
+            const Dtype xd = static_cast<Dtype>(x_dtype), yd = static_cast<Dtype>(y_dtype);
+            if (n <= 0) throw std::runtime_error("b200h_layer_create: no layers");
+            const Device dev = static_cast<const Tensor*>(weights[0])->device;
+            auto pad = [](unsigned long long v) { return (v + 255ull) & ~255ull; };
+            for (int i = 0; i < n; ++i) {
+                const Tensor* W = static_cast<const Tensor*>(weights[i]);
+                if (W->device != dev) throw std::runtime_error("b200h_layer_create: weights on different devices");
+                up->W.push_back(W);
+                up->x_off.push_back(up->x_bytes);
+                up->y_off.push_back(up->y_bytes);
+                up->x_bytes += pad(dtype_storage_bytes(xd, W->cols));
+                up->y_bytes += pad(dtype_storage_bytes(yd, W->rows));
+            }
+            up->X_all = Tensor::zeros_on(dev, static_cast<int>(up->x_bytes / 4), 1, Dtype::FP32);
+            up->Y_all = Tensor::zeros_on(dev, static_cast<int>(up->y_bytes / 4), 1, Dtype::FP32);
+            for (int i = 0; i < n; ++i) {
+                up->x.push_back(Tensor::view(dev, static_cast<char*>(up->X_all.data) + up->x_off[i], up->W[i]->cols, 1, xd));
+                up->y.push_back(Tensor::view(dev, static_cast<char*>(up->Y_all.data) + up->y_off[i], up->W[i]->rows, 1, yd));
+            }
+            L = up.release();
+        }))
+        return nullptr;
+    return L;
+}
+void b200h_layer_free(void* h) { delete static_cast<LayerSet*>(h); }
+// Byte offsets of every op's x and y inside the arenas (the host arenas use the same layout).
+int b200h_layer_layout(void* h, unsigned long long* x_off, unsigned long long* y_off, unsigned long long* x_bytes,
+                       unsigned long long* y_bytes) {
+    LayerSet& L = *static_cast<LayerSet*>(h);
+    for (std::size_t i = 0; i < L.W.size(); ++i) {
+        x_off[i] = L.x_off[i];
+        y_off[i] = L.y_off[i];
+    }
+    *x_bytes = L.x_bytes;
+    *y_bytes = L.y_bytes;
+    return 0;
+}
+// One copy in (page-locked x arena), the n GEMVs through the public ops, one copy out.
+int b200h_layer_enqueue(void* h, const void* x_pinned_arena, void* y_pinned_arena) {
+    return guarded([&] {
+        LayerSet& L = *static_cast<LayerSet*>(h);
+        L.X_all.copy_raw_from_host_async(x_pinned_arena);
+        for (std::size_t i = 0; i < L.W.size(); ++i) {
+            const Tensor& W = *L.W[i];
+            switch (W.dtype) {
+                case Dtype::Q4_K: linear_forward_q4k_fp16(W, nullptr, L.x[i], L.y[i]); break;
+                case Dtype::Q6_K: linear_forward_q6k_fp16(W, nullptr, L.x[i], L.y[i]); break;
+                case Dtype::Q8_0: linear_forward_q8_0_fp16(W, nullptr, L.x[i], L.y[i]); break;
+                default: throw std::runtime_error("b200h_layer_enqueue: weight is not Q4_K / Q6_K / Q8_0");
+            }
+        }
+        L.Y_all.copy_raw_to_host_async(y_pinned_arena);
+    });
+}
+
+// ---- graph capture of a sequence of the calls above (CudaGraphCapture / CudaGraph) -------------
+void* b200h_capture_begin() {
+    CudaGraphCapture* c = nullptr;
+    if (guarded([&] { c = new CudaGraphCapture(); })) return nullptr;
+    return c;
+}
+// Ends the capture (consumes the capture handle) and returns a graph handle, or NULL.
+void* b200h_capture_finish(void* ch) {
+    std::unique_ptr<CudaGraphCapture> c(static_cast<CudaGraphCapture*>(ch));
+    CudaGraph* g = nullptr;
+    if (guarded([&] { g = new CudaGraph(c->finish()); })) return nullptr;
+    return g;
+}
+int b200h_graph_launch(void* gh) {
+    return guarded([&] { static_cast<CudaGraph*>(gh)->launch(); });
+}
+void b200h_graph_free(void* gh) { delete static_cast<CudaGraph*>(gh); }
+
+int b200h_sync(int device) {
+    return guarded([&] { sync(device < 0 ? Device::CPU : Device::cuda(device)); });
 }
 int b200h_session_y_dtype(void* sh) { return static_cast<int>(static_cast<Session*>(sh)->y.dtype); }
 

@@ -65,6 +65,14 @@ void c_d2h(void* d, const void* s, std::size_t n, int dev) {
     B200_CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToHost, cur_stream(dev)));
     B200_CUDA_CHECK(cudaStreamSynchronize(cur_stream(dev)));
 }
+void c_h2d_async(void* d, const void* s, std::size_t n, int dev) {
+    DeviceGuard g(dev);
+    B200_CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyHostToDevice, cur_stream(dev)));
+}
+void c_d2h_async(void* d, const void* s, std::size_t n, int dev) {
+    DeviceGuard g(dev);
+    B200_CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToHost, cur_stream(dev)));
+}
 void c_d2d(void* d, const void* s, std::size_t n, int dev) {
     DeviceGuard g(dev);
     B200_CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToDevice, cur_stream(dev)));
@@ -217,7 +225,7 @@ void fill_cuda_tables(OpsVTable& ops, AllocVTable& alloc) {
     ops.linear_forward_q6k_fp16 = gemv_q6k;
     ops.linear_forward_batched_q6k_fp16 = batched_q6k;
     alloc.alloc = c_alloc; alloc.free = c_free;
-    alloc.memcpy_h2d = c_h2d; alloc.memcpy_d2h = c_d2h; alloc.memcpy_d2d = c_d2d; alloc.memcpy_peer = c_peer;
+    alloc.memcpy_h2d = c_h2d; alloc.memcpy_d2h = c_d2h; alloc.memcpy_h2d_async = c_h2d_async; alloc.memcpy_d2h_async = c_d2h_async; alloc.memcpy_d2d = c_d2d; alloc.memcpy_peer = c_peer;
     alloc.memset_zero = c_zero; alloc.sync = c_sync; alloc.mem_info = c_mem_info; alloc.device_name = c_name;
 }
 

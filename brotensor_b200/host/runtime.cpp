@@ -37,6 +37,7 @@ struct CpuRegistrar {
         detail::AllocVTable a{};
         a.alloc = cpu_alloc; a.free = cpu_free;
         a.memcpy_h2d = cpu_copy; a.memcpy_d2h = cpu_copy; a.memcpy_d2d = cpu_copy;
+        a.memcpy_h2d_async = cpu_copy; a.memcpy_d2h_async = cpu_copy;
         a.memcpy_peer = cpu_peer; a.memset_zero = cpu_zero; a.sync = cpu_sync;
         detail::register_backend(DeviceType::CPU, ops, a);
     }

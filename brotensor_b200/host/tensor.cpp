@@ -195,6 +195,24 @@ void Tensor::copy_raw_to_host(void* dst) const {
     if (device.is_cpu()) std::memcpy(dst, data, n);
     else detail::alloc_for(device).memcpy_d2h(dst, data, n, device.index);
 }
+// Stream-ordered forms for page-locked host memory (an extension over brotensor's Tensor,
+// whose host round trips are blocking): enqueue on the calling thread's current stream and
+// return; the data is valid after sync(device).
+void Tensor::copy_raw_from_host_async(const void* src) {
+    const std::size_t n = bytes();
+    if (!n) return;
+    if (!data) fail("copy_from_host_async: tensor has no storage");
+    if (!src) fail("copy_from_host_async: null source");
+    if (device.is_cpu()) std::memcpy(data, src, n);
+    else detail::alloc_for(device).memcpy_h2d_async(data, src, n, device.index);
+}
+void Tensor::copy_raw_to_host_async(void* dst) const {
+    const std::size_t n = bytes();
+    if (!n) return;
+    if (!data) fail("copy_to_host_async: tensor has no storage");
+    if (device.is_cpu()) std::memcpy(dst, data, n);
+    else detail::alloc_for(device).memcpy_d2h_async(dst, data, n, device.index);
+}
 void Tensor::copy_to_host(float* dst) const {
     if (dtype != Dtype::FP32) fail("copy_to_host: tensor is not FP32");
     copy_raw_to_host(dst);

@@ -35,6 +35,18 @@ def lib() -> C.CDLL:
         L.b200h_session_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.b200h_session_free.argtypes = [C.c_void_p]
         L.b200h_session_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.b200h_session_enqueue.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.b200h_sync.argtypes = [C.c_int]
+        L.b200h_layer_create.restype = C.c_void_p
+        L.b200h_layer_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
+        L.b200h_layer_free.argtypes = [C.c_void_p]
+        L.b200h_layer_layout.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.b200h_layer_enqueue.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        L.b200h_capture_begin.restype = C.c_void_p
+        L.b200h_capture_finish.restype = C.c_void_p
+        L.b200h_capture_finish.argtypes = [C.c_void_p]
+        L.b200h_graph_launch.argtypes = [C.c_void_p]
+        L.b200h_graph_free.argtypes = [C.c_void_p]
         L.b200h_head_create.restype = C.c_void_p
         L.b200h_head_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.b200h_head_connect.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
@@ -109,9 +121,75 @@ class Session:
         _check(lib().b200h_session_run(self.h, x.ctypes.data, self.y.ctypes.data) == 0)
         return self.y
 
+    def enqueue(self, x_pinned_ptr: int, y_pinned_ptr: int) -> None:
+        """Copy in, op, copy out enqueued on the calling thread's stream; page-locked host
+        pointers; valid after sync(device)."""
+        _check(lib().b200h_session_enqueue(self.h, x_pinned_ptr, y_pinned_ptr) == 0)
+
     def close(self):
         if self.h:
             lib().b200h_session_free(self.h)
+            self.h = None
+
+
+class LayerSet:
+    """GEMV layers (M = 1) whose activations and results share one device arena each: a step is
+    one copy in, the ops through the public signatures, one copy out. `x_off` / `y_off` are the
+    byte offsets of every op's vector inside the arenas; host arenas use the same layout."""
+
+    def __init__(self, weights, x_dtype: int = 0, y_dtype: int = 0):
+        n = len(weights)
+        arr = (C.c_void_p * n)(*[w.h for w in weights])
+        self.h = lib().b200h_layer_create(arr, n, x_dtype, y_dtype)
+        _check(bool(self.h))
+        self.weights = list(weights)
+        xo, yo = (C.c_ulonglong * n)(), (C.c_ulonglong * n)()
+        xb, yb = C.c_ulonglong(), C.c_ulonglong()
+        lib().b200h_layer_layout(self.h, xo, yo, C.byref(xb), C.byref(yb))
+        self.x_off, self.y_off, self.x_bytes, self.y_bytes = list(xo), list(yo), xb.value, yb.value
+
+    def enqueue(self, x_pinned_ptr: int, y_pinned_ptr: int) -> None:
+        _check(lib().b200h_layer_enqueue(self.h, x_pinned_ptr, y_pinned_ptr) == 0)
+
+    def close(self):
+        if self.h:
+            lib().b200h_layer_free(self.h)
+            self.h = None
+
+
+def sync(device: int = 0) -> None:
+    _check(lib().b200h_sync(device) == 0)
+
+
+class Graph:
+    """brotensor_b200::CudaGraph: `with Graph.capture() as g: ...enqueue ops...` then g.launch()."""
+
+    def __init__(self):
+        self.h = None
+        self._cap = None
+
+    @classmethod
+    def capture(cls) -> "Graph":
+        return cls()
+
+    def __enter__(self):
+        self._cap = lib().b200h_capture_begin()
+        _check(bool(self._cap))
+        return self
+
+    def __exit__(self, et, ev, tb):
+        cap, self._cap = self._cap, None
+        self.h = lib().b200h_capture_finish(cap)
+        if et is None:
+            _check(bool(self.h))
+        return False
+
+    def launch(self) -> None:
+        _check(lib().b200h_graph_launch(self.h) == 0)
+
+    def close(self):
+        if self.h:
+            lib().b200h_graph_free(self.h)
             self.h = None
 
 

@@ -33,6 +33,10 @@ struct AllocVTable {
     void (*memcpy_h2d)(void* dst, const void* src, std::size_t n, int device_index) = nullptr;
     void (*memcpy_d2h)(void* dst, const void* src, std::size_t n, int device_index) = nullptr;
     void (*memcpy_d2d)(void* dst, const void* src, std::size_t n, int device_index) = nullptr;
+    // Stream-ordered copies that return at once; `src` / `dst` on the host should be page-locked
+    // (pageable memory works but makes the copy synchronous). Not in brotensor's table.
+    void (*memcpy_h2d_async)(void* dst, const void* src, std::size_t n, int device_index) = nullptr;
+    void (*memcpy_d2h_async)(void* dst, const void* src, std::size_t n, int device_index) = nullptr;
     void (*memcpy_peer)(void* dst, int dst_device, const void* src, int src_device, std::size_t n) = nullptr;
     void (*memset_zero)(void* dst, std::size_t n, int device_index) = nullptr;
     void (*sync)(int device_index) = nullptr;

@@ -92,6 +92,10 @@ struct Tensor {
     void copy_to_host_fp16(std::uint16_t* dst) const;
     void copy_to_host_bf16(std::uint16_t* dst) const;
     void copy_raw_to_host(void* dst) const;  // bytes() bytes, any dtype
+    // Stream-ordered, non-blocking forms (not in brotensor): bytes() bytes between this tensor's
+    // storage and page-locked host memory, on the calling thread's current stream.
+    void copy_raw_from_host_async(const void* src);
+    void copy_raw_to_host_async(void* dst) const;
 
 private:
     bool owns_ = false;

@@ -158,3 +158,89 @@ def test_shape_to_2d_agrees_with_reference(hostlib):
             assert (r1.value, c1.value) == (r2.value, c2.value)
         else:
             assert err.value.decode() == hostlib.b200h_last_error().decode()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,N,K", [(synth.Q4_K, 1024, 512), (synth.Q6_K, 256, 2048), (synth.Q8_0, 384, 256)])
+def test_session_enqueue_with_pinned_buffers_equals_blocking_run(built, fmt, N, K):
+    """The non-blocking round trip (page-locked host buffers, one sync) gives the blocking one's bytes."""
+    import torch
+    from brotensor_b200 import hostapi
+    hostapi.init()
+    w = hostapi.Weight(fmt, synth.make_blocks(fmt, N, K, seed=11), N, K, 0)
+    sess = hostapi.Session(w, 1, 0, 0)
+    outs = []
+    for i in range(3):
+        xh = synth.make_activations(1, K, seed=30 + i)
+        ref = sess.run(xh).copy().reshape(-1)
+        xp = torch.from_numpy(xh.reshape(-1)).pin_memory()
+        yp = torch.zeros(N, dtype=torch.float32).pin_memory()
+        sess.enqueue(xp.data_ptr(), yp.data_ptr())
+        hostapi.sync(0)
+        assert np.array_equal(yp.numpy(), ref)
+        outs.append(ref)
+    assert not np.array_equal(outs[0], outs[1])
+    sess.close()
+
+
+@pytest.mark.gpu
+def test_captured_step_replays_with_new_inputs(built):
+    """CudaGraphCapture around two ops with their host round trips; the replay sees what is in
+    the pinned input buffers at launch time."""
+    import torch
+    from brotensor_b200 import hostapi
+    hostapi.init()
+    specs = [(synth.Q4_K, 512, 512), (synth.Q6_K, 256, 2048)]
+    ws = [hostapi.Weight(f, synth.make_blocks(f, N, K, seed=5 + i), N, K, 0) for i, (f, N, K) in enumerate(specs)]
+    ss = [hostapi.Session(w, 1, 0, 0) for w in ws]
+    xp = [torch.zeros(K, dtype=torch.float32).pin_memory() for _, _, K in specs]
+    yp = [torch.zeros(N, dtype=torch.float32).pin_memory() for _, N, _ in specs]
+
+    def enqueue():
+        for s, x, y in zip(ss, xp, yp):
+            s.enqueue(x.data_ptr(), y.data_ptr())
+
+    enqueue()                     # warm-up: outputs allocated, kernels configured
+    hostapi.sync(0)
+    with hostapi.Graph.capture() as g:
+        enqueue()
+    for rep in range(3):
+        xs = [synth.make_activations(1, K, seed=70 + rep + i).reshape(-1) for i, (_, _, K) in enumerate(specs)]
+        for x, v in zip(xp, xs):
+            x.copy_(torch.from_numpy(v))
+        g.launch()
+        hostapi.sync(0)
+        for s, v, y in zip(ss, xs, yp):
+            assert np.array_equal(y.numpy(), s.run(v.reshape(1, -1)).reshape(-1)), f"replay {rep}"
+    g.close()
+
+
+@pytest.mark.gpu
+def test_layer_set_one_copy_in_one_copy_out(built):
+    """LayerSet: activations and results of several GEMVs in one arena each; a captured step with
+    one copy in and one copy out gives every op's blocking result."""
+    import torch
+    from brotensor_b200 import hostapi
+    hostapi.init()
+    specs = [(synth.Q4_K, 512, 512), (synth.Q4_K, 100, 256), (synth.Q6_K, 256, 2048), (synth.Q8_0, 96, 128)]
+    ws = [hostapi.Weight(f, synth.make_blocks(f, N, K, seed=9 + i), N, K, 0) for i, (f, N, K) in enumerate(specs)]
+    L = hostapi.LayerSet(ws)
+    assert all(o % 256 == 0 for o in L.x_off + L.y_off)
+    xa = torch.zeros(L.x_bytes, dtype=torch.uint8).pin_memory()
+    ya = torch.zeros(L.y_bytes, dtype=torch.uint8).pin_memory()
+    L.enqueue(xa.data_ptr(), ya.data_ptr())
+    hostapi.sync(0)
+    with hostapi.Graph.capture() as g:
+        L.enqueue(xa.data_ptr(), ya.data_ptr())
+    ss = [hostapi.Session(w, 1, 0, 0) for w in ws]
+    for rep in range(2):
+        xs = [synth.make_activations(1, K, seed=90 + rep + i) for i, (_, _, K) in enumerate(specs)]
+        for off, v in zip(L.x_off, xs):
+            xa[off:off + v.nbytes] = torch.from_numpy(v.reshape(-1).view(np.uint8))
+        g.launch()
+        hostapi.sync(0)
+        for s, v, off, (_, N, _) in zip(ss, xs, L.y_off, specs):
+            got = ya[off:off + 4 * N].numpy().view(np.float32)
+            assert np.array_equal(got, s.run(v).reshape(-1)), f"replay {rep}"
+    g.close()
+    L.close()
