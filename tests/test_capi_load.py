@@ -55,6 +55,14 @@ def test_argument_validation_needs_no_device(L):
     assert L.b200q_gemv(capi.Q4_K, p16, p16, capi.F32, None, p16, capi.F32, 9, 4, 256, None) == capi.ERR_UNSUPPORTED
     assert L.b200q_gemv(capi.Q4_K, None, p16, capi.F32, None, p16, capi.F32, 1, 4, 256, None) == capi.ERR_BAD_ARG
     assert L.b200q_gemv(capi.Q4_K, p16, p16 + 4, capi.F32, None, p16, capi.F32, 1, 4, 256, None) == capi.ERR_BAD_ARG
+    # the sharded form checks its rank / row arguments before it touches the device
+    tab = (ctypes.c_void_p * 8)(*([p16] * 8))
+    sh = lambda rows, off, total, rank, world: L.b200q_gemv_shard(capi.Q4_K, p16, p16, capi.F32, None, rows, 256, off,
+                                                                  total, rank, world, tab, tab, p16, None)
+    assert sh(4, 0, 4, 2, 2) == capi.ERR_BAD_ARG and b"rank 2 of 2" in L.b200q_last_error()
+    assert sh(4, 0, 4, 0, 9) == capi.ERR_BAD_ARG
+    assert sh(4, 2, 4, 0, 1) == capi.ERR_BAD_ARG and b"do not lie in" in L.b200q_last_error()
+    assert sh(0, 0, 4, 0, 1) == capi.ERR_UNSUPPORTED
     # empty problems are legal and touch nothing
     assert L.b200q_gemv(capi.Q4_K, None, None, capi.F32, None, None, capi.F32, 0, 4, 256, None) == capi.OK
     assert L.b200q_dequant(capi.Q8_0, None, None, capi.F16, 0, 32, None) == capi.OK
