@@ -28,6 +28,7 @@ struct StreamParams {
     int n_slices;        // stages per row tile
     int row_stride;      // bytes between rows inside a stage (padded)
     int n_stages;        // ring depth
+    int n_tiles_total;   // > 0: CTAs own whole 16-row tiles (tile-balanced grid); 0: rows split evenly
     // shared-memory offsets (bytes from the 128-byte aligned base)
     int off_xhi, off_xlo, off_sxhi, off_sxlo, off_red, off_stage;
     // Row-sharded output (world > 0): instead of Y, every finished row goes to all ranks'
