@@ -22,6 +22,8 @@ void stream_set_option(int which, int value);
 void gemm_set_pair(int v);
 int gemm_get_pair();
 void dp_set_groups(int v);
+void dp_set_tile_pairs(int v);
+int dp_get_tile_pairs();
 int dp_get_groups();
 int stream_get_option(int which);
 size_t gemm_tc_workspace_bytes(int fmt, int x_dtype, int M, int N, int K);
@@ -287,6 +289,7 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "gemv_stage_kb")) stream_set_option(2, value);
     else if (!strcmp(key, "gemv_grid")) stream_set_option(3, value);
     else if (!strcmp(key, "gemv_groups")) dp_set_groups(value);
+    else if (!strcmp(key, "gemv_tile_pairs")) dp_set_tile_pairs(value);
     else if (!strcmp(key, "gemm_pair")) gemm_set_pair(value);
     else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
     return B200Q_OK;
@@ -300,6 +303,7 @@ int b200q_get_option(const char* key, int* out) {
     else if (!strcmp(key, "gemv_stage_kb")) *out = stream_get_option(2);
     else if (!strcmp(key, "gemv_grid")) *out = stream_get_option(3);
     else if (!strcmp(key, "gemv_groups")) *out = dp_get_groups();
+    else if (!strcmp(key, "gemv_tile_pairs")) *out = dp_get_tile_pairs();
     else if (!strcmp(key, "gemm_pair")) *out = gemm_get_pair();
     else return fail(B200Q_ERR_BAD_ARG, "get_option: unknown key '%s'", key);
     return B200Q_OK;

@@ -396,8 +396,12 @@ __device__ __forceinline__ void item_q6k(uint32_t rowA, uint32_t rowB, int gi, i
 // the row tiles t with t % NG == g. The pipelines share only the staged activations,
 // so twice as many warps hide each other's latencies without any coupling between
 // their barrier phases.
-template <int FMT, int MT, int NG>
+// RP = row pairs per consumer warp and tile: a tile has 16 * RP rows. Two pairs per warp double
+// the bytes a tile moves per barrier round trip (what the per-tile overheads are paid on) and
+// give every lane two independent chains of work.
+template <int FMT, int MT, int NG, int RP>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_kernel(const StreamParams p) {
+    constexpr int TR = kTileRows * RP;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;  // shared-space address
     __shared__ uint64_t bar_full[NG][kMaxStages];
@@ -406,12 +410,12 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x;
-    const int row_begin = p.n_tiles_total > 0 ? min(p.N, kTileRows * (int)((long long)p.n_tiles_total * blockIdx.x / G))
+    const int row_begin = p.n_tiles_total > 0 ? min(p.N, TR * (int)((long long)p.n_tiles_total * blockIdx.x / G))
                                               : (int)((long long)p.N * blockIdx.x / G);
-    const int row_end = p.n_tiles_total > 0 ? min(p.N, kTileRows * (int)((long long)p.n_tiles_total * (blockIdx.x + 1) / G))
+    const int row_end = p.n_tiles_total > 0 ? min(p.N, TR * (int)((long long)p.n_tiles_total * (blockIdx.x + 1) / G))
                                             : (int)((long long)p.N * (blockIdx.x + 1) / G);
-    const int n_tiles = (row_end - row_begin + kTileRows - 1) / kTileRows;
-    const int stage_bytes = kTileRows * p.row_stride;
+    const int n_tiles = (row_end - row_begin + TR - 1) / TR;
+    const int stage_bytes = TR * p.row_stride;
 
     if (tid == 0) {
         abort_flag = 0;
@@ -434,8 +438,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         int slot = 0;
         uint32_t phase = 0;
         for (int tile = g; tile < n_tiles; tile += NG) {
-            const int row0 = row_begin + tile * kTileRows;
-            const int nrows = min(kTileRows, row_end - row0);
+            const int row0 = row_begin + tile * TR;
+            const int nrows = min(TR, row_end - row0);
             for (int slice = 0; slice < p.n_slices; ++slice) {
                 if (!wait_or_abort(smem_u32(&bar_empty[g][slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty)) return;
                 const int c0 = slice * p.slice_chunks;
@@ -474,15 +478,17 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     bool live = true;
     int slot = 0;
     uint32_t phase = 0;
-    float acc[2][MT];
+    float acc[RP][2][MT];
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
+    for (int pi = 0; pi < RP; ++pi)
 #pragma unroll
-        for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[pi][r][m] = 0.f;
 
     for (int tile = g; tile < n_tiles; tile += NG) {
-        const int row0 = row_begin + tile * kTileRows;
-        const int nrows = min(kTileRows, row_end - row0);
+        const int row0 = row_begin + tile * TR;
+        const int nrows = min(TR, row_end - row0);
         for (int slice = 0; slice < p.n_slices; ++slice) {
             if (live) {
                 // keep the decision warp-uniform
@@ -493,13 +499,24 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 const int c0 = slice * p.slice_chunks;
                 const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
                 const int ng = nch * kGroupsPerChunk, g0 = c0 * kGroupsPerChunk;
-                const uint32_t rowA = ring + (uint32_t)(slot * stage_bytes + (2 * wl) * p.row_stride);
-                // a tile with an odd row count has no second row for its last pair: reuse the first
-                const uint32_t rowB = (2 * wl + 1 < nrows) ? rowA + (uint32_t)p.row_stride : rowA;
+                // pair pi of this warp: rows 2 * (wl + 8 pi) and the next one; a pair past the end of
+                // the tile re-reads the warp's first pair and its sums are dropped; a tile with an
+                // odd row count has no second row for its last pair: reuse the first
+                uint32_t rowA[RP], rowB[RP];
+#pragma unroll
+                for (int pi = 0; pi < RP; ++pi) {
+                    const int r0 = 2 * (wl + kConsumerWarps * pi);
+                    const int ra = r0 < nrows ? r0 : 2 * wl;
+                    rowA[pi] = ring + (uint32_t)(slot * stage_bytes + ra * p.row_stride);
+                    rowB[pi] = (ra + 1 < nrows) ? rowA[pi] + (uint32_t)p.row_stride : rowA[pi];
+                }
                 for (int gi = lane; gi < ng; gi += 32) {
-                    if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
-                    else if constexpr (FMT == kQ8_0) item_q8_0<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
-                    else item_q6k<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
+#pragma unroll
+                    for (int pi = 0; pi < RP; ++pi) {
+                        if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                        else if constexpr (FMT == kQ8_0) item_q8_0<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                        else item_q6k<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                    }
                 }
             }
             __syncwarp();
@@ -512,29 +529,32 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         // the rows' partial sums live in this warp's lanes: lanes 0..15 finish the first
         // row of the pair, lanes 16..31 the second (five shuffles for both), then write
 #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            const bool up = lane >= 16;
-            float s = (up ? acc[1][m] : acc[0][m]) + __shfl_xor_sync(0xffffffffu, up ? acc[0][m] : acc[1][m], 16);
+        for (int pi = 0; pi < RP; ++pi) {
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            acc[0][m] = acc[1][m] = 0.f;
-            const int rr = 2 * wl + (up ? 1 : 0);
-            if ((lane & 15) == 0 && rr < nrows && m < p.M && !*(volatile int*)&abort_flag) {
-                const int n = row0 + rr;
-                if (p.bias) {
-                    if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(p.bias)[n];
-                    else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(p.bias)[n]);
-                    else s += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+            for (int m = 0; m < MT; ++m) {
+                const bool up = lane >= 16;
+                float s = (up ? acc[pi][1][m] : acc[pi][0][m]) + __shfl_xor_sync(0xffffffffu, up ? acc[pi][0][m] : acc[pi][1][m], 16);
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                acc[pi][0][m] = acc[pi][1][m] = 0.f;
+                const int rr = 2 * (wl + kConsumerWarps * pi) + (up ? 1 : 0);
+                if ((lane & 15) == 0 && rr < nrows && m < p.M && !*(volatile int*)&abort_flag) {
+                    const int n = row0 + rr;
+                    if (p.bias) {
+                        if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(p.bias)[n];
+                        else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(p.bias)[n]);
+                        else s += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+                    }
+                    const size_t o = (size_t)m * p.N + n;
+                    if (p.sh_world > 0) {
+                        // sharded output: the row goes to every rank's result vector (own included) with
+                        // plain peer stores over NVLink; which of the two vectors is this launch's parity
+                        const size_t go = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n);
+                        for (int q = 0; q < p.sh_world; ++q) p.sh_out[q][go] = s;
+                    } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
+                    else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(s);
+                    else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(s);
                 }
-                const size_t o = (size_t)m * p.N + n;
-                if (p.sh_world > 0) {
-                    // sharded output: the row goes to every rank's result vector (own included) with
-                    // plain peer stores over NVLink; which of the two vectors is this launch's parity
-                    const size_t go = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n);
-                    for (int q = 0; q < p.sh_world; ++q) p.sh_out[q][go] = s;
-                } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
-                else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(s);
-                else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(s);
             }
         }
     }
@@ -584,12 +604,17 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
 // ---- host side ------------------------------------------------------------------------
 
 static int g_opt_groups = 2;
+// 0: by shape; 1: 16-row tiles; 2: prefer one pipeline with two row pairs per warp (32-row tiles)
+static int g_opt_tile_pairs = 0;
+void dp_set_tile_pairs(int v) { g_opt_tile_pairs = v == 2 ? 2 : (v == 1 ? 1 : 0); }
+int dp_get_tile_pairs() { return g_opt_tile_pairs; }
 void dp_set_groups(int v) { g_opt_groups = v < 1 ? 1 : (v > 2 ? 2 : v); }
 int dp_get_groups() { return g_opt_groups; }
 
 // p.n_stages is the ring depth of ONE pipeline; `ng` pipelines share the shared memory.
 template <int FMT>
-static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, StreamParams& p, int& grid, size_t& smem) {
+static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int rp, StreamParams& p, int& grid, size_t& smem) {
+    const int tile_rows = kTileRows * rp;
     if (K % Chunk<FMT>::elems != 0 || M > 4) return false;
     p.M = M; p.N = N; p.K = K;
     p.row_bytes = (K / Blk<FMT>::elems) * Blk<FMT>::bytes;
@@ -616,8 +641,8 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, Strea
         const int groups = sc * gpc;
         if (groups % 32 != 0 && sc != cpr && groups < 32) continue;
         int rs = sc * Chunk<FMT>::bytes;
-        rs += ((16 - (rs % 128)) + 128) % 128;
-        const size_t sb = (size_t)kTileRows * rs;
+        if (rp == 1) rs += ((16 - (rs % 128)) + 128) % 128;
+        const size_t sb = (size_t)tile_rows * rs;
         if (sb * 2 * ng > avail) break;
         if (best && sb > target) break;
         if (groups % 32 == 0 || sc == cpr) best = sc;
@@ -626,9 +651,11 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, Strea
     if (!best) return false;
     p.slice_chunks = best;
     p.row_stride = best * Chunk<FMT>::bytes;
-    p.row_stride += ((16 - (p.row_stride % 128)) + 128) % 128;  // rows padded to 16 (mod 128)
+    // 16-row tiles: rows padded to 16 (mod 128). 32-row tiles go unpadded - all lanes of a warp read
+    // the same row pair, so the row start does not decide bank conflicts - and a third stage fits.
+    if (rp == 1) p.row_stride += ((16 - (p.row_stride % 128)) + 128) % 128;
     p.n_slices = (cpr + best - 1) / best;
-    const size_t sb = (size_t)kTileRows * p.row_stride;
+    const size_t sb = (size_t)tile_rows * p.row_stride;
     int ns = (int)(avail / (sb * ng));
     if (ns > want) ns = want;
     if (ns < 2) return false;
@@ -639,7 +666,7 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, Strea
     // whole tiles and pick, among grids of 3/4 .. 1 x the SM count, the one with the fewest
     // rounds and then the least idle tile slots: 128 CTAs x 7 tiles beat 148 CTAs x 6.05.
     p.n_tiles_total = 0;
-    const int tiles_total = (N + kTileRows - 1) / kTileRows;
+    const int tiles_total = (N + tile_rows - 1) / tile_rows;
     if (stream_get_option(3) <= 0 && tiles_total >= sms) {
         long long best_cost = -1;
         for (int gsz = sms; gsz >= (3 * sms) / 4; --gsz) {
@@ -654,7 +681,7 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, Strea
     // away from the next kernel, which under programmatic dependent launch can move in
     // beside this one and prefetch its weights
     const int rows_per_cta = (N + grid - 1) / grid;
-    const int tiles = (rows_per_cta + kTileRows - 1) / kTileRows;
+    const int tiles = (rows_per_cta + tile_rows - 1) / tile_rows;
     const int stages_seen = ((tiles + ng - 1) / ng) * p.n_slices;
     if (ns > stages_seen) ns = stages_seen < 1 ? 1 : stages_seen;
     p.n_stages = ns;
@@ -662,9 +689,9 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, Strea
     return true;
 }
 
-template <int FMT, int MT, int NG>
+template <int FMT, int MT, int NG, int RP>
 static int launch_dp_k(const StreamParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = gemv_dp_kernel<FMT, MT, NG>;
+    auto kern = gemv_dp_kernel<FMT, MT, NG, RP>;
     static bool configured[64] = {};
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
@@ -687,8 +714,9 @@ static int launch_dp_k(const StreamParams& p, int grid, size_t smem, cudaStream_
 }
 
 template <int FMT, int MT>
-static int launch_dp_g(const StreamParams& p, int ng, int grid, size_t smem, cudaStream_t st) {
-    return ng == 2 ? launch_dp_k<FMT, MT, 2>(p, grid, smem, st) : launch_dp_k<FMT, MT, 1>(p, grid, smem, st);
+static int launch_dp_g(const StreamParams& p, int ng, int rp, int grid, size_t smem, cudaStream_t st) {
+    if (ng == 2) return launch_dp_k<FMT, MT, 2, 1>(p, grid, smem, st);
+    return rp == 2 ? launch_dp_k<FMT, MT, 1, 2>(p, grid, smem, st) : launch_dp_k<FMT, MT, 1, 1>(p, grid, smem, st);
 }
 
 template <int FMT>
@@ -697,11 +725,24 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
     StreamParams p = {};
     int grid = 0;
     size_t smem = 0;
-    int ng = g_opt_groups;
-    *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, p, grid, smem);
+    // Candidates in order of preference: one pipeline with 32-row tiles (tile height option 2),
+    // two pipelines with 16-row tiles, one pipeline with 16-row tiles.
+    int ng = g_opt_groups, rp = 1;
+    *taken = false;
+    // Measured on B200: 32-row tiles pay for long Q6_K streams (LM head 128256 x 4096: 81 -> 89 % of
+    // the HBM copy rate, 32064 rows: 70 -> 74 %) and make no difference or lose elsewhere.
+    const bool tall = g_opt_tile_pairs == 2 || (g_opt_tile_pairs == 0 && FMT == kQ6_K && N >= 24000);
+    if (tall && N >= 32 * sms / 2) {
+        ng = 1; rp = 2;
+        *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, rp, p, grid, smem);
+    }
+    if (!*taken) {
+        ng = g_opt_groups; rp = 1;
+        *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, rp, p, grid, smem);
+    }
     if (!*taken && ng == 2) {  // two pipelines do not fit: one
         ng = 1;
-        *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, p, grid, smem);
+        *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, rp, p, grid, smem);
     }
     if (!*taken) return B200Q_OK;
     p.W = static_cast<const uint8_t*>(W);
@@ -723,10 +764,10 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
         p.sh_state = sh->state;
     }
     switch (M) {
-        case 1: return launch_dp_g<FMT, 1>(p, ng, grid, smem, st);
-        case 2: return launch_dp_g<FMT, 2>(p, ng, grid, smem, st);
-        case 3: return launch_dp_g<FMT, 3>(p, ng, grid, smem, st);
-        default: return launch_dp_g<FMT, 4>(p, ng, grid, smem, st);
+        case 1: return launch_dp_g<FMT, 1>(p, ng, rp, grid, smem, st);
+        case 2: return launch_dp_g<FMT, 2>(p, ng, rp, grid, smem, st);
+        case 3: return launch_dp_g<FMT, 3>(p, ng, rp, grid, smem, st);
+        default: return launch_dp_g<FMT, 4>(p, ng, rp, grid, smem, st);
     }
 }
 
