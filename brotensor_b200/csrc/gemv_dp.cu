@@ -391,6 +391,95 @@ __device__ __forceinline__ void item_q6k(uint32_t rowA, uint32_t rowB, int gi, i
     }
 }
 
+// ---- Q6_K in units of half a group --------------------------------------------------------
+// The 64 elements {32 Q + 16 H + i : Q = 0..3, i = 0..15} of a 128-element group use ql words
+// 4H..4H+3 and 4H+8..4H+11 and qh words 4H..4H+3 of the group's bytes - half of its loads - so
+// a lane can take (group, H) as its unit of work: 32 lanes then cover 16 groups (one 2048-element
+// chunk), slices can be half as long and two pipelines fit beside a long activation vector.
+template <int MT, int Q>
+__device__ __forceinline__ void q6_sub_h(const uint32_t (&ql)[2][8], const uint32_t (&qh)[2][4], const uint32_t (&su)[2][2],
+                                         int H, int gg, const XAddr& xa, float (&accg)[2][MT]) {
+    const int SI = 2 * Q + H;  // scale byte and 16-element sum index inside the group
+    uint4 x0[MT], x1[MT];
+    int sx[MT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const uint32_t xg = x_group(xa, m, gg) + (uint32_t)(32 * H);
+        x0[m] = lds128i<64 * Q>(xg);
+        x1[m] = lds128i<64 * Q + 16>(xg);
+        sx[m] = (int)lds32i<8 * Q>(xa.sxi + (uint32_t)((m * (xa.K >> 4) + gg * 8 + H) * 4));
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        uint32_t v[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t a = ql[r][4 * (Q & 1) + w], hb = qh[r][w];
+            const uint32_t nib = (Q < 2 ? a : (a >> 4)) & 0x0F0F0F0Fu;
+            const uint32_t h2 = (Q == 0 ? hb << 4 : Q == 1 ? hb << 2 : Q == 2 ? hb : hb >> 2) & 0x30303030u;
+            v[w] = nib | h2;
+        }
+        const float scf = biased_s8_to_f32(su[r][Q >> 1], 2 * (Q & 1) + H);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            int c0 = 0, c1 = 0;
+            c0 = dp2a_lo_su(x0[m].x, v[0], c0);
+            c0 = dp2a_hi_su(x0[m].y, v[0], c0);
+            c1 = dp2a_lo_su(x0[m].z, v[1], c1);
+            c1 = dp2a_hi_su(x0[m].w, v[1], c1);
+            c0 = dp2a_lo_su(x1[m].x, v[2], c0);
+            c0 = dp2a_hi_su(x1[m].y, v[2], c0);
+            c1 = dp2a_lo_su(x1[m].z, v[3], c1);
+            c1 = dp2a_hi_su(x1[m].w, v[3], c1);
+            accg[r][m] = fmaf(scf, (float)(c0 + c1 - 32 * sx[m]), accg[r][m]);
+        }
+    }
+}
+
+template <int MT>
+__device__ __forceinline__ void item_q6k_half(uint32_t rowA, uint32_t rowB, int gi, int H, int gg, const XAddr& xa,
+                                              float (&acc)[2][MT]) {
+    const int bi = gi >> 1, G = gi & 1;
+    const uint32_t sh = (uint32_t)(bi & 1) * 16u;  // odd blocks start at 2 (mod 4): aligned words + funnel shift
+    uint32_t ql[2][8], qh[2][4], su[2][2];
+    float d[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t L = (r ? rowB : rowA) + (uint32_t)(bi * 210 - (bi & 1) * 2);
+        const uint32_t La = L + 64u * G + 16u * H, Lh = L + 128u + 32u * G + 16u * H, Ls = L + 192u + 8u * G;
+        uint32_t ra[5], rb[5], rh[5], rs[3];
+        load_words<5>(La, ra);
+        load_words<5>(La + 32u, rb);
+        load_words<5>(Lh, rh);
+        load_words<3>(Ls, rs);
+        const uint32_t rd = lds32i<208>(L);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            ql[r][k] = __funnelshift_r(ra[k], ra[k + 1], sh);
+            ql[r][4 + k] = __funnelshift_r(rb[k], rb[k + 1], sh);
+            qh[r][k] = __funnelshift_r(rh[k], rh[k + 1], sh);
+        }
+        su[r][0] = __funnelshift_r(rs[0], rs[1], sh) ^ 0x80808080u;
+        su[r][1] = __funnelshift_r(rs[1], rs[2], sh) ^ 0x80808080u;
+        d[r] = h2f((rd >> sh) & 0xFFFFu);
+    }
+    float accg[2][MT];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) accg[r][m] = 0.f;
+    q6_sub_h<MT, 0>(ql, qh, su, H, gg, xa, accg);
+    q6_sub_h<MT, 1>(ql, qh, su, H, gg, xa, accg);
+    q6_sub_h<MT, 2>(ql, qh, su, H, gg, xa, accg);
+    q6_sub_h<MT, 3>(ql, qh, su, H, gg, xa, accg);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const float xs = __uint_as_float(lds32i<0>(xa.xsc + (uint32_t)(m * xa.groups + gg) * 4u));
+#pragma unroll
+        for (int r = 0; r < 2; ++r) acc[r][m] = fmaf(d[r] * xs, accg[r][m], acc[r][m]);
+    }
+}
+
 // NG independent pipelines inside one CTA: pipeline g has eight consumer warps, its own
 // producer warp, its own ring of p.n_stages stages and its own barriers, and works on
 // the row tiles t with t % NG == g. The pipelines share only the staged activations,
@@ -510,12 +599,19 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                     rowA[pi] = ring + (uint32_t)(slot * stage_bytes + ra * p.row_stride);
                     rowB[pi] = (ra + 1 < nrows) ? rowA[pi] + (uint32_t)p.row_stride : rowA[pi];
                 }
-                for (int gi = lane; gi < ng; gi += 32) {
+                if constexpr (FMT == kQ6_K) {
+                    // half-group units: lanes 0..15 take H = 0 of sixteen groups, lanes 16..31 H = 1
+                    for (int gi = (lane & 15); gi < ng; gi += 16) {
 #pragma unroll
-                    for (int pi = 0; pi < RP; ++pi) {
-                        if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
-                        else if constexpr (FMT == kQ8_0) item_q8_0<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
-                        else item_q6k<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                        for (int pi = 0; pi < RP; ++pi) item_q6k_half<MT>(rowA[pi], rowB[pi], gi, lane >> 4, g0 + gi, xa, acc[pi]);
+                    }
+                } else {
+                    for (int gi = lane; gi < ng; gi += 32) {
+#pragma unroll
+                        for (int pi = 0; pi < RP; ++pi) {
+                            if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                            else item_q8_0<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                        }
                     }
                 }
             }
@@ -637,15 +733,16 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
     int want = stream_get_option(0);
     want = want < 2 ? 2 : (want > kMaxStages ? kMaxStages : want);
     int best = 0;
+    constexpr int glanes = FMT == kQ6_K ? 16 : 32;  // groups that keep a warp's 32 lanes busy
     for (int sc = 1; sc <= cpr; ++sc) {
         const int groups = sc * gpc;
-        if (groups % 32 != 0 && sc != cpr && groups < 32) continue;
+        if (groups % glanes != 0 && sc != cpr && groups < glanes) continue;
         int rs = sc * Chunk<FMT>::bytes;
         if (rp == 1) rs += ((16 - (rs % 128)) + 128) % 128;
         const size_t sb = (size_t)tile_rows * rs;
         if (sb * 2 * ng > avail) break;
         if (best && sb > target) break;
-        if (groups % 32 == 0 || sc == cpr) best = sc;
+        if (groups % glanes == 0 || sc == cpr) best = sc;
         else if (!best) best = sc;
     }
     if (!best) return false;
@@ -729,9 +826,10 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
     // two pipelines with 16-row tiles, one pipeline with 16-row tiles.
     int ng = g_opt_groups, rp = 1;
     *taken = false;
-    // Measured on B200: 32-row tiles pay for long Q6_K streams (LM head 128256 x 4096: 81 -> 89 % of
-    // the HBM copy rate, 32064 rows: 70 -> 74 %) and make no difference or lose elsewhere.
-    const bool tall = g_opt_tile_pairs == 2 || (g_opt_tile_pairs == 0 && FMT == kQ6_K && N >= 24000);
+    // Measured on B200: with two pipelines of 16-row tiles available, 32-row tiles in one pipeline
+    // make no difference (Q4_K, Q8_0) or lose (Q6_K in half-group units: LM head 94 % vs 70 % of
+    // the HBM copy rate), so they are only taken on request.
+    const bool tall = g_opt_tile_pairs == 2;
     if (tall && N >= 32 * sms / 2) {
         ng = 1; rp = 2;
         *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, rp, p, grid, smem);
