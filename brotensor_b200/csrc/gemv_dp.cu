@@ -764,7 +764,7 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
     // rounds and then the least idle tile slots: 128 CTAs x 7 tiles beat 148 CTAs x 6.05.
     p.n_tiles_total = 0;
     const int tiles_total = (N + tile_rows - 1) / tile_rows;
-    if (stream_get_option(3) <= 0 && tiles_total >= sms) {
+    if (stream_get_option(3) <= 0 && M == 1 && tiles_total >= sms) {  // more rows are compute-bound: every SM counts
         long long best_cost = -1;
         for (int gsz = sms; gsz >= (3 * sms) / 4; --gsz) {
             const int per = (tiles_total + gsz - 1) / gsz;

@@ -360,3 +360,4 @@ def test_gemm_cta_pair_equals_single_cta(fmt, N, K, M, cpu_oracle):
     assert torch.equal(y0, y1)
     assert oracle.rel_l2(y1.cpu().numpy(), cpu_oracle.matmul(fmt, Wh, xh, threads=8)) < 2e-3
     assert ops.device_status() == 0
+
