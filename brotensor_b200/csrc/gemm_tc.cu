@@ -199,8 +199,8 @@ static int round_up16(int v) { return (v + 15) & ~15; }
 
 int launch_gemm_pair_pass(int fmt, const void* W, const uint8_t* Xp, int tok_stride, const void* bias, int bias_dtype,
                           void* Y, int y_dtype, int tokens, int N, int K, int* status, cudaStream_t st);
-// 1: passes run on CTA pairs (gemm_tc2.cu); 0: one CTA per 128 weight rows (this file);
-// -1: by format - pairs where their producers are the faster ones (Q4_K, Q8_0)
+// non-zero: passes run on CTA pairs (gemm_tc2.cu, the default); 0: one CTA per 128 weight rows
+// (this file; kept as the reference the pair kernel is compared with bit for bit)
 static int g_gemm_pair = -1;
 void gemm_set_pair(int v) { g_gemm_pair = v < 0 ? -1 : (v ? 1 : 0); }
 int gemm_get_pair() { return g_gemm_pair; }
@@ -208,7 +208,7 @@ int gemm_get_pair() { return g_gemm_pair; }
 static bool gemm_tc_takes(int fmt, const void* W, int M, int K) {
     if (M <= 8) return false;                 // small batches stream the weight through the decode GEMV
     if (K % 256 != 0) return false;
-    if (fmt == kQ4_K && (reinterpret_cast<uintptr_t>(W) & 15) != 0) return false;  // 16-byte block loads
+    if ((reinterpret_cast<uintptr_t>(W) & 15) != 0) return false;  // the producers load aligned words / 16-byte blocks
     return fmt == kQ4_K || fmt == kQ6_K || fmt == kQ8_0;
 }
 
@@ -255,7 +255,7 @@ int launch_gemm_tc(int fmt, const void* W, const void* X, int x_dtype, const voi
     }
     const int ysz = y_dtype == B200Q_DT_F32 ? 4 : 2;
     for (int t0 = 0; t0 < M; t0 += kMaxTokens) {
-        if (g_gemm_pair > 0 || (g_gemm_pair < 0 && fmt != kQ6_K)) {
+        if (g_gemm_pair != 0) {
             const int tokens = M - t0 < kMaxTokens ? M - t0 : kMaxTokens;
             if (int rc = launch_gemm_pair_pass(fmt, W, static_cast<const uint8_t*>(ws) + (size_t)t0 * 128u, tok_total, bias, x_dtype,
                                                static_cast<char*>(Y) + (size_t)t0 * N * ysz, y_dtype, tokens, N, K, status, st))

@@ -134,6 +134,53 @@ __device__ __forceinline__ void generic_half_to_smem(const uint8_t* row, int kb,
         sts128(rowaddr + (((uint32_t)c ^ r7) << 4), o);
     }
 }
+// One Q8_0 block (FP16 d + 32 int8) held as the nine aligned words that cover it: an even block
+// (H = 0) starts on a word, its quants two bytes in; an odd block (H = 1) was read from two bytes
+// before its start, so d is the high half of word 0 and the quants are words 1..8. The thread
+// writes its 32 weights as 16-byte chunks 4H .. 4H+3 of the row: d * q is exact in FP32, one rounding.
+__device__ __forceinline__ void q8_0_half_to_smem(const uint32_t (&w)[9], uint32_t rowaddr, uint32_t r7, int H) {
+    const float d = h2f(H ? (w[0] >> 16) : (w[0] & 0xFFFFu));
+    const uint32_t sh = 16u + 16u * (uint32_t)H;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t q = __funnelshift_rc(w[2 * c + j], w[2 * c + j + 1], sh) ^ 0x80808080u;  // int8 + 128
+            float f[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = d * (__uint_as_float(__byte_perm(q, 0x4B000000u, 0x7440 | i)) - 8388736.0f);
+            o[2 * j] = pack_h2(f[0], f[1]);
+            o[2 * j + 1] = pack_h2(f[2], f[3]);
+        }
+        sts128(rowaddr + (((uint32_t)(c + 4 * H) ^ r7) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+    }
+}
+// One quad (32 elements) of a Q6_K block: `ql` its 32 nibble bytes (low nibbles for quads 0 and 1,
+// high for 2 and 3), `qh` the group's 32 high-bit bytes (two bits per quad), `sc2` the quad's two
+// int8 sub-block scales, `d16` the block's FP16 d. w = d * sc * (raw6 - 32): d * sc and the product
+// with the 6-bit value are exact in FP32, one rounding to FP16. Written as chunks 4H .. 4H+3 of the row.
+__device__ __forceinline__ void q6k_quad_to_smem(const uint32_t (&ql)[8], const uint32_t (&qh)[8], uint32_t sc2, uint32_t d16,
+                                                 int quad, uint32_t rowaddr, uint32_t r7, int H) {
+    const float d = h2f(d16 & 0xFFFFu);
+    const float ds0 = d * (float)(int)(signed char)(sc2 & 0xFFu), ds1 = d * (float)(int)(signed char)((sc2 >> 8) & 0xFFu);
+    const uint32_t nsh = quad >= 2 ? 4u : 0u, hsh = 2u * (uint32_t)quad;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const float ds = c < 2 ? ds0 : ds1;  // elements 0..15 / 16..31 of the quad
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t v = ((ql[2 * c + j] >> nsh) & 0x0F0F0F0Fu) | (((qh[2 * c + j] >> hsh) & 0x03030303u) << 4);  // raw6, 0..63
+            float f[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = ds * (__uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440 | i)) - 8388640.0f);  // 2^23 + 32
+            o[2 * j] = pack_h2(f[0], f[1]);
+            o[2 * j + 1] = pack_h2(f[2], f[3]);
+        }
+        sts128(rowaddr + (((uint32_t)(c + 4 * H) ^ r7) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+    }
+}
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 template <int FMT>
@@ -274,7 +321,50 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
 #pragma unroll
             for (int i = 0; i < 9; ++i) nxt[i] = __ldg(reinterpret_cast<const uint4*>(rowp) + i);
         }
+        // Q8_0: the thread's block of the next stage (nine aligned words), loaded one stage ahead
+        uint32_t w8[9], w8n[9];
+        const uint8_t* q8p = rowp + 34 * H - 2 * H;  // block 2 kb + H of the row, from a word boundary
+        if constexpr (FMT == kQ8_0) {
+#pragma unroll
+            for (int i = 0; i < 9; ++i) w8n[i] = __ldg(reinterpret_cast<const uint32_t*>(q8p) + i);
+        }
+        // Q6_K: the thread's quad of the next stage - nine aligned words each of nibble and high-bit
+        // bytes (blocks are 210 bytes, so odd blocks start two bytes past a word: funnel shift), its
+        // two scales and d - loaded one stage ahead
+        uint32_t l6[9], h6[9], s6 = 0, d6 = 0, f6 = 0, l6n[9], h6n[9], s6n = 0, d6n = 0, f6n = 0;
+        auto q6_load = [&](int kbb, uint32_t (&L)[9], uint32_t (&Hh)[9], uint32_t& S, uint32_t& D, uint32_t& F) {
+            const int blk = kbb >> 2, P = kbb & 3, grp = P >> 1, quad = 2 * (P & 1) + H;
+            const uint8_t* b0 = rowp + (size_t)blk * 210;
+            // blocks and rows are only 2-byte aligned (210 bytes; a row of an odd number of blocks):
+            // read from the word boundary at or before the block and shift by what was skipped
+            const uint32_t skip = (uint32_t)(reinterpret_cast<uintptr_t>(b0) & 2u);
+            F = skip * 8u;
+            const uint8_t* al = b0 - skip;
+            const uint32_t* pl = reinterpret_cast<const uint32_t*>(al + grp * 64 + H * 32);
+            const uint32_t* ph = reinterpret_cast<const uint32_t*>(al + 128 + grp * 32);
+#pragma unroll
+            for (int i = 0; i < 9; ++i) L[i] = __ldg(pl + i);
+#pragma unroll
+            for (int i = 0; i < 9; ++i) Hh[i] = __ldg(ph + i);
+            S = __ldg(reinterpret_cast<const unsigned short*>(b0 + 192 + grp * 8 + quad * 2));
+            D = __ldg(reinterpret_cast<const unsigned short*>(b0 + 208));
+        };
+        if constexpr (FMT == kQ6_K) q6_load(0, l6n, h6n, s6n, d6n, f6n);
         for (int kb = 0; kb < n_kb; ++kb) {
+            if constexpr (FMT == kQ6_K) {
+#pragma unroll
+                for (int i = 0; i < 9; ++i) { l6[i] = l6n[i]; h6[i] = h6n[i]; }
+                s6 = s6n; d6 = d6n; f6 = f6n;
+                if (kb + 1 < n_kb) q6_load(kb + 1, l6n, h6n, s6n, d6n, f6n);
+            }
+            if constexpr (FMT == kQ8_0) {
+#pragma unroll
+                for (int i = 0; i < 9; ++i) w8[i] = w8n[i];
+                if (kb + 1 < n_kb) {
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) w8n[i] = __ldg(reinterpret_cast<const uint32_t*>(q8p + (size_t)(kb + 1) * 68) + i);
+                }
+            }
             if constexpr (FMT == kQ4_K) {
                 if ((kb & 3) == 0) {
                     const int b = kb >> 2;
@@ -299,8 +389,16 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                         case 2: q4k_half_to_smem<2>(cur, rowaddr, r7, H); break;
                         default: q4k_half_to_smem<3>(cur, rowaddr, r7, H); break;
                     }
+                } else if constexpr (FMT == kQ8_0) {
+                    q8_0_half_to_smem(w8, rowaddr, r7, H);
                 } else {
-                    generic_half_to_smem<FMT>(rowp, kb, H, rowaddr, r7);
+                    uint32_t ql[8], qh[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        ql[i] = __funnelshift_r(l6[i], l6[i + 1], f6);
+                        qh[i] = __funnelshift_r(h6[i], h6[i + 1], f6);
+                    }
+                    q6k_quad_to_smem(ql, qh, s6, d6, 2 * (kb & 1) + H, rowaddr, r7, H);
                 }
                 fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor cores of the pair
             }
