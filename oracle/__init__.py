@@ -26,12 +26,16 @@ _f64p = C.POINTER(C.c_double)
 _u16p = C.POINTER(C.c_uint16)
 
 
+# where the reference checkout lives when it is available (the Makefile's REF)
+REF_TREE = os.environ.get("BROTENSOR_REF", os.path.join(os.sep, "root", "reference"))
+
+
 def build(force: bool = False) -> None:
     """Compile liboracle.so (and _ref/libref.so where the reference tree exists)."""
     if force or not os.path.exists(os.path.join(HERE, "liboracle.so")) or (
-        os.path.isdir("/root/reference/tests") and not os.path.exists(os.path.join(HERE, "_ref", "libref.so"))
+        os.path.isdir(os.path.join(REF_TREE, "tests")) and not os.path.exists(os.path.join(HERE, "_ref", "libref.so"))
     ):
-        subprocess.run(["make", "-s", "-C", HERE], check=True)
+        subprocess.run(["make", "-s", "-C", HERE, "REF=" + REF_TREE], check=True)
 
 
 def _ptr(a: np.ndarray, t):
@@ -187,7 +191,7 @@ def ref():
     if _ref is None:
         p = os.path.join(HERE, "_ref", "libref.so")
         if not os.path.exists(p):
-            if os.path.isdir("/root/reference/tests"):
+            if os.path.isdir(os.path.join(REF_TREE, "tests")):
                 build(force=True)
             else:
                 return None
