@@ -18,6 +18,9 @@ int launch_gemv_stream(int fmt, const void* W, const void* X, int x_dtype, const
                        int M, int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken);
 int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
                    int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh);
+int launch_gemv_dp_multi(int fmt, int n_seg, const void* const* W, const int* N, void* const* Y, const void* const* bias,
+                         const void* X, int x_dtype, int y_dtype, int K, int sms, size_t smem_max, int* status, cudaStream_t st,
+                         bool* taken);
 void stream_set_option(int which, int value);
 void gemm_set_pair(int v);
 int gemm_get_pair();
@@ -180,6 +183,29 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
             return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the streaming kernel", M, N, K, fmt);
     }
     return launch_gemv_simple(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
+}
+
+int b200q_gemv_multi(int fmt, int n, const void* const* W, const int* N, void* const* Y, const void* const* bias,
+                     const void* x, int x_dtype, int y_dtype, int K, void* stream) {
+    if (n < 1 || n > kMaxSegments) return fail(B200Q_ERR_BAD_ARG, "gemv_multi: %d matrices (1..%d)", n, kMaxSegments);
+    if (!W || !N || !Y) return fail(B200Q_ERR_BAD_ARG, "gemv_multi: null table");
+    for (int s = 0; s < n; ++s) {
+        if (N[s] <= 0) return fail(B200Q_ERR_BAD_ARG, "gemv_multi: matrix %d has %d rows", s, N[s]);
+        if (int rc = check_linear_args("gemv_multi", fmt, W[s], x, x_dtype, Y[s], y_dtype, 1, N[s], K)) return rc;
+    }
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (n > 1 && (g_opt_gemv_path == 0 || g_opt_gemv_path == 3)) {
+        bool taken = false;
+        if (int rc = launch_gemv_dp_multi(fmt, n, W, N, Y, bias, x, x_dtype, y_dtype, K, d->sms, d->smem_optin - 1024, d->status, st, &taken))
+            return rc;
+        if (taken) return B200Q_OK;
+    }
+    // shapes the grouped kernel does not take: one launch per matrix
+    for (int s = 0; s < n; ++s)
+        if (int rc = b200q_gemv(fmt, W[s], x, x_dtype, bias ? bias[s] : nullptr, Y[s], y_dtype, 1, N[s], K, stream)) return rc;
+    return B200Q_OK;
 }
 
 int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,

@@ -52,6 +52,7 @@ void set_error(const char* fmt, ...);
 int fail(int code, const char* fmt, ...);
 
 constexpr int kMaxShardRanks = 8;
+constexpr int kMaxSegments = 4;  // weight matrices one grouped GEMV launch can take
 // Host-side description of a row-sharded GEMV output (StreamParams::sh_* on the device side).
 struct ShardOut {
     int world, rank, row_offset, total_rows;

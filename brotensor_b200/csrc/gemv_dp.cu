@@ -485,6 +485,23 @@ __device__ __forceinline__ void item_q6k_half(uint32_t rowA, uint32_t rowB, int 
 // the row tiles t with t % NG == g. The pipelines share only the staged activations,
 // so twice as many warps hide each other's latencies without any coupling between
 // their barrier phases.
+// Where the tile that starts at virtual row `vrow` lives: which matrix, which of its rows.
+struct TileRef {
+    const uint8_t* W;
+    void* Y;
+    const void* bias;
+    int N;     // rows of that matrix (leading dimension of its Y)
+    int row0;  // first row of the tile inside that matrix
+};
+__device__ __forceinline__ TileRef tile_ref(const StreamParams& p, int vrow) {
+    if (p.n_seg <= 1) return {p.W, p.Y, p.bias, p.N, vrow};
+    int s = 0;
+#pragma unroll
+    for (int i = 1; i < kMaxSegments; ++i)
+        if (i < p.n_seg && vrow >= kTileRows * p.seg_tile0[i]) s = i;
+    return {p.seg_W[s], p.seg_Y[s], p.seg_bias[s], p.seg_rows[s], vrow - kTileRows * p.seg_tile0[s]};
+}
+
 // RP = row pairs per consumer warp and tile: a tile has 16 * RP rows. Two pairs per warp double
 // the bytes a tile moves per barrier round trip (what the per-tile overheads are paid on) and
 // give every lane two independent chains of work.
@@ -499,10 +516,12 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x;
-    const int row_begin = p.n_tiles_total > 0 ? min(p.N, TR * (int)((long long)p.n_tiles_total * blockIdx.x / G))
-                                              : (int)((long long)p.N * blockIdx.x / G);
-    const int row_end = p.n_tiles_total > 0 ? min(p.N, TR * (int)((long long)p.n_tiles_total * (blockIdx.x + 1) / G))
-                                            : (int)((long long)p.N * (blockIdx.x + 1) / G);
+    // virtual rows of the launch: the matrix's rows, or with several matrices their tile-padded concatenation
+    const int vrows = p.n_seg > 1 ? kTileRows * p.seg_tile0[p.n_seg] : p.N;
+    const int row_begin = p.n_tiles_total > 0 ? min(vrows, TR * (int)((long long)p.n_tiles_total * blockIdx.x / G))
+                                              : (int)((long long)vrows * blockIdx.x / G);
+    const int row_end = p.n_tiles_total > 0 ? min(vrows, TR * (int)((long long)p.n_tiles_total * (blockIdx.x + 1) / G))
+                                            : (int)((long long)vrows * (blockIdx.x + 1) / G);
     const int n_tiles = (row_end - row_begin + TR - 1) / TR;
     const int stage_bytes = TR * p.row_stride;
 
@@ -527,8 +546,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         int slot = 0;
         uint32_t phase = 0;
         for (int tile = g; tile < n_tiles; tile += NG) {
-            const int row0 = row_begin + tile * TR;
-            const int nrows = min(TR, row_end - row0);
+            const TileRef tr = tile_ref(p, row_begin + tile * TR);
+            const int row0 = tr.row0;
+            const int nrows = min(min(TR, row_end - (row_begin + tile * TR)), tr.N - row0);
             for (int slice = 0; slice < p.n_slices; ++slice) {
                 if (!wait_or_abort(smem_u32(&bar_empty[g][slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty)) return;
                 const int c0 = slice * p.slice_chunks;
@@ -538,7 +558,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 if (lane == 0) mbar_arrive_expect_tx(full, bytes * (uint32_t)nrows);
                 __syncwarp();
                 if (lane < nrows) {
-                    const uint8_t* src = p.W + (size_t)(row0 + lane) * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
+                    const uint8_t* src = tr.W + (size_t)(row0 + lane) * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
                     bulk_g2s(ring + slot * stage_bytes + lane * p.row_stride, src, bytes, full);
                 }
                 if (++slot == p.n_stages) {
@@ -576,8 +596,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
             for (int m = 0; m < MT; ++m) acc[pi][r][m] = 0.f;
 
     for (int tile = g; tile < n_tiles; tile += NG) {
-        const int row0 = row_begin + tile * TR;
-        const int nrows = min(TR, row_end - row0);
+        const TileRef tr = tile_ref(p, row_begin + tile * TR);
+        const int row0 = tr.row0;
+        const int nrows = min(min(TR, row_end - (row_begin + tile * TR)), tr.N - row0);
         for (int slice = 0; slice < p.n_slices; ++slice) {
             if (live) {
                 // keep the decision warp-uniform
@@ -636,20 +657,20 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 const int rr = 2 * (wl + kConsumerWarps * pi) + (up ? 1 : 0);
                 if ((lane & 15) == 0 && rr < nrows && m < p.M && !*(volatile int*)&abort_flag) {
                     const int n = row0 + rr;
-                    if (p.bias) {
-                        if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(p.bias)[n];
-                        else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(p.bias)[n]);
-                        else s += __bfloat162float(static_cast<const __nv_bfloat16*>(p.bias)[n]);
+                    if (tr.bias) {
+                        if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(tr.bias)[n];
+                        else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(tr.bias)[n]);
+                        else s += __bfloat162float(static_cast<const __nv_bfloat16*>(tr.bias)[n]);
                     }
-                    const size_t o = (size_t)m * p.N + n;
+                    const size_t o = (size_t)m * tr.N + n;
                     if (p.sh_world > 0) {
                         // sharded output: the row goes to every rank's result vector (own included) with
                         // plain peer stores over NVLink; which of the two vectors is this launch's parity
                         const size_t go = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n);
                         for (int q = 0; q < p.sh_world; ++q) p.sh_out[q][go] = s;
-                    } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(p.Y)[o] = s;
-                    else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(p.Y)[o] = __float2half_rn(s);
-                    else static_cast<__nv_bfloat16*>(p.Y)[o] = __float2bfloat16_rn(s);
+                    } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(tr.Y)[o] = s;
+                    else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(tr.Y)[o] = __float2half_rn(s);
+                    else static_cast<__nv_bfloat16*>(tr.Y)[o] = __float2bfloat16_rn(s);
                 }
             }
         }
@@ -880,6 +901,59 @@ int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const voi
         case kQ8_0: return launch_dp_f<kQ8_0>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
     }
     return fail(B200Q_ERR_BAD_ARG, "gemv: unknown block format %d", fmt);
+}
+
+// Several matrices of one format and K against one activation vector (M = 1) in one launch: the
+// fixed cost of a decode GEMV launch (a few microseconds) is paid once for q/k/v or gate/up.
+template <int FMT>
+static int launch_dp_multi_f(int n_seg, const void* const* W, const int* N, void* const* Y, const void* const* bias, const void* X,
+                             int x_dtype, int y_dtype, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken) {
+    StreamParams p = {};
+    int tiles = 0;
+    for (int s = 0; s < n_seg; ++s) {
+        p.seg_tile0[s] = tiles;
+        p.seg_rows[s] = N[s];
+        p.seg_W[s] = static_cast<const uint8_t*>(W[s]);
+        p.seg_Y[s] = Y[s];
+        p.seg_bias[s] = bias ? bias[s] : nullptr;
+        tiles += (N[s] + kTileRows - 1) / kTileRows;
+    }
+    p.seg_tile0[n_seg] = tiles;
+    int grid = 0, ng = g_opt_groups;
+    size_t smem = 0;
+    *taken = plan_dp<FMT>(1, kTileRows * tiles, K, sms, smem_max, ng, 1, p, grid, smem);
+    if (!*taken && ng == 2) {
+        ng = 1;
+        *taken = plan_dp<FMT>(1, kTileRows * tiles, K, sms, smem_max, ng, 1, p, grid, smem);
+    }
+    if (!*taken) return B200Q_OK;
+    if (p.n_tiles_total == 0) {  // fewer tiles than SMs: still whole tiles per CTA, so that no tile spans two matrices
+        p.n_tiles_total = tiles;
+        if (grid > tiles) grid = tiles;
+    }
+    p.n_seg = n_seg;
+    p.W = p.seg_W[0];
+    p.Y = p.seg_Y[0];
+    p.bias = p.seg_bias[0];
+    p.X = X;
+    p.status = status;
+    p.x_dtype = x_dtype;
+    p.y_dtype = y_dtype;
+    return launch_dp_g<FMT, 1>(p, ng, 1, grid, smem, st);
+}
+
+int launch_gemv_dp_multi(int fmt, int n_seg, const void* const* W, const int* N, void* const* Y, const void* const* bias,
+                         const void* X, int x_dtype, int y_dtype, int K, int sms, size_t smem_max, int* status, cudaStream_t st,
+                         bool* taken) {
+    *taken = false;
+    for (int s = 0; s < n_seg; ++s)
+        if ((reinterpret_cast<uintptr_t>(W[s]) & 15) != 0) return B200Q_OK;
+    switch (fmt) {
+        case kQ4_K: return launch_dp_multi_f<kQ4_K>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);
+        case kQ6_K: return launch_dp_multi_f<kQ6_K>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);
+        case kQ8_0: return launch_dp_multi_f<kQ8_0>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);
+    }
+    return fail(B200Q_ERR_BAD_ARG, "gemv_multi: unknown block format %d", fmt);
 }
 
 }  // namespace b200q

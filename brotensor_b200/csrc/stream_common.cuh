@@ -31,6 +31,15 @@ struct StreamParams {
     int n_tiles_total;   // > 0: CTAs own whole 16-row tiles (tile-balanced grid); 0: rows split evenly
     // shared-memory offsets (bytes from the 128-byte aligned base)
     int off_xhi, off_xlo, off_sxhi, off_sxlo, off_red, off_stage;
+    // Several weight matrices of one format and K that share the activation vector (n_seg > 1):
+    // segment s occupies the virtual rows [16 * seg_tile0[s], 16 * seg_tile0[s] + seg_rows[s]) of the
+    // launch; W / Y / bias / N above describe segment 0 when n_seg <= 1.
+    int n_seg;
+    int seg_rows[kMaxSegments];
+    int seg_tile0[kMaxSegments + 1];
+    const uint8_t* seg_W[kMaxSegments];
+    void* seg_Y[kMaxSegments];
+    const void* seg_bias[kMaxSegments];
     // Row-sharded output (world > 0): instead of Y, every finished row goes to all ranks'
     // result vectors through peer pointers, followed by an arrival flag per rank.
     int sh_world, sh_rank;       // sh_world == 0: plain GEMV

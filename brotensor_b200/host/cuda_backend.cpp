@@ -176,6 +176,41 @@ void gemv_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op,
                             K, cuda_current_stream(W.device.index)), op);
 }
 
+void group_impl(const Tensor* const* W, const Tensor* const* bias, int n, const Tensor& x, Tensor* const* y) {
+    const char* op = "linear_forward_group_fp16";
+    if (n > 4) op_fail(op, "at most four matrices per call");
+    const Dtype wdt = W[0]->dtype;
+    const int block = wdt == Dtype::Q8_0 ? 32 : 256;
+    const char* dname = wdt == Dtype::Q4_K ? "Q4_K" : wdt == Dtype::Q6_K ? "Q6_K" : wdt == Dtype::Q8_0 ? "Q8_0" : nullptr;
+    if (!dname) op_fail(op, "W must be Dtype::Q4_K, Q6_K or Q8_0");
+    if (!act_dtype(x.dtype)) op_fail(op, "x must be FP16 (FP32 and BF16 are accepted as well)");
+    const int K = W[0]->cols;
+    if (x.rows != K || x.cols != 1) op_fail(op, "x shape must be (in, 1)");
+    const void* Wp[4];
+    void* Yp[4];
+    const void* Bp[4];
+    int Np[4];
+    const Dtype ydt = (y[0]->data && act_dtype(y[0]->dtype)) ? y[0]->dtype : (x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    for (int s = 0; s < n; ++s) {
+        check_w(*W[s], wdt, dname, block, op);
+        if (W[s]->cols != K) op_fail(op, "all matrices must have the same number of columns");
+        const int out = W[s]->rows;
+        const Tensor* b = bias ? bias[s] : nullptr;
+        if (b) {
+            if (b->dtype != x.dtype) op_fail(op, x.dtype == Dtype::FP16 ? "bias must be FP16" : "bias must have x's dtype");
+            if (b->rows != out || b->cols != 1) op_fail(op, "bias shape must be (out, 1)");
+        }
+        const bool keep = y[s]->rows == out && y[s]->cols == 1 && y[s]->dtype == ydt && y[s]->data;
+        if (!keep) y[s]->resize(out, 1, ydt);
+        Wp[s] = W[s]->data;
+        Yp[s] = y[s]->data;
+        Bp[s] = (b && b->size() > 0) ? b->data : nullptr;
+        Np[s] = out;
+    }
+    check_status(b200q_gemv_multi(static_cast<int>(wdt), n, Wp, Np, Yp, Bp, x.data, static_cast<int>(x.dtype), static_cast<int>(ydt), K,
+                                  cuda_current_stream(W[0]->device.index)), op);
+}
+
 void batched_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op, const Tensor& W, const Tensor* bias,
                   const Tensor& X, Tensor& Y) {
     check_w(W, wdt, dname, block, op);
@@ -215,6 +250,7 @@ B200_FMT_OPS(q8_0, B200Q_FMT_Q8_0, Dtype::Q8_0, "Q8_0", 32)
 // The registration point: what brotensor does in fill_cuda_vtable_specialised
 // (src/cuda/concat.cu:359-372) for the same nine slots.
 void fill_cuda_tables(OpsVTable& ops, AllocVTable& alloc) {
+    ops.linear_forward_group_fp16 = group_impl;
     ops.dequant_q4k_to_fp16 = dequant_q4k;
     ops.linear_forward_q4k_fp16 = gemv_q4k;
     ops.linear_forward_batched_q4k_fp16 = batched_q4k;

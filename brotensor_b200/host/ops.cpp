@@ -1,5 +1,7 @@
 // Public op wrappers: resolve the device, refuse a null slot, pin an unsized output to
 // the op's device, call the backend (brotensor src/ops.cpp:2049-2125).
+#include <stdexcept>
+
 #include "brotensor_b200/detail/dispatch.h"
 #include "brotensor_b200/ops/quant.h"
 
@@ -36,5 +38,18 @@ B200_LINEAR_OP(linear_forward_batched_q8_0_fp16)
 B200_DEQUANT_OP(dequant_q6k_to_fp16)
 B200_LINEAR_OP(linear_forward_q6k_fp16)
 B200_LINEAR_OP(linear_forward_batched_q6k_fp16)
+
+void linear_forward_group_fp16(const Tensor* const* W, const Tensor* const* bias, int n, const Tensor& x, Tensor* const* y) {
+    if (n <= 0 || !W || !y || !W[0] || !y[0]) throw std::runtime_error("brotensor: linear_forward_group_fp16: no matrices");
+    const detail::OpsVTable& v = detail::dispatch_with_opts(*W[0], {&x, y[0]});
+    const Device dev = W[0]->device;
+    if (!v.linear_forward_group_fp16) detail::throw_not_implemented("linear_forward_group_fp16", dev);
+    for (int s = 0; s < n; ++s) {
+        if (!W[s] || !y[s]) throw std::runtime_error("brotensor: linear_forward_group_fp16: null tensor");
+        if (W[s]->device != dev) throw std::runtime_error("brotensor: linear_forward_group_fp16: matrices on different devices");
+        detail::adopt_output(*y[s], dev);
+    }
+    v.linear_forward_group_fp16(W, bias, n, x, y);
+}
 
 }  // namespace brotensor_b200

@@ -71,6 +71,25 @@ def gemv(fmt, W, X, N, bias=None, out=None, out_dtype=None):
     return _linear("gemv", fmt, W, X, N, bias, out, out_dtype, None)
 
 
+def gemv_multi(fmt, Ws, x, Ns, outs=None, biases=None):
+    """Several matrices against one activation vector in one launch; returns the list of (1, N_s) results."""
+    import ctypes as C
+    n = len(Ws)
+    K = x.numel()
+    for W, N in zip(Ws, Ns):
+        _check_w(fmt, W, N, K)
+    if outs is None:
+        outs = [torch.empty((1, N), dtype=torch.float32, device=x.device) for N in Ns]
+    Wp = (C.c_void_p * n)(*[W.data_ptr() for W in Ws])
+    Yp = (C.c_void_p * n)(*[y.data_ptr() for y in outs])
+    Np = (C.c_int * n)(*Ns)
+    Bp = None if biases is None else (C.c_void_p * n)(*[(b.data_ptr() if b is not None else None) for b in biases])
+    with torch.cuda.device(x.device):
+        rc = capi.lib().b200q_gemv_multi(fmt, n, Wp, Np, Yp, Bp, x.data_ptr(), _DT[x.dtype], _DT[outs[0].dtype], K, _stream())
+    capi.check(rc)
+    return outs
+
+
 def gemm(fmt, W, X, N, bias=None, out=None, out_dtype=None, ws=None):
     """Prefill GEMM on the tensor cores, any M."""
     return _linear("gemm", fmt, W, X, N, bias, out, out_dtype, ws)

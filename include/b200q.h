@@ -79,6 +79,18 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
                int M, int N, int K, void* stream);
 
 /*
+ * Several weight matrices of one format and one K against the SAME activation
+ * vector (M = 1) in one launch: y_s(N_s) = decode(W_s(N_s,K)) * x (+ bias_s),
+ * s = 0..n-1, n <= 4. A decode GEMV launch has a fixed cost of a few
+ * microseconds; q/k/v or gate/up of a transformer layer pay it once this way.
+ * Results are bit-identical to n calls of b200q_gemv. `bias` may be NULL or
+ * hold NULL entries. brotensor issues one launch per projection
+ * (src/cuda/q4k.cu:326-362); there is no grouped form in its op table.
+ */
+int b200q_gemv_multi(int fmt, int n, const void* const* W, const int* N, void* const* Y, const void* const* bias,
+                     const void* x, int x_dtype, int y_dtype, int K, void* stream);
+
+/*
  * Row-sharded decode GEMV for one rank of a multi-GPU LM head (M = 1):
  * this rank owns rows [row_offset, row_offset + rows) of a matrix of total_rows
  * rows; W_shard is the byte range of those rows, x is replicated. The kernel

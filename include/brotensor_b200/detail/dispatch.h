@@ -14,6 +14,7 @@ namespace brotensor_b200::detail {
 
 using DequantFn = void (*)(const Tensor& W, Tensor& out);
 using LinearFn = void (*)(const Tensor& W, const Tensor* bias, const Tensor& x, Tensor& y);
+using GroupFn = void (*)(const Tensor* const* W, const Tensor* const* bias, int n, const Tensor& x, Tensor* const* y);
 
 struct OpsVTable {
     DequantFn dequant_q4k_to_fp16 = nullptr;
@@ -25,6 +26,8 @@ struct OpsVTable {
     DequantFn dequant_q6k_to_fp16 = nullptr;
     LinearFn linear_forward_q6k_fp16 = nullptr;
     LinearFn linear_forward_batched_q6k_fp16 = nullptr;
+    // Extension, not in brotensor's table: several matrices against one activation vector.
+    GroupFn linear_forward_group_fp16 = nullptr;
 };
 
 struct AllocVTable {

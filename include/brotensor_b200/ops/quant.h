@@ -29,4 +29,12 @@ void dequant_q6k_to_fp16(const Tensor& W_q6k, Tensor& W_fp16);
 void linear_forward_q6k_fp16(const Tensor& W_q6k, const Tensor* bias, const Tensor& x, Tensor& y);
 void linear_forward_batched_q6k_fp16(const Tensor& W_q6k, const Tensor* bias, const Tensor& X_BD, Tensor& Y_BD);
 
+// Extension (brotensor issues one launch per projection): n <= 4 weight matrices of ONE quant
+// dtype (Q4_K, Q6_K or Q8_0) and one `in` against the same activation vector x (in, 1) in a
+// single launch; y[s] = W[s] * x (+ bias[s]). A decode GEMV launch has a fixed cost of a few
+// microseconds, which q/k/v or gate/up of a transformer layer pay once this way. Shapes, dtypes
+// and error behaviour per matrix are those of linear_forward_q4k_fp16; results are bit-identical
+// to n separate calls. `bias` may be null or hold null entries.
+void linear_forward_group_fp16(const Tensor* const* W, const Tensor* const* bias, int n, const Tensor& x, Tensor* const* y);
+
 }  // namespace brotensor_b200

@@ -374,6 +374,44 @@ static void test_gpu_large_rows_and_views() {
     CHECK(y.device == Device::CUDA && y.data == p && y.rows == H0);
 }
 
+static void test_gpu_group_op() {
+    std::printf("test_gpu_group_op\n");
+    // three Q4_K matrices against one x in one launch == three linear_forward_q4k_fp16 calls
+    FmtCase c{"q4k", B200Q_FMT_Q4_K, Dtype::Q4_K, 256, 144, nullptr, nullptr, nullptr, nullptr};
+    const int IN = 512, outs[3] = {96, 40, 250};
+    std::vector<Tensor> W(3), yg(3), ys(3);
+    for (int i = 0; i < 3; ++i) {
+        std::vector<uint8_t> b = make_blocks(c, outs[i], IN);
+        b[7 * i] ^= 0x11;  // make the three matrices differ
+        W[i] = Tensor::from_raw_bytes_on(Device::CUDA, b.data(), outs[i], IN, Dtype::Q4_K, b.size());
+    }
+    std::vector<float> xh(IN);
+    for (int i = 0; i < IN; ++i) xh[i] = 0.01f * (float)((i * 37) % 61 - 30);
+    Tensor x = Tensor::from_host_on(Device::CUDA, xh.data(), IN, 1);
+    const Tensor* Wp[3] = {&W[0], &W[1], &W[2]};
+    Tensor* yp[3] = {&yg[0], &yg[1], &yg[2]};
+    bt::linear_forward_group_fp16(Wp, nullptr, 3, x, yp);
+    for (int i = 0; i < 3; ++i) bt::linear_forward_q4k_fp16(W[i], nullptr, x, ys[i]);
+    bt::sync_all();
+    for (int i = 0; i < 3; ++i) {
+        CHECK(yg[i].rows == outs[i] && yg[i].cols == 1 && yg[i].dtype == Dtype::FP32 && yg[i].device == Device::CUDA);
+        CHECK(yg[i].to_host_vector() == ys[i].to_host_vector());
+    }
+    // a matrix with another number of columns is refused with the op's name
+    std::vector<uint8_t> b2 = make_blocks(c, 16, 256);
+    Tensor W2 = Tensor::from_raw_bytes_on(Device::CUDA, b2.data(), 16, 256, Dtype::Q4_K, b2.size());
+    const Tensor* bad[2] = {&W[0], &W2};
+    Tensor t0, t1;
+    Tensor* yb[2] = {&t0, &t1};
+    bool threw = false;
+    try {
+        bt::linear_forward_group_fp16(bad, nullptr, 2, x, yb);
+    } catch (const std::runtime_error& e) {
+        threw = std::string(e.what()).find("brotensor: linear_forward_group_fp16:") == 0;
+    }
+    CHECK(threw);
+}
+
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "cpu";
     bt::init();
@@ -395,6 +433,7 @@ int main(int argc, char** argv) {
         };
         for (const auto& c : cases) run_fmt(c);
         test_gpu_large_rows_and_views();
+        test_gpu_group_op();
         int st = 0;
         CHECK(b200q_device_status(&st) == B200Q_OK && st == 0);
     }

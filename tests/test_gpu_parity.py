@@ -361,3 +361,36 @@ def test_gemm_cta_pair_equals_single_cta(fmt, N, K, M, cpu_oracle):
     assert oracle.rel_l2(y1.cpu().numpy(), cpu_oracle.matmul(fmt, Wh, xh, threads=8)) < 2e-3
     assert ops.device_status() == 0
 
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,K,Ns", [(synth.Q4_K, 4096, [4096, 1024, 1024]), (synth.Q4_K, 512, [100, 7, 33, 16]),
+                                      (synth.Q6_K, 2048, [256, 300]), (synth.Q8_0, 256, [48, 1000]), (synth.Q4_K, 4096, [14336, 14336])])
+def test_grouped_gemv_equals_separate_launches(fmt, K, Ns, cpu_oracle):
+    """Several matrices against one activation vector in one launch: bit-identical to one launch each."""
+    Whs = [synth.make_blocks(fmt, N, K, seed=10 + i) for i, N in enumerate(Ns)]
+    Ws = [torch.from_numpy(w).cuda() for w in Whs]
+    xh = synth.make_activations(1, K, seed=4)
+    x = torch.from_numpy(xh).cuda()
+    biases = [torch.from_numpy(synth.make_activations(1, N, seed=20 + i)).cuda().view(-1) if i % 2 == 0 else None
+              for i, N in enumerate(Ns)]
+    outs = ops.gemv_multi(fmt, Ws, x, Ns, biases=biases)
+    torch.cuda.synchronize()
+    for W, Wh, N, b, y in zip(Ws, Whs, Ns, biases, outs):
+        ref = ops.gemv(fmt, W, x, N, bias=b)
+        assert torch.equal(y, ref)
+        if N <= 4096:
+            want = cpu_oracle.matmul(fmt, Wh, xh, threads=8)
+            if b is not None:
+                want = want + b.cpu().numpy()[None, :]
+            assert oracle.rel_l2(y.cpu().numpy(), want) < 2e-3
+    assert ops.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_grouped_gemv_argument_checks():
+    fmt, K = synth.Q4_K, 256
+    W = torch.from_numpy(synth.make_blocks(fmt, 16, K, seed=1)).cuda()
+    x = torch.zeros(K, device="cuda")
+    with pytest.raises(Exception):
+        ops.gemv_multi(fmt, [W] * 5, x, [16] * 5)       # more than four matrices
