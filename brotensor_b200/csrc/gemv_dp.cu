@@ -664,10 +664,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                     }
                     const size_t o = (size_t)m * tr.N + n;
                     if (p.sh_world > 0) {
-                        // sharded output: the row goes to every rank's result vector (own included) with
-                        // plain peer stores over NVLink; which of the two vectors is this launch's parity
-                        const size_t go = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n);
-                        for (int q = 0; q < p.sh_world; ++q) p.sh_out[q][go] = s;
+                        // sharded output: into this rank's own result vector first (which of the two
+                        // vectors is this launch's parity); the CTA forwards its rows to the peers below
+                        p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
                     } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(tr.Y)[o] = s;
                     else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(tr.Y)[o] = __float2half_rn(s);
                     else static_cast<__nv_bfloat16*>(tr.Y)[o] = __float2bfloat16_rn(s);
@@ -681,6 +680,19 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         // until every rank has arrived at this one, so that on return from the kernel the
         // full result vector of this launch is complete in this rank's memory.
         asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+        // This CTA's rows are one contiguous piece of the result vector: forward it to every peer
+        // with coalesced stores (a warp writes 128 consecutive bytes per peer) instead of one
+        // 4-byte NVLink write per row and peer.
+        if (p.sh_world > 1) {
+            const size_t base = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + row_begin);
+            const float* own = p.sh_out[p.sh_rank] + base;
+            for (int i = tid; i < row_end - row_begin; i += kConsumers * 32) {
+                const float v = __ldcg(own + i);
+                for (int q = 0; q < p.sh_world; ++q)
+                    if (q != p.sh_rank) p.sh_out[q][base + i] = v;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
+        }
         if (tid == 0) {
             // Release chain with one system-scope fence on the critical path: each CTA's arrival
             // is a gpu-scope release (its rows, seen through the barrier above, come before it);
