@@ -122,18 +122,6 @@ __device__ __forceinline__ void q4k_half_to_smem(const uint4 (&blk)[9], uint32_t
         sts128(rowaddr + (((uint32_t)(c + 4 * H) ^ r7) << 4), o);
     }
 }
-// Any format straight from global memory: four chunks of eight weights through the exact scalar decode.
-template <int FMT>
-__device__ __forceinline__ void generic_half_to_smem(const uint8_t* row, int kb, int H, uint32_t rowaddr, uint32_t r7) {
-#pragma unroll 2
-    for (int c = 4 * H; c < 4 * H + 4; ++c) {
-        float w[8];
-        decode8<FMT>(row, kb * 8 + c, w);
-        uint4 o;
-        o.x = pack_h2(w[0], w[1]); o.y = pack_h2(w[2], w[3]); o.z = pack_h2(w[4], w[5]); o.w = pack_h2(w[6], w[7]);
-        sts128(rowaddr + (((uint32_t)c ^ r7) << 4), o);
-    }
-}
 // One Q8_0 block (FP16 d + 32 int8) held as the nine aligned words that cover it: an even block
 // (H = 0) starts on a word, its quants two bytes in; an odd block (H = 1) was read from two bytes
 // before its start, so d is the high half of word 0 and the quants are words 1..8. The thread
@@ -181,7 +169,6 @@ __device__ __forceinline__ void q6k_quad_to_smem(const uint32_t (&ql)[8], const 
         sts128(rowaddr + (((uint32_t)(c + 4 * H) ^ r7) << 4), make_uint4(o[0], o[1], o[2], o[3]));
     }
 }
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 template <int FMT>
 __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairParams p) {
