@@ -226,70 +226,6 @@ __device__ __forceinline__ void item_q4k(uint32_t rowA, uint32_t rowB, int gi, i
     }
 }
 
-// ---- Q4_K in units of half a group ---------------------------------------------------------
-// One 32-byte quant group of a block holds two sub-blocks (low / high nibbles, 64 elements). With
-// (block, group) as a lane's unit of work 32 lanes cover eight blocks (2048 elements), so a
-// 4096-long row is two stages instead of one: twice as many, half as large stages in the ring,
-// the first math starts after half the bytes and the last stage's math is half as long.
-// u: unit index inside the stage (block u >> 2, quant group j = u & 3); gg: 128-element group
-// along the whole row (the unit's activations are its half c2 = j & 1).
-template <int MT>
-__device__ __forceinline__ void item_q4k_half(uint32_t rowA, uint32_t rowB, int u, int gg, const XAddr& xa,
-                                              float (&acc)[2][MT]) {
-    const int b = u >> 2, j = u & 3, c2 = j & 1;
-    const uint32_t prA = rowA + (uint32_t)b * 144u, prB = rowB + (uint32_t)b * 144u;
-    const uint32_t qo = 16u + 32u * (uint32_t)j;
-    const uint4 hA = lds128(prA), hB = lds128(prB);
-    uint4 q[2][2];  // [row][half of the 32 bytes]
-    q[0][0] = lds128(prA + qo); q[0][1] = lds128(prA + qo + 16u);
-    q[1][0] = lds128(prB + qo); q[1][1] = lds128(prB + qo + 16u);
-    uint4 x[8];
-    const uint32_t xo = 128u * (uint32_t)c2;  // 64 int16 activations per quant group
-    {
-        const uint32_t xg = x_group(xa, 0, gg) + xo;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = lds128(xg + 16u * i);
-    }
-    // 6-bit scale / min of sub-blocks 2j and 2j+1
-    uint32_t sc0[2], sc1[2], m0[2], m1[2];
-    float d[2], dm[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const uint4 h = r ? hB : hA;
-        const uint32_t sclo = h.y & 0x3f3f3f3fu, schi = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
-        const uint32_t mlo = h.z & 0x3f3f3f3fu, mhi = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
-        const uint32_t scw = (j & 2) ? schi : sclo, mw = (j & 2) ? mhi : mlo;  // sub-blocks 0..3 / 4..7
-        const uint32_t sh = 16u * (uint32_t)c2;                                 // bytes 2 c2, 2 c2 + 1
-        sc0[r] = (scw >> sh) & 0xFFu; sc1[r] = (scw >> (sh + 8u)) & 0xFFu;
-        m0[r] = (mw >> sh) & 0xFFu;   m1[r] = (mw >> (sh + 8u)) & 0xFFu;
-        d[r] = h2f(h.x & 0xFFFFu);
-        dm[r] = h2f(h.x >> 16);
-    }
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        int isum[2];
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            int cl, ch;
-            q4k_dot(q[r][0], q[r][1], x, cl, ch);
-            isum[r] = (int)sc0[r] * cl + (int)sc1[r] * ch;
-        }
-        // sums of the two sub-blocks' activations, and the group's 2^-e
-        const uint2 sv = lds64(xa.sxi + (uint32_t)(m * (xa.K >> 5) + gg * 4 + 2 * c2) * 4u);
-        const float xs = __uint_as_float(lds32(xa.xsc + (uint32_t)(m * xa.groups + gg) * 4u));
-        if (m + 1 < MT) {
-            const uint32_t xg = x_group(xa, m + 1, gg) + xo;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = lds128(xg + 16u * i);
-        }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const int imin = (int)m0[r] * (int)sv.x + (int)m1[r] * (int)sv.y;
-            acc[r][m] = fmaf(xs, d[r] * (float)isum[r] - dm[r] * (float)imin, acc[r][m]);
-        }
-    }
-}
-
 template <int J>
 __device__ __forceinline__ void q8_block_words(uint32_t base, uint32_t (&w)[9]) {
     // block J of the group starts at 34*J: 4-byte aligned for even J, 2 (mod 4) for odd J
@@ -361,97 +297,6 @@ __device__ __forceinline__ void load_words(uint32_t a, uint32_t* out) {
     if constexpr (K0 < N) {
         out[K0] = lds32i<4 * K0>(a);
         load_words<N, K0 + 1>(a, out);
-    }
-}
-
-template <int MT, int H, int Q>
-__device__ __forceinline__ void q6_sub(const uint32_t (&ql)[2][16], const uint32_t (&qh)[2][8],
-                                       const uint32_t (&su)[2][2], int gg, const XAddr& xa, float (&accg)[2][MT]) {
-    // sub-block (Q, H): 16 elements at 32*Q + 16*H of the group, raw6 = nibble | two qh bits << 4
-    constexpr int SI = 2 * Q + H;  // scale byte and 16-element sum index inside the group
-    uint4 x0[MT], x1[MT];
-    int sx[MT];
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        const uint32_t xg = x_group(xa, m, gg);
-        x0[m] = x_seg<4 * Q + 2 * H>(xg);
-        x1[m] = x_seg<4 * Q + 2 * H + 1>(xg);
-        sx[m] = (int)lds32i<4 * SI>(xa.sxi + (uint32_t)(m * (xa.K >> 4) + gg * 8) * 4u);
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        uint32_t v[4];
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const uint32_t a = ql[r][4 * H + 8 * (Q & 1) + w], hb = qh[r][4 * H + w];
-            const uint32_t nib = (Q < 2 ? a : (a >> 4)) & 0x0F0F0F0Fu;
-            const uint32_t h2 = (Q == 0 ? hb << 4 : Q == 1 ? hb << 2 : Q == 2 ? hb : hb >> 2) & 0x30303030u;
-            v[w] = nib | h2;
-        }
-        const float scf = biased_s8_to_f32(su[r][SI >> 2], SI & 3);
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            int c0 = 0, c1 = 0;
-            c0 = dp2a_lo_su(x0[m].x, v[0], c0);
-            c0 = dp2a_hi_su(x0[m].y, v[0], c0);
-            c1 = dp2a_lo_su(x0[m].z, v[1], c1);
-            c1 = dp2a_hi_su(x0[m].w, v[1], c1);
-            c0 = dp2a_lo_su(x1[m].x, v[2], c0);
-            c0 = dp2a_hi_su(x1[m].y, v[2], c0);
-            c1 = dp2a_lo_su(x1[m].z, v[3], c1);
-            c1 = dp2a_hi_su(x1[m].w, v[3], c1);
-            // sum (raw6 - 32) * x = c - 32 * sum x
-            accg[r][m] = fmaf(scf, (float)(c0 + c1 - 32 * sx[m]), accg[r][m]);
-        }
-    }
-}
-
-template <int MT>
-__device__ __forceinline__ void item_q6k(uint32_t rowA, uint32_t rowB, int gi, int gg, const XAddr& xa,
-                                         float (&acc)[2][MT]) {
-    const int bi = gi >> 1, G = gi & 1;
-    // blocks are 210 bytes: odd blocks of a 16-byte aligned chunk start at 2 (mod 4). Read
-    // aligned words from 2 bytes earlier and funnel-shift; for even blocks the shift is 0.
-    const uint32_t sh = (uint32_t)(bi & 1) * 16u;
-    uint32_t rl[2][17], rh[2][9], rs[2][3], rd[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const uint32_t L = (r ? rowB : rowA) + (uint32_t)(bi * 210 - (bi & 1) * 2);
-        load_words<17>(L + 64u * G, rl[r]);
-        load_words<9>(L + 128u + 32u * G, rh[r]);
-        load_words<3>(L + 192u + 8u * G, rs[r]);
-        rd[r] = lds32i<208>(L);
-    }
-    uint32_t ql[2][16], qh[2][8], su[2][2];
-    float d[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-#pragma unroll
-        for (int k = 0; k < 16; ++k) ql[r][k] = __funnelshift_r(rl[r][k], rl[r][k + 1], sh);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) qh[r][k] = __funnelshift_r(rh[r][k], rh[r][k + 1], sh);
-        su[r][0] = __funnelshift_r(rs[r][0], rs[r][1], sh) ^ 0x80808080u;
-        su[r][1] = __funnelshift_r(rs[r][1], rs[r][2], sh) ^ 0x80808080u;
-        d[r] = h2f((rd[r] >> sh) & 0xFFFFu);
-    }
-    float accg[2][MT];
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int m = 0; m < MT; ++m) accg[r][m] = 0.f;
-    q6_sub<MT, 0, 0>(ql, qh, su, gg, xa, accg);
-    q6_sub<MT, 0, 1>(ql, qh, su, gg, xa, accg);
-    q6_sub<MT, 0, 2>(ql, qh, su, gg, xa, accg);
-    q6_sub<MT, 0, 3>(ql, qh, su, gg, xa, accg);
-    q6_sub<MT, 1, 0>(ql, qh, su, gg, xa, accg);
-    q6_sub<MT, 1, 1>(ql, qh, su, gg, xa, accg);
-    q6_sub<MT, 1, 2>(ql, qh, su, gg, xa, accg);
-    q6_sub<MT, 1, 3>(ql, qh, su, gg, xa, accg);
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-        const float xs = __uint_as_float(lds32i<0>(xa.xsc + (uint32_t)(m * xa.groups + gg) * 4u));
-#pragma unroll
-        for (int r = 0; r < 2; ++r) acc[r][m] = fmaf(d[r] * xs, accg[r][m], acc[r][m]);
     }
 }
 
@@ -690,16 +535,15 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
 #pragma unroll
                         for (int pi = 0; pi < RP; ++pi) item_q6k_half<MT>(rowA[pi], rowB[pi], gi, lane >> 4, g0 + gi, xa, acc[pi]);
                     }
-                } else if constexpr (FMT == kQ4_K) {
-                    // half-group units: two per 128-element group
-                    for (int u = lane; u < 2 * ng; u += 32) {
-#pragma unroll
-                        for (int pi = 0; pi < RP; ++pi) item_q4k_half<MT>(rowA[pi], rowB[pi], u, g0 + (u >> 1), xa, acc[pi]);
-                    }
                 } else {
+                    // (half-group units were measured for Q4_K as well: its items are cheap enough that
+                    // the second header decode per group costs more than the finer stages give back)
                     for (int gi = lane; gi < ng; gi += 32) {
 #pragma unroll
-                        for (int pi = 0; pi < RP; ++pi) item_q8_0<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                        for (int pi = 0; pi < RP; ++pi) {
+                            if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                            else item_q8_0<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                        }
                     }
                 }
             }
@@ -833,7 +677,7 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
     int want = stream_get_option(0);
     want = want < 2 ? 2 : (want > kMaxStages ? kMaxStages : want);
     int best = 0;
-    constexpr int glanes = FMT == kQ8_0 ? 32 : 16;  // groups that keep a warp's 32 lanes busy (Q4_K, Q6_K: half-group units)
+    constexpr int glanes = FMT == kQ6_K ? 16 : 32;  // groups that keep a warp's 32 lanes busy (Q6_K: half-group units)
     for (int sc = 1; sc <= cpr; ++sc) {
         const int groups = sc * gpc;
         if (groups % glanes != 0 && sc != cpr && groups < glanes) continue;
