@@ -123,8 +123,8 @@ __device__ __forceinline__ void q4k_half_to_smem(const uint4 (&blk)[9], uint32_t
     }
 }
 // One Q8_0 block (FP16 d + 32 int8) held as the nine aligned words that cover it: an even block
-// (H = 0) starts on a word, its quants two bytes in; an odd block (H = 1) was read from two bytes
-// before its start, so d is the high half of word 0 and the quants are words 1..8. The thread
+// (H = 0) starts on word 0, its quants two bytes in; an odd block (H = 1) starts two bytes into
+// word 0, so d is the high half of word 0 and the quants are words 1..8. The thread
 // writes its 32 weights as 16-byte chunks 4H .. 4H+3 of the row: d * q is exact in FP32, one rounding.
 __device__ __forceinline__ void q8_0_half_to_smem(const uint32_t (&w)[9], uint32_t rowaddr, uint32_t r7, int H) {
     const float d = h2f(H ? (w[0] >> 16) : (w[0] & 0xFFFFu));
@@ -308,13 +308,18 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
 #pragma unroll
             for (int i = 0; i < 9; ++i) nxt[i] = __ldg(reinterpret_cast<const uint4*>(rowp) + i);
         }
-        // Q8_0: the thread's block of the next stage (nine aligned words), loaded one stage ahead
-        uint32_t w8[9], w8n[9];
-        const uint8_t* q8p = rowp + 34 * H - 2 * H;  // block 2 kb + H of the row, from a word boundary
-        if constexpr (FMT == kQ8_0) {
+        // Q8_0: eight blocks (256 k, 272 bytes = 17 x 16) form a 16-byte aligned chunk. The thread's
+        // block of stage P = kb & 3 is block 2P + H of the chunk: it lies inside the three 16-byte
+        // words 4P + 2H .. +2, starting at byte 4P + 2H of them. They are loaded one stage ahead.
+        uint4 c8[3], c8n[3];
+        auto q8_load = [&](int kbb, uint4 (&dst)[3]) {
+            const uint4* src = reinterpret_cast<const uint4*>(rowp + (size_t)(kbb >> 2) * 272) + 4 * (kbb & 3) + 2 * H;
 #pragma unroll
-            for (int i = 0; i < 9; ++i) w8n[i] = __ldg(reinterpret_cast<const uint32_t*>(q8p) + i);
-        }
+            for (int i = 0; i < 3; ++i) dst[i] = __ldg(src + i);
+        };
+#pragma unroll
+        for (int i = 0; i < 3; ++i) c8[i] = c8n[i] = make_uint4(0, 0, 0, 0);
+        if constexpr (FMT == kQ8_0) q8_load(0, c8n);
         // Q6_K: the thread's quad of the next stage - nine aligned words each of nibble and high-bit
         // bytes (blocks are 210 bytes, so odd blocks start two bytes past a word: funnel shift), its
         // two scales and d - loaded one stage ahead
@@ -346,11 +351,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
             }
             if constexpr (FMT == kQ8_0) {
 #pragma unroll
-                for (int i = 0; i < 9; ++i) w8[i] = w8n[i];
-                if (kb + 1 < n_kb) {
-#pragma unroll
-                    for (int i = 0; i < 9; ++i) w8n[i] = __ldg(reinterpret_cast<const uint32_t*>(q8p + (size_t)(kb + 1) * 68) + i);
-                }
+                for (int i = 0; i < 3; ++i) c8[i] = c8n[i];
+                if (kb + 1 < n_kb) q8_load(kb + 1, c8n);
             }
             if constexpr (FMT == kQ4_K) {
                 if ((kb & 3) == 0) {
@@ -377,7 +379,17 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                         default: q4k_half_to_smem<3>(cur, rowaddr, r7, H); break;
                     }
                 } else if constexpr (FMT == kQ8_0) {
-                    q8_0_half_to_smem(w8, rowaddr, r7, H);
+                    const uint32_t w12[12] = {c8[0].x, c8[0].y, c8[0].z, c8[0].w, c8[1].x, c8[1].y, c8[1].z, c8[1].w,
+                                              c8[2].x, c8[2].y, c8[2].z, c8[2].w};
+                    // the block starts in word P of the twelve: on it for H = 0, two bytes into it for H = 1
+                    uint32_t w9[9];
+                    switch (kb & 3) {
+                        case 0: for (int i = 0; i < 9; ++i) w9[i] = w12[i]; break;
+                        case 1: for (int i = 0; i < 9; ++i) w9[i] = w12[1 + i]; break;
+                        case 2: for (int i = 0; i < 9; ++i) w9[i] = w12[2 + i]; break;
+                        default: for (int i = 0; i < 9; ++i) w9[i] = w12[3 + i]; break;
+                    }
+                    q8_0_half_to_smem(w9, rowaddr, r7, H);
                 } else {
                     uint32_t ql[8], qh[8];
 #pragma unroll
