@@ -320,32 +320,32 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
 #pragma unroll
         for (int i = 0; i < 3; ++i) c8[i] = c8n[i] = make_uint4(0, 0, 0, 0);
         if constexpr (FMT == kQ8_0) q8_load(0, c8n);
-        // Q6_K: the thread's quad of the next stage - nine aligned words each of nibble and high-bit
-        // bytes (blocks are 210 bytes, so odd blocks start two bytes past a word: funnel shift), its
-        // two scales and d - loaded one stage ahead
-        uint32_t l6[9], h6[9], s6 = 0, d6 = 0, f6 = 0, l6n[9], h6n[9], s6n = 0, d6n = 0, f6n = 0;
-        auto q6_load = [&](int kbb, uint32_t (&L)[9], uint32_t (&Hh)[9], uint32_t& S, uint32_t& D, uint32_t& F) {
+        // Q6_K: the thread's quad of the next stage, loaded one stage ahead. Blocks are 210 bytes and
+        // only 2-byte aligned: the 32 nibble bytes and the 32 high-bit bytes the quad needs are read
+        // as three 16-byte words each from the 16-byte boundary at or before the block (both
+        // regions start on a multiple of 32 bytes inside the block, so 48 bytes from the boundary
+        // cover them for any alignment); `f6` keeps the block's byte offset from that boundary.
+        uint4 l6[3], h6[3], l6n[3], h6n[3];
+        uint32_t s6 = 0, d6 = 0, f6 = 0, s6n = 0, d6n = 0, f6n = 0;
+        auto q6_load = [&](int kbb, uint4 (&L)[3], uint4 (&Hh)[3], uint32_t& S, uint32_t& D, uint32_t& F) {
             const int blk = kbb >> 2, P = kbb & 3, grp = P >> 1, quad = 2 * (P & 1) + H;
             const uint8_t* b0 = rowp + (size_t)blk * 210;
-            // blocks and rows are only 2-byte aligned (210 bytes; a row of an odd number of blocks):
-            // read from the word boundary at or before the block and shift by what was skipped
-            const uint32_t skip = (uint32_t)(reinterpret_cast<uintptr_t>(b0) & 2u);
-            F = skip * 8u;
-            const uint8_t* al = b0 - skip;
-            const uint32_t* pl = reinterpret_cast<const uint32_t*>(al + grp * 64 + H * 32);
-            const uint32_t* ph = reinterpret_cast<const uint32_t*>(al + 128 + grp * 32);
+            F = (uint32_t)(reinterpret_cast<uintptr_t>(b0) & 15u);
+            const uint4* al = reinterpret_cast<const uint4*>(b0 - F);
 #pragma unroll
-            for (int i = 0; i < 9; ++i) L[i] = __ldg(pl + i);
+            for (int i = 0; i < 3; ++i) L[i] = __ldg(al + 4 * grp + 2 * H + i);
 #pragma unroll
-            for (int i = 0; i < 9; ++i) Hh[i] = __ldg(ph + i);
+            for (int i = 0; i < 3; ++i) Hh[i] = __ldg(al + 8 + 2 * grp + i);
             S = __ldg(reinterpret_cast<const unsigned short*>(b0 + 192 + grp * 8 + quad * 2));
             D = __ldg(reinterpret_cast<const unsigned short*>(b0 + 208));
         };
+#pragma unroll
+        for (int i = 0; i < 3; ++i) l6[i] = h6[i] = l6n[i] = h6n[i] = make_uint4(0, 0, 0, 0);
         if constexpr (FMT == kQ6_K) q6_load(0, l6n, h6n, s6n, d6n, f6n);
         for (int kb = 0; kb < n_kb; ++kb) {
             if constexpr (FMT == kQ6_K) {
 #pragma unroll
-                for (int i = 0; i < 9; ++i) { l6[i] = l6n[i]; h6[i] = h6n[i]; }
+                for (int i = 0; i < 3; ++i) { l6[i] = l6n[i]; h6[i] = h6n[i]; }
                 s6 = s6n; d6 = d6n; f6 = f6n;
                 if (kb + 1 < n_kb) q6_load(kb + 1, l6n, h6n, s6n, d6n, f6n);
             }
@@ -391,11 +391,19 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                     }
                     q8_0_half_to_smem(w9, rowaddr, r7, H);
                 } else {
+                    const uint32_t wl[12] = {l6[0].x, l6[0].y, l6[0].z, l6[0].w, l6[1].x, l6[1].y, l6[1].z, l6[1].w,
+                                             l6[2].x, l6[2].y, l6[2].z, l6[2].w};
+                    const uint32_t wh[12] = {h6[0].x, h6[0].y, h6[0].z, h6[0].w, h6[1].x, h6[1].y, h6[1].z, h6[1].w,
+                                             h6[2].x, h6[2].y, h6[2].z, h6[2].w};
+                    // the data starts f6 bytes (even, 0..14) into the twelve words: whole words by the
+                    // switch (the same for every lane when rows are a multiple of 16 bytes), two bytes by the shift
+                    const uint32_t bits = (f6 & 2u) * 8u;
                     uint32_t ql[8], qh[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        ql[i] = __funnelshift_r(l6[i], l6[i + 1], f6);
-                        qh[i] = __funnelshift_r(h6[i], h6[i + 1], f6);
+                    switch (f6 >> 2) {
+                        case 0: for (int i = 0; i < 8; ++i) { ql[i] = __funnelshift_r(wl[i], wl[i + 1], bits); qh[i] = __funnelshift_r(wh[i], wh[i + 1], bits); } break;
+                        case 1: for (int i = 0; i < 8; ++i) { ql[i] = __funnelshift_r(wl[1 + i], wl[2 + i], bits); qh[i] = __funnelshift_r(wh[1 + i], wh[2 + i], bits); } break;
+                        case 2: for (int i = 0; i < 8; ++i) { ql[i] = __funnelshift_r(wl[2 + i], wl[3 + i], bits); qh[i] = __funnelshift_r(wh[2 + i], wh[3 + i], bits); } break;
+                        default: for (int i = 0; i < 8; ++i) { ql[i] = __funnelshift_r(wl[3 + i], wl[4 + i], bits); qh[i] = __funnelshift_r(wh[3 + i], wh[4 + i], bits); } break;
                     }
                     q6k_quad_to_smem(ql, qh, s6, d6, 2 * (kb & 1) + H, rowaddr, r7, H);
                 }
