@@ -174,6 +174,23 @@ def _fused_head(fmt, rows, K, row0, N, rank, world, Ws, x, stream, n_launch, ref
         return {"error": repr(ex)}
 
 
+def dequant_case(fmt, N, K, stream, peak_gbs, R=6, n_launch=12):
+    """Decode to FP16 (the reference's dequant_*_to_fp16): bytes = packed read + FP16 written."""
+    from . import _capi
+    W = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=2)).cuda()
+    outs = [torch.empty((N, K), dtype=torch.float16, device="cuda") for _ in range(R)]  # R x 32 MiB > L2
+
+    def run(i):
+        _capi.check(_capi.lib().b200q_dequant(fmt, W.data_ptr(), outs[i % R].data_ptr(), 1, N, K, torch.cuda.current_stream().cuda_stream))
+
+    for i in range(3):
+        run(i)
+    med, mn = _time_graph(run, n_launch, stream)
+    nbytes = synth.packed_bytes(fmt, N, K) + 2 * N * K
+    gbs = nbytes / (med * 1e-3) / 1e9
+    return {"fmt": synth.FMT_NAME[fmt], "N": N, "K": K, "us": med * 1e3, "GBps_read_plus_written": gbs, "frac_of_hbm_peak": gbs / peak_gbs}
+
+
 def grouped_layer_set(stream, peak_gbs, R=8, n_steps=24):
     """The decode layer set with the GEMVs that share an activation vector fused into one launch
     each (b200q_gemv_multi): [q, k, v], o, [gate, up], down - four launches instead of seven."""
@@ -220,5 +237,6 @@ def run(rank, world, peaks, stream):
                                           for dt in (torch.float32, torch.bfloat16)]
         out["prefill_other_formats_512"] = [gemm_case(f, 14336, 4096, 512, torch.float32, stream, peaks) for f in (synth.Q6_K, synth.Q8_0)]
         out["layer_set_grouped"] = grouped_layer_set(stream, peaks["hbm_gbs"])
+        out["dequant_to_fp16_4096x4096"] = [dequant_case(f, 4096, 4096, stream, peaks["hbm_gbs"]) for f in (synth.Q4_K, synth.Q6_K, synth.Q8_0)]
     out["lm_head"] = lm_head_case(rank, world, stream, peaks["hbm_gbs"])
     return out
