@@ -389,6 +389,64 @@ __device__ __forceinline__ void item_q6k_half(uint32_t rowA, uint32_t rowB, int 
     }
 }
 
+// Sharded epilogue, run by all `nthreads` consumer threads of a CTA (thread ids 0 .. nthreads-1) after
+// they have stored the CTA's rows [row_begin, row_end) into this rank's result vector.
+__device__ __forceinline__ void shard_publish(const StreamParams& p, int row_begin, int row_end, unsigned int sh_epoch,
+                                              unsigned int sh_buf, int tid, int nthreads) {
+    // Every consumer warp gets here (aborted ones too). When the whole grid has stored its
+    // rows, the last CTA publishes this rank's arrival to all ranks and waits - bounded -
+    // until every rank has arrived at this one, so that on return from the kernel the
+    // full result vector of this launch is complete in this rank's memory.
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    // This CTA's rows are one contiguous piece of the result vector: forward it to every peer
+    // with coalesced stores (a warp writes 128 consecutive bytes per peer) instead of one
+    // 4-byte NVLink write per row and peer.
+    if (p.sh_world > 1) {
+        const size_t base = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + row_begin);
+        const float* own = p.sh_out[p.sh_rank] + base;
+        for (int i = tid; i < row_end - row_begin; i += nthreads) {
+            const float v = __ldcg(own + i);
+            for (int q = 0; q < p.sh_world; ++q)
+                if (q != p.sh_rank) p.sh_out[q][base + i] = v;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    }
+    if (tid == 0) {
+        // Release chain with one system-scope fence on the critical path: each CTA's arrival
+        // is a gpu-scope release (its rows, seen through the barrier above, come before it);
+        // the last CTA acquires those, then one system-scope fence orders the whole grid's
+        // peer stores before the arrival words (release cumulativity).
+        unsigned int done;
+        asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
+        if (done == gridDim.x - 1) {
+            asm volatile("fence.acq_rel.gpu;" ::: "memory");
+            p.sh_state[0] = 0;
+            const unsigned int epoch = sh_epoch + 1u;
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+            for (int q = 0; q < p.sh_world; ++q)
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[q] + p.sh_rank), "r"(epoch) : "memory");
+            const uint64_t t0 = global_timer_ns();
+            bool ok = true;
+            for (int q = 0; q < p.sh_world && ok; ++q) {
+                for (;;) {
+                    unsigned int v;
+                    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
+                    if ((int)(v - epoch) >= 0) break;
+                    if (global_timer_ns() - t0 > 1000000000ull) {  // one second: a peer never arrived
+                        if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
+                        ok = false;
+                        break;
+                    }
+                }
+            }
+            // acquire side for the peers' rows (they sit in this GPU's L2 already: a peer's rows
+            // are performed before its arrival word); needed only when there are peers
+            if (p.sh_world > 1) asm volatile("fence.acq_rel.sys;" ::: "memory");
+            *(volatile unsigned int*)&p.sh_state[1] = epoch;
+        }
+    }
+}
+
 // NG independent pipelines inside one CTA: pipeline g has eight consumer warps, its own
 // producer warp, its own ring of p.n_stages stages and its own barriers, and works on
 // the row tiles t with t % NG == g. The pipelines share only the staged activations,
@@ -419,7 +477,11 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     constexpr int TR = kTileRows * RP;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;  // shared-space address
-    __shared__ uint64_t bar_full[NG][kMaxStages];
+    // With p.split_full, one full barrier per consumer warp and stage: a warp's rows complete on
+    // their own barrier, so it starts on them as soon as they have landed instead of when the whole
+    // tile has. That shortens what a launch cannot overlap - the wait for the first tile and the work
+    // after the last. Otherwise one barrier per stage (long Q6_K streams, where the split gains nothing).
+    __shared__ uint64_t bar_full[NG][kMaxStages][kConsumerWarps];
     __shared__ uint64_t bar_empty[NG][kMaxStages];
     __shared__ int abort_flag;
 
@@ -434,14 +496,15 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     const int n_tiles = (row_end - row_begin + TR - 1) / TR;
     const int stage_bytes = TR * p.row_stride;
 
-    if (tid == 0) {
-        abort_flag = 0;
-        for (int g = 0; g < NG; ++g)
-            for (int s = 0; s < p.n_stages; ++s) {
-                mbar_init(smem_u32(&bar_full[g][s]), 1);
-                mbar_init(smem_u32(&bar_empty[g][s]), kConsumerWarps);
-            }
-        fence_mbar_init();
+    if (tid == 0) abort_flag = 0;
+    if (tid < NG * kMaxStages * (kConsumerWarps + 1)) {  // one barrier per thread
+        const int g = tid / (kMaxStages * (kConsumerWarps + 1));
+        const int s = (tid / (kConsumerWarps + 1)) % kMaxStages, j = tid % (kConsumerWarps + 1);
+        if (s < p.n_stages) {
+            if (j < kConsumerWarps) mbar_init(smem_u32(&bar_full[g][s][j]), 1);
+            else mbar_init(smem_u32(&bar_empty[g][s]), kConsumerWarps);
+            fence_mbar_init();
+        }
     }
     __syncthreads();
     grid_dep_launch();
@@ -463,12 +526,20 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 const int c0 = slice * p.slice_chunks;
                 const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
                 const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
-                const uint32_t full = smem_u32(&bar_full[g][slot]);
-                if (lane == 0) mbar_arrive_expect_tx(full, bytes * (uint32_t)nrows);
+                const uint32_t full = smem_u32(&bar_full[g][slot][0]);
+                if (!p.split_full) {
+                    if (lane == 0) mbar_arrive_expect_tx(full, bytes * (uint32_t)nrows);
+                } else if (lane < kConsumerWarps) {
+                    // rows of consumer warp `lane` in this tile: its pair, and with 32-row tiles a second pair
+                    int cnt = min(max(nrows - 2 * lane, 0), 2);
+                    if (RP == 2) cnt += min(max(nrows - 2 * (lane + kConsumerWarps), 0), 2);
+                    mbar_arrive_expect_tx(full + 8u * lane, bytes * (uint32_t)cnt);  // no rows: a plain arrival
+                }
                 __syncwarp();
                 if (lane < nrows) {
                     const uint8_t* src = tr.W + (size_t)(row0 + lane) * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
-                    bulk_g2s(ring + slot * stage_bytes + lane * p.row_stride, src, bytes, full);
+                    bulk_g2s(ring + slot * stage_bytes + lane * p.row_stride, src, bytes,
+                             p.split_full ? full + 8u * ((lane >> 1) & (kConsumerWarps - 1)) : full);
                 }
                 if (++slot == p.n_stages) {
                     slot = 0;
@@ -511,7 +582,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         for (int slice = 0; slice < p.n_slices; ++slice) {
             if (live) {
                 // keep the decision warp-uniform
-                const bool ok = wait_or_abort(smem_u32(&bar_full[g][slot]), phase, &abort_flag, p.status, kDevTimeoutFull);
+                const bool ok = wait_or_abort(smem_u32(&bar_full[g][slot][p.split_full ? wl : 0]), phase, &abort_flag, p.status, kDevTimeoutFull);
                 live = __all_sync(0xffffffffu, ok);
             }
             if (live && 2 * wl < nrows) {
@@ -585,69 +656,172 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
             }
         }
     }
-    if (p.sh_world > 0) {
-        // Every consumer warp gets here (aborted ones too). When the whole grid has stored its
-        // rows, the last CTA publishes this rank's arrival to all ranks and waits - bounded -
-        // until every rank has arrived at this one, so that on return from the kernel the
-        // full result vector of this launch is complete in this rank's memory.
-        asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
-        // This CTA's rows are one contiguous piece of the result vector: forward it to every peer
-        // with coalesced stores (a warp writes 128 consecutive bytes per peer) instead of one
-        // 4-byte NVLink write per row and peer.
-        if (p.sh_world > 1) {
-            const size_t base = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + row_begin);
-            const float* own = p.sh_out[p.sh_rank] + base;
-            for (int i = tid; i < row_end - row_begin; i += kConsumers * 32) {
-                const float v = __ldcg(own + i);
-                for (int q = 0; q < p.sh_world; ++q)
-                    if (q != p.sh_rank) p.sh_out[q][base + i] = v;
+    if (p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32);
+}
+
+// ---- self-feeding form ---------------------------------------------------------------
+// Every warp is its own pipeline: it owns a private ring of p.n_stages slots, each holding one
+// slice of one row pair, and one full barrier per slot. Lane 0 issues the bulk copies of the
+// warp's first slots before anything else (weights do not depend on the stream-ordered
+// predecessor), and refills a slot right after the warp has finished with it. There are no
+// producer warps, no empty barriers and no coupling between warps, so a warp starts on its rows
+// as soon as they have landed and its next rows are requested the moment their slot is free.
+// What a launch cannot overlap shrinks to one DRAM round trip at the start and one row pair's
+// arithmetic at the end. The CTA's row pairs go round-robin over its warps.
+constexpr int kSelfWarpsMax = 16;
+
+template <int FMT, int MT>
+__global__ void __launch_bounds__(kSelfWarpsMax * 32, 1) gemv_dpw_kernel(const StreamParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;  // shared-space address
+    __shared__ uint64_t bar_full[kSelfWarpsMax][kMaxStages];
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nthreads = blockDim.x, nwarps = nthreads >> 5;
+    const int G = gridDim.x;
+    // virtual rows of the launch: the matrix's rows, or with several matrices their tile-padded concatenation
+    const int vrows = p.n_seg > 1 ? kTileRows * p.seg_tile0[p.n_seg] : p.N;
+    const int vpairs = (vrows + 1) >> 1;
+    const int pair_begin = (int)((long long)vpairs * blockIdx.x / G);
+    const int pair_end = (int)((long long)vpairs * (blockIdx.x + 1) / G);
+    const int row_begin = 2 * pair_begin, row_end = min(vrows, 2 * pair_end);
+    const int cta_pairs = pair_end - pair_begin;
+    const int my_pairs = cta_pairs > warp ? (cta_pairs - warp + nwarps - 1) / nwarps : 0;
+    const int n_steps = my_pairs * p.n_slices;
+    const int slot_bytes = 2 * p.row_stride;
+    const uint32_t ring = sbase + (uint32_t)(p.off_stage + warp * p.n_stages * slot_bytes);
+    const uint32_t bar0 = smem_u32(&bar_full[warp][0]);
+
+    // lane 0: request slice `slice` of this warp's pair number `it` into slot `slot`
+    auto issue = [&](int it, int slice, int slot) {
+        const TileRef tr = tile_ref(p, 2 * (pair_begin + warp + it * nwarps));
+        const int cnt = min(max(tr.N - tr.row0, 0), 2);  // rows of the pair that exist (0: padding between matrices)
+        const int c0 = slice * p.slice_chunks;
+        const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
+        const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
+        const uint32_t full = bar0 + 8u * (uint32_t)slot;
+        const uint32_t dst = ring + (uint32_t)(slot * slot_bytes);
+        const uint8_t* src = tr.W + (size_t)tr.row0 * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
+        mbar_arrive_expect_tx(full, bytes * (uint32_t)cnt);  // no rows: a plain arrival
+        if (cnt > 0) bulk_g2s(dst, src, bytes, full);
+        if (cnt > 1) bulk_g2s(dst + (uint32_t)p.row_stride, src + p.row_bytes, bytes, full);
+    };
+    // the next step to request, kept as (pair, slice, slot) so that a refill costs no division
+    int iss_it = 0, iss_slice = 0, iss_slot = 0, iss_k = 0;
+    auto issue_next = [&]() {
+        if (lane == 0) issue(iss_it, iss_slice, iss_slot);
+        ++iss_k;
+        if (++iss_slice == p.n_slices) { iss_slice = 0; ++iss_it; }
+        if (++iss_slot == p.n_stages) iss_slot = 0;
+    };
+
+    if (tid == 0) abort_flag = 0;
+    if (lane == 0) {
+        for (int s = 0; s < p.n_stages; ++s) mbar_init(bar0 + 8u * (uint32_t)s, 1);
+        fence_mbar_init();
+    }
+    for (int k = 0, first = min(n_steps, p.n_stages); k < first; ++k) issue_next();
+    grid_dep_launch();
+    grid_dep_wait();  // activations (and Y) belong to the stream-ordered predecessor
+    // launch counter of the sharded form: stable while this launch runs (only its last CTA bumps it)
+    const unsigned int sh_epoch = p.sh_world > 0 ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
+    const unsigned int sh_buf = (sh_epoch + 1u) & 1u;
+    if (p.x_dtype == B200Q_DT_F32) stage_x16<FMT, float>(p, sbase, tid, nthreads);
+    else if (p.x_dtype == B200Q_DT_F16) stage_x16<FMT, __half>(p, sbase, tid, nthreads);
+    else stage_x16<FMT, __nv_bfloat16>(p, sbase, tid, nthreads);
+    __syncthreads();
+
+    const XAddr xa = {sbase + (uint32_t)p.off_xhi, sbase + (uint32_t)p.off_xlo, sbase + (uint32_t)p.off_sxhi, p.K >> 7, p.K};
+    constexpr int kGroupsPerChunk = Chunk<FMT>::elems / 128;
+    bool live = true;
+    int slot = 0, k = 0;
+    uint32_t phase = 0;
+    float acc[2][MT];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+
+    for (int it = 0; it < my_pairs; ++it) {
+        const TileRef tr = tile_ref(p, 2 * (pair_begin + warp + it * nwarps));
+        const int cnt = min(max(tr.N - tr.row0, 0), 2);
+        for (int slice = 0; slice < p.n_slices; ++slice, ++k) {
+            if (live) {
+                // keep the decision warp-uniform
+                const bool ok = wait_or_abort(bar0 + 8u * (uint32_t)slot, phase, &abort_flag, p.status, kDevTimeoutFull);
+                live = __all_sync(0xffffffffu, ok);
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
-        }
-        if (tid == 0) {
-            // Release chain with one system-scope fence on the critical path: each CTA's arrival
-            // is a gpu-scope release (its rows, seen through the barrier above, come before it);
-            // the last CTA acquires those, then one system-scope fence orders the whole grid's
-            // peer stores before the arrival words (release cumulativity).
-            unsigned int done;
-            asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
-            if (done == gridDim.x - 1) {
-                asm volatile("fence.acq_rel.gpu;" ::: "memory");
-                p.sh_state[0] = 0;
-                const unsigned int epoch = sh_epoch + 1u;
-                asm volatile("fence.acq_rel.sys;" ::: "memory");
-                for (int q = 0; q < p.sh_world; ++q)
-                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[q] + p.sh_rank), "r"(epoch) : "memory");
-                const uint64_t t0 = global_timer_ns();
-                bool ok = true;
-                for (int q = 0; q < p.sh_world && ok; ++q) {
-                    for (;;) {
-                        unsigned int v;
-                        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
-                        if ((int)(v - epoch) >= 0) break;
-                        if (global_timer_ns() - t0 > 1000000000ull) {  // one second: a peer never arrived
-                            if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
-                            ok = false;
-                            break;
-                        }
+            if (live && cnt > 0) {
+                const int c0 = slice * p.slice_chunks;
+                const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
+                const int ng = nch * kGroupsPerChunk, g0 = c0 * kGroupsPerChunk;
+                // a pair with one row (odd row count) reuses it as the second row; that sum is dropped
+                const uint32_t rowA = ring + (uint32_t)(slot * slot_bytes);
+                const uint32_t rowB = cnt > 1 ? rowA + (uint32_t)p.row_stride : rowA;
+                if constexpr (FMT == kQ6_K) {
+                    // half-group units: lanes 0..15 take H = 0 of sixteen groups, lanes 16..31 H = 1
+                    for (int gi = (lane & 15); gi < ng; gi += 16) item_q6k_half<MT>(rowA, rowB, gi, lane >> 4, g0 + gi, xa, acc);
+                } else {
+                    for (int gi = lane; gi < ng; gi += 32) {
+                        if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
+                        else item_q8_0<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
                     }
                 }
-                // acquire side for the peers' rows (they sit in this GPU's L2 already: a peer's rows
-                // are performed before its arrival word); needed only when there are peers
-                if (p.sh_world > 1) asm volatile("fence.acq_rel.sys;" ::: "memory");
-                *(volatile unsigned int*)&p.sh_state[1] = epoch;
+            }
+            __syncwarp();  // every lane has read its part of the slot
+            // The lanes' reads of the slot are ordered before the refill by the warp barrier above and
+            // program order in lane 0, like a consumer-release / producer-acquire pair on an mbarrier.
+            if (live && iss_k < n_steps) issue_next();
+            if (++slot == p.n_stages) {
+                slot = 0;
+                phase ^= 1;
+            }
+        }
+        // the rows' partial sums live in this warp's lanes: lanes 0..15 finish the first
+        // row of the pair, lanes 16..31 the second (five shuffles for both), then write
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const bool up = lane >= 16;
+            float s = (up ? acc[1][m] : acc[0][m]) + __shfl_xor_sync(0xffffffffu, up ? acc[0][m] : acc[1][m], 16);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            acc[0][m] = acc[1][m] = 0.f;
+            const int rr = up ? 1 : 0;
+            if ((lane & 15) == 0 && rr < cnt && m < p.M && live && !*(volatile int*)&abort_flag) {
+                const int n = tr.row0 + rr;
+                if (tr.bias) {
+                    if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(tr.bias)[n];
+                    else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(tr.bias)[n]);
+                    else s += __bfloat162float(static_cast<const __nv_bfloat16*>(tr.bias)[n]);
+                }
+                const size_t o = (size_t)m * tr.N + n;
+                if (p.sh_world > 0) {
+                    // sharded output: into this rank's own result vector first (which of the two
+                    // vectors is this launch's parity); the CTA forwards its rows to the peers below
+                    p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
+                } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(tr.Y)[o] = s;
+                else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(tr.Y)[o] = __float2half_rn(s);
+                else static_cast<__nv_bfloat16*>(tr.Y)[o] = __float2bfloat16_rn(s);
             }
         }
     }
+    if (p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, nthreads);
 }
 
 // ---- host side ------------------------------------------------------------------------
 
 static int g_opt_groups = 2;
+// Q6_K: per-warp full barriers pay while the first and last stage are a visible part of a
+// pipeline's stream; beyond this many stages per pipeline one barrier per stage is as fast or faster.
+constexpr int kSplitFullMaxStages = 16;
 // 0: by shape; 1: 16-row tiles; 2: prefer one pipeline with two row pairs per warp (32-row tiles)
 static int g_opt_tile_pairs = 0;
 void dp_set_tile_pairs(int v) { g_opt_tile_pairs = v == 2 ? 2 : (v == 1 ? 1 : 0); }
 int dp_get_tile_pairs() { return g_opt_tile_pairs; }
+// -1: by stream length; 0: one full barrier per stage; 1: one per consumer warp and stage
+static int g_opt_split_full = -1;
+void dp_set_split_full(int v) { g_opt_split_full = v < 0 ? -1 : (v ? 1 : 0); }
 void dp_set_groups(int v) { g_opt_groups = v < 1 ? 1 : (v > 2 ? 2 : v); }
 int dp_get_groups() { return g_opt_groups; }
 
@@ -726,6 +900,11 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
     const int stages_seen = ((tiles + ng - 1) / ng) * p.n_slices;
     if (ns > stages_seen) ns = stages_seen < 1 ? 1 : stages_seen;
     p.n_stages = ns;
+    // measured on B200: Q4_K and Q8_0 gain at every stream length (14336 x 4096 Q4_K 8.75 -> 8.0 us,
+    // 128256 x 4096 48.5 -> 46.5 us); Q6_K gains on short whole-row streams only
+    p.split_full = g_opt_split_full >= 0 ? g_opt_split_full
+                   : FMT != kQ6_K        ? 1
+                                         : (p.n_slices == 1 && stages_seen <= kSplitFullMaxStages ? 1 : 0);
     smem = off + (size_t)ns * ng * sb + 128;
     return true;
 }
@@ -737,7 +916,7 @@ static int launch_dp_k(const StreamParams& p, int grid, size_t smem, cudaStream_
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -760,6 +939,113 @@ static int launch_dp_g(const StreamParams& p, int ng, int rp, int grid, size_t s
     return rp == 2 ? launch_dp_k<FMT, MT, 1, 2>(p, grid, smem, st) : launch_dp_k<FMT, MT, 1, 1>(p, grid, smem, st);
 }
 
+
+// ---- self-feeding form: plan and launch -------------------------------------------------
+// 0 (default): the producer-warp kernel above; 1: the self-feeding kernel where its ring fits
+static int g_opt_self = 0;
+static int g_opt_self_warps = 0;  // 0: the most warps (16, 12, 8) whose private rings are at least two slots deep
+void dp_set_self(int v) { g_opt_self = v ? 1 : 0; }
+void dp_set_self_warps(int v) { g_opt_self_warps = (v == 8 || v == 12 || v == 16) ? v : 0; }
+
+template <int FMT>
+static bool plan_dpw(int M, int N, int K, int sms, size_t smem_max, StreamParams& p, int& grid, int& warps, size_t& smem) {
+    if (K % Chunk<FMT>::elems != 0 || M > 4) return false;
+    p.M = M; p.N = N; p.K = K;
+    p.row_bytes = (K / Blk<FMT>::elems) * Blk<FMT>::bytes;
+    p.chunks_per_row = K / Chunk<FMT>::elems;
+    size_t off = 0;
+    p.off_xhi = (int)off; off += ((size_t)kXGroupStride * (K / 128) * M + 127) & ~size_t(127);  // int16 activations
+    p.off_xlo = (int)off; off += (((size_t)4 * (K / 128) * M) + 127) & ~size_t(127);            // per-group 2^-e
+    const size_t sums = FMT == kQ4_K ? (size_t)4 * (K / 32) * M : FMT == kQ6_K ? (size_t)4 * (K / 16) * M : 0;
+    p.off_sxhi = (int)off; off += (sums + 127) & ~size_t(127);
+    p.off_sxlo = p.off_red = (int)off;
+    p.off_stage = (int)off;
+    if (off + 128 + 4096 > smem_max) return false;
+    const size_t avail = smem_max - off - 128;
+    // A slot holds one slice of a row pair. A lane works on one 128-element group (Q6_K: half of
+    // one), so a slice should hold a multiple of 32 (16) groups per row; among those take the
+    // largest within the per-row target, else the smallest, then the most warps whose rings are
+    // two slots deep.
+    constexpr int gpc = Chunk<FMT>::elems / 128;
+    constexpr int glanes = FMT == kQ6_K ? 16 : 32;
+    const int cpr = p.chunks_per_row;
+    const size_t target_row = (size_t)stream_get_option(2) * 1024 / kTileRows;
+    int want = stream_get_option(0);
+    want = want < 2 ? 2 : (want > kMaxStages ? kMaxStages : want);
+    auto stride_of = [](int sc) {
+        int rs = sc * Chunk<FMT>::bytes;
+        return rs + ((16 - (rs % 128)) + 128) % 128;  // 16 (mod 128): the two rows of a pair start in different banks
+    };
+    int best = 0;
+    for (int sc = 1; sc <= cpr; ++sc) {
+        if ((sc * gpc) % glanes != 0 && sc != cpr) continue;
+        if (best && (size_t)stride_of(sc) > target_row) break;
+        best = sc;
+        if ((size_t)stride_of(sc) > target_row) break;  // the smallest qualifying slice is already past the target
+    }
+    if (!best) return false;
+    const int rs = stride_of(best);
+    static const int kWarpChoices[3] = {16, 12, 8};
+    warps = 0;
+    for (int w : kWarpChoices) {
+        if (g_opt_self_warps && w != g_opt_self_warps) continue;
+        if ((size_t)w * 2 * rs * 2 <= avail) { warps = w; break; }
+    }
+    if (!warps) return false;
+    p.slice_chunks = best;
+    p.row_stride = rs;
+    p.n_slices = (cpr + best - 1) / best;
+    int ns = (int)(avail / ((size_t)warps * 2 * rs));
+    if (ns > want) ns = want;
+    const int vpairs = (N + 1) / 2;
+    grid = stream_get_option(3) > 0 ? stream_get_option(3) : sms;
+    if (grid > vpairs) grid = vpairs;
+    // a ring deeper than the steps a warp will ever see only takes shared memory away from the
+    // next kernel's CTAs
+    const int pairs_per_cta = (vpairs + grid - 1) / grid;
+    const int steps_seen = ((pairs_per_cta + warps - 1) / warps) * p.n_slices;
+    if (ns > steps_seen) ns = steps_seen < 1 ? 1 : steps_seen;
+    p.n_stages = ns;
+    p.n_tiles_total = 0;
+    p.split_full = 0;
+    smem = off + (size_t)ns * warps * 2 * rs + 128;
+    return true;
+}
+
+template <int FMT, int MT>
+static int launch_dpw_k(const StreamParams& p, int grid, int warps, size_t smem, cudaStream_t st) {
+    auto kern = gemv_dpw_kernel<FMT, MT>;
+    static bool configured[64] = {};
+    int dev = 0;
+    B200Q_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        B200Q_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)warps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = stream_get_option(1) ? 1 : 0;
+    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
+    return B200Q_OK;
+}
+
+template <int FMT>
+static int launch_dpw_m(const StreamParams& p, int grid, int warps, size_t smem, cudaStream_t st) {
+    switch (p.M) {
+        case 1: return launch_dpw_k<FMT, 1>(p, grid, warps, smem, st);
+        case 2: return launch_dpw_k<FMT, 2>(p, grid, warps, smem, st);
+        case 3: return launch_dpw_k<FMT, 3>(p, grid, warps, smem, st);
+        default: return launch_dpw_k<FMT, 4>(p, grid, warps, smem, st);
+    }
+}
+
 template <int FMT>
 static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N,
                        int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh) {
@@ -770,11 +1056,14 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
     // two pipelines with 16-row tiles, one pipeline with 16-row tiles.
     int ng = g_opt_groups, rp = 1;
     *taken = false;
+    int warps = 0;
+    const bool self = g_opt_self && plan_dpw<FMT>(M, N, K, sms, smem_max, p, grid, warps, smem);
+    if (self) *taken = true;
     // Measured on B200: with two pipelines of 16-row tiles available, 32-row tiles in one pipeline
     // make no difference (Q4_K, Q8_0) or lose (Q6_K in half-group units: LM head 94 % vs 70 % of
     // the HBM copy rate), so they are only taken on request.
     const bool tall = g_opt_tile_pairs == 2;
-    if (tall && N >= 32 * sms / 2) {
+    if (!*taken && tall && N >= 32 * sms / 2) {
         ng = 1; rp = 2;
         *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, rp, p, grid, smem);
     }
@@ -805,6 +1094,7 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
         }
         p.sh_state = sh->state;
     }
+    if (self) return launch_dpw_m<FMT>(p, grid, warps, smem, st);
     switch (M) {
         case 1: return launch_dp_g<FMT, 1>(p, ng, rp, grid, smem, st);
         case 2: return launch_dp_g<FMT, 2>(p, ng, rp, grid, smem, st);
@@ -818,6 +1108,7 @@ int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const voi
                    int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh) {
     *taken = false;
     if ((reinterpret_cast<uintptr_t>(W) & 15) != 0) return B200Q_OK;  // bulk copies need 16-byte aligned rows
+    smem_max -= 1024;  // the kernel's barriers are static shared memory
     switch (fmt) {
         case kQ4_K: return launch_dp_f<kQ4_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
         case kQ6_K: return launch_dp_f<kQ6_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
@@ -842,8 +1133,20 @@ static int launch_dp_multi_f(int n_seg, const void* const* W, const int* N, void
         tiles += (N[s] + kTileRows - 1) / kTileRows;
     }
     p.seg_tile0[n_seg] = tiles;
-    int grid = 0, ng = g_opt_groups;
+    int grid = 0, ng = g_opt_groups, warps = 0;
     size_t smem = 0;
+    if (g_opt_self && plan_dpw<FMT>(1, kTileRows * tiles, K, sms, smem_max, p, grid, warps, smem)) {
+        *taken = true;
+        p.n_seg = n_seg;
+        p.W = p.seg_W[0];
+        p.Y = p.seg_Y[0];
+        p.bias = p.seg_bias[0];
+        p.X = X;
+        p.status = status;
+        p.x_dtype = x_dtype;
+        p.y_dtype = y_dtype;
+        return launch_dpw_m<FMT>(p, grid, warps, smem, st);
+    }
     *taken = plan_dp<FMT>(1, kTileRows * tiles, K, sms, smem_max, ng, 1, p, grid, smem);
     if (!*taken && ng == 2) {
         ng = 1;
@@ -871,6 +1174,7 @@ int launch_gemv_dp_multi(int fmt, int n_seg, const void* const* W, const int* N,
     *taken = false;
     for (int s = 0; s < n_seg; ++s)
         if ((reinterpret_cast<uintptr_t>(W[s]) & 15) != 0) return B200Q_OK;
+    smem_max -= 1024;  // the kernel's barriers are static shared memory
     switch (fmt) {
         case kQ4_K: return launch_dp_multi_f<kQ4_K>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);
         case kQ6_K: return launch_dp_multi_f<kQ6_K>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);

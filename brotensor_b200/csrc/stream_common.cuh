@@ -29,6 +29,7 @@ struct StreamParams {
     int row_stride;      // bytes between rows inside a stage (padded)
     int n_stages;        // ring depth
     int n_tiles_total;   // > 0: CTAs own whole 16-row tiles (tile-balanced grid); 0: rows split evenly
+    int split_full;      // 1: one full barrier per consumer warp and stage; 0: one per stage
     // shared-memory offsets (bytes from the 128-byte aligned base)
     int off_xhi, off_xlo, off_sxhi, off_sxlo, off_red, off_stage;
     // Several weight matrices of one format and K that share the activation vector (n_seg > 1):
