@@ -27,8 +27,6 @@ int gemm_get_pair();
 void dp_set_groups(int v);
 void dp_set_tile_pairs(int v);
 void dp_set_split_full(int v);
-void dp_set_self(int v);
-void dp_set_self_warps(int v);
 int dp_get_tile_pairs();
 int dp_get_groups();
 int stream_get_option(int which);
@@ -320,8 +318,6 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "gemv_groups")) dp_set_groups(value);
     else if (!strcmp(key, "gemv_tile_pairs")) dp_set_tile_pairs(value);
     else if (!strcmp(key, "gemv_split_full")) dp_set_split_full(value);
-    else if (!strcmp(key, "gemv_self")) dp_set_self(value);
-    else if (!strcmp(key, "gemv_self_warps")) dp_set_self_warps(value);
     else if (!strcmp(key, "gemm_pair")) gemm_set_pair(value);
     else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
     return B200Q_OK;

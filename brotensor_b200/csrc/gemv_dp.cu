@@ -59,63 +59,91 @@ __device__ __forceinline__ int dp2a_hi_ss(uint32_t x, uint32_t b, int c) {
 // traffic below goes through explicit ld.shared / st.shared with 32-bit addresses.
 constexpr int kXGroupStride = 272;
 
+template <typename XT>
+__device__ __forceinline__ void x_load_seg(const StreamParams& p, int idx, float (&v)[8]) {
+    const XT* X = static_cast<const XT*>(p.X);
+    const int segs = p.K >> 3;
+    const int m = idx / segs, seg = idx - m * segs;
+    if constexpr (sizeof(XT) == 4) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(X + (size_t)m * p.K) + 2 * seg);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(X + (size_t)m * p.K) + 2 * seg + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        union {
+            uint4 q;
+            XT h[8];
+        } pk;
+        pk.q = __ldg(reinterpret_cast<const uint4*>(X + (size_t)m * p.K) + seg);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = to_f32<XT>(pk.h[k]);
+    }
+}
+
+// One segment (eight consecutive activations) of the staged image; called by whole warps.
+template <int FMT>
+__device__ __forceinline__ void x_store_seg(const StreamParams& p, uint32_t sbase, int idx, const float (&v)[8]) {
+    const int segs = p.K >> 3, groups = p.K >> 7;
+    const int m = idx / segs, seg = idx - m * segs;
+    const int gg = seg >> 4, i = seg & 15;
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+    // the 16 segments of a group are 16 consecutive lanes
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+    // 2^e with amax * 2^e in [2^13, 2^14); e clamped so both 2^e and 2^-e are normal floats
+    int e = 0;
+    if (amax > 0.f && amax < 3.0e38f) e = 13 - (int)((__float_as_uint(amax) >> 23) & 0xFFu) + 127;
+    e = max(-126, min(126, e));
+    const float s = __uint_as_float((uint32_t)(e + 127) << 23);
+    int q[8], sum = 0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        q[k] = max(-16383, min(16383, __float2int_rn(v[k] * s)));
+        sum += q[k];
+    }
+    uint4 o;
+    o.x = (uint32_t)(q[0] & 0xFFFF) | ((uint32_t)q[1] << 16);
+    o.y = (uint32_t)(q[2] & 0xFFFF) | ((uint32_t)q[3] << 16);
+    o.z = (uint32_t)(q[4] & 0xFFFF) | ((uint32_t)q[5] << 16);
+    o.w = (uint32_t)(q[6] & 0xFFFF) | ((uint32_t)q[7] << 16);
+    sts128(sbase + p.off_xhi + (uint32_t)((m * groups + gg) * kXGroupStride + (i << 4)), o);
+    if (i == 0) sts32(sbase + p.off_xlo + (uint32_t)(m * groups + gg) * 4, (uint32_t)(127 - e) << 23);
+    if constexpr (FMT == kQ4_K) {  // sums over 32 elements = 4 segments
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((i & 3) == 0) sts32(sbase + p.off_sxhi + (uint32_t)(m * (p.K >> 5) + (seg >> 2)) * 4, (uint32_t)sum);
+    } else if constexpr (FMT == kQ6_K) {  // sums over 16 elements = 2 segments
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        if ((i & 1) == 0) sts32(sbase + p.off_sxhi + (uint32_t)(m * (p.K >> 4) + (seg >> 1)) * 4, (uint32_t)sum);
+    }
+}
+
+// Stages the activations as int16 with one power-of-two scale per 128-element group. A thread's
+// global loads go out four segments at a time before any of them is converted, so a long row
+// (K = 14336: 3.5 segments per thread) costs one load latency instead of one per segment.
 template <int FMT, typename XT>
 __device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase, int tid, int nthreads) {
-    const XT* X = static_cast<const XT*>(p.X);
-    const int segs = p.K >> 3, groups = p.K >> 7;
-    const int total = segs * p.M;  // K % 256 == 0, so a multiple of 32
-    for (int idx = tid; idx < total; idx += nthreads) {
-        const int m = idx / segs, seg = idx - m * segs;
-        const int gg = seg >> 4, i = seg & 15;
-        float v[8];
-        if constexpr (sizeof(XT) == 4) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(X + (size_t)m * p.K) + 2 * seg);
-            const float4 b = __ldg(reinterpret_cast<const float4*>(X + (size_t)m * p.K) + 2 * seg + 1);
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-            v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-        } else {
-            union {
-                uint4 q;
-                XT h[8];
-            } pk;
-            pk.q = __ldg(reinterpret_cast<const uint4*>(X + (size_t)m * p.K) + seg);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) v[k] = to_f32<XT>(pk.h[k]);
+    const int total = (p.K >> 3) * p.M;  // K % 256 == 0, so a multiple of 32: whole warps are in or out
+    if (total <= nthreads) {  // at most one segment per thread (K = 4096, one activation row)
+        if (tid < total) {
+            float v[8];
+            x_load_seg<XT>(p, tid, v);
+            x_store_seg<FMT>(p, sbase, tid, v);
         }
-        float amax = 0.f;
+        return;
+    }
+    for (int base = tid; base < total; base += 4 * nthreads) {
+        float v[4][8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
-        // the 16 segments of a group are 16 consecutive lanes
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
-        // 2^e with amax * 2^e in [2^13, 2^14); e clamped so both 2^e and 2^-e are normal floats
-        int e = 0;
-        if (amax > 0.f && amax < 3.0e38f) e = 13 - (int)((__float_as_uint(amax) >> 23) & 0xFFu) + 127;
-        e = max(-126, min(126, e));
-        const float s = __uint_as_float((uint32_t)(e + 127) << 23);
-        int q[8], sum = 0;
+        for (int u = 0; u < 4; ++u)
+            if (base + u * nthreads < total) x_load_seg<XT>(p, base + u * nthreads, v[u]);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            q[k] = max(-16383, min(16383, __float2int_rn(v[k] * s)));
-            sum += q[k];
-        }
-        uint4 o;
-        o.x = (uint32_t)(q[0] & 0xFFFF) | ((uint32_t)q[1] << 16);
-        o.y = (uint32_t)(q[2] & 0xFFFF) | ((uint32_t)q[3] << 16);
-        o.z = (uint32_t)(q[4] & 0xFFFF) | ((uint32_t)q[5] << 16);
-        o.w = (uint32_t)(q[6] & 0xFFFF) | ((uint32_t)q[7] << 16);
-        sts128(sbase + p.off_xhi + (uint32_t)((m * groups + gg) * kXGroupStride + (i << 4)), o);
-        if (i == 0) sts32(sbase + p.off_xlo + (uint32_t)(m * groups + gg) * 4, (uint32_t)(127 - e) << 23);
-        if constexpr (FMT == kQ4_K) {  // sums over 32 elements = 4 segments
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            if ((i & 3) == 0) sts32(sbase + p.off_sxhi + (uint32_t)(m * (p.K >> 5) + (seg >> 2)) * 4, (uint32_t)sum);
-        } else if constexpr (FMT == kQ6_K) {  // sums over 16 elements = 2 segments
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            if ((i & 1) == 0) sts32(sbase + p.off_sxhi + (uint32_t)(m * (p.K >> 4) + (seg >> 1)) * 4, (uint32_t)sum);
-        }
+        for (int u = 0; u < 4; ++u)
+            if (base + u * nthreads < total) x_store_seg<FMT>(p, sbase, base + u * nthreads, v[u]);
     }
 }
 
@@ -659,156 +687,6 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     if (p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32);
 }
 
-// ---- self-feeding form ---------------------------------------------------------------
-// Every warp is its own pipeline: it owns a private ring of p.n_stages slots, each holding one
-// slice of one row pair, and one full barrier per slot. Lane 0 issues the bulk copies of the
-// warp's first slots before anything else (weights do not depend on the stream-ordered
-// predecessor), and refills a slot right after the warp has finished with it. There are no
-// producer warps, no empty barriers and no coupling between warps, so a warp starts on its rows
-// as soon as they have landed and its next rows are requested the moment their slot is free.
-// What a launch cannot overlap shrinks to one DRAM round trip at the start and one row pair's
-// arithmetic at the end. The CTA's row pairs go round-robin over its warps.
-constexpr int kSelfWarpsMax = 16;
-
-template <int FMT, int MT>
-__global__ void __launch_bounds__(kSelfWarpsMax * 32, 1) gemv_dpw_kernel(const StreamParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;  // shared-space address
-    __shared__ uint64_t bar_full[kSelfWarpsMax][kMaxStages];
-    __shared__ int abort_flag;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nthreads = blockDim.x, nwarps = nthreads >> 5;
-    const int G = gridDim.x;
-    // virtual rows of the launch: the matrix's rows, or with several matrices their tile-padded concatenation
-    const int vrows = p.n_seg > 1 ? kTileRows * p.seg_tile0[p.n_seg] : p.N;
-    const int vpairs = (vrows + 1) >> 1;
-    const int pair_begin = (int)((long long)vpairs * blockIdx.x / G);
-    const int pair_end = (int)((long long)vpairs * (blockIdx.x + 1) / G);
-    const int row_begin = 2 * pair_begin, row_end = min(vrows, 2 * pair_end);
-    const int cta_pairs = pair_end - pair_begin;
-    const int my_pairs = cta_pairs > warp ? (cta_pairs - warp + nwarps - 1) / nwarps : 0;
-    const int n_steps = my_pairs * p.n_slices;
-    const int slot_bytes = 2 * p.row_stride;
-    const uint32_t ring = sbase + (uint32_t)(p.off_stage + warp * p.n_stages * slot_bytes);
-    const uint32_t bar0 = smem_u32(&bar_full[warp][0]);
-
-    // lane 0: request slice `slice` of this warp's pair number `it` into slot `slot`
-    auto issue = [&](int it, int slice, int slot) {
-        const TileRef tr = tile_ref(p, 2 * (pair_begin + warp + it * nwarps));
-        const int cnt = min(max(tr.N - tr.row0, 0), 2);  // rows of the pair that exist (0: padding between matrices)
-        const int c0 = slice * p.slice_chunks;
-        const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
-        const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
-        const uint32_t full = bar0 + 8u * (uint32_t)slot;
-        const uint32_t dst = ring + (uint32_t)(slot * slot_bytes);
-        const uint8_t* src = tr.W + (size_t)tr.row0 * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
-        mbar_arrive_expect_tx(full, bytes * (uint32_t)cnt);  // no rows: a plain arrival
-        if (cnt > 0) bulk_g2s(dst, src, bytes, full);
-        if (cnt > 1) bulk_g2s(dst + (uint32_t)p.row_stride, src + p.row_bytes, bytes, full);
-    };
-    // the next step to request, kept as (pair, slice, slot) so that a refill costs no division
-    int iss_it = 0, iss_slice = 0, iss_slot = 0, iss_k = 0;
-    auto issue_next = [&]() {
-        if (lane == 0) issue(iss_it, iss_slice, iss_slot);
-        ++iss_k;
-        if (++iss_slice == p.n_slices) { iss_slice = 0; ++iss_it; }
-        if (++iss_slot == p.n_stages) iss_slot = 0;
-    };
-
-    if (tid == 0) abort_flag = 0;
-    if (lane == 0) {
-        for (int s = 0; s < p.n_stages; ++s) mbar_init(bar0 + 8u * (uint32_t)s, 1);
-        fence_mbar_init();
-    }
-    for (int k = 0, first = min(n_steps, p.n_stages); k < first; ++k) issue_next();
-    grid_dep_launch();
-    grid_dep_wait();  // activations (and Y) belong to the stream-ordered predecessor
-    // launch counter of the sharded form: stable while this launch runs (only its last CTA bumps it)
-    const unsigned int sh_epoch = p.sh_world > 0 ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
-    const unsigned int sh_buf = (sh_epoch + 1u) & 1u;
-    if (p.x_dtype == B200Q_DT_F32) stage_x16<FMT, float>(p, sbase, tid, nthreads);
-    else if (p.x_dtype == B200Q_DT_F16) stage_x16<FMT, __half>(p, sbase, tid, nthreads);
-    else stage_x16<FMT, __nv_bfloat16>(p, sbase, tid, nthreads);
-    __syncthreads();
-
-    const XAddr xa = {sbase + (uint32_t)p.off_xhi, sbase + (uint32_t)p.off_xlo, sbase + (uint32_t)p.off_sxhi, p.K >> 7, p.K};
-    constexpr int kGroupsPerChunk = Chunk<FMT>::elems / 128;
-    bool live = true;
-    int slot = 0, k = 0;
-    uint32_t phase = 0;
-    float acc[2][MT];
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
-
-    for (int it = 0; it < my_pairs; ++it) {
-        const TileRef tr = tile_ref(p, 2 * (pair_begin + warp + it * nwarps));
-        const int cnt = min(max(tr.N - tr.row0, 0), 2);
-        for (int slice = 0; slice < p.n_slices; ++slice, ++k) {
-            if (live) {
-                // keep the decision warp-uniform
-                const bool ok = wait_or_abort(bar0 + 8u * (uint32_t)slot, phase, &abort_flag, p.status, kDevTimeoutFull);
-                live = __all_sync(0xffffffffu, ok);
-            }
-            if (live && cnt > 0) {
-                const int c0 = slice * p.slice_chunks;
-                const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
-                const int ng = nch * kGroupsPerChunk, g0 = c0 * kGroupsPerChunk;
-                // a pair with one row (odd row count) reuses it as the second row; that sum is dropped
-                const uint32_t rowA = ring + (uint32_t)(slot * slot_bytes);
-                const uint32_t rowB = cnt > 1 ? rowA + (uint32_t)p.row_stride : rowA;
-                if constexpr (FMT == kQ6_K) {
-                    // half-group units: lanes 0..15 take H = 0 of sixteen groups, lanes 16..31 H = 1
-                    for (int gi = (lane & 15); gi < ng; gi += 16) item_q6k_half<MT>(rowA, rowB, gi, lane >> 4, g0 + gi, xa, acc);
-                } else {
-                    for (int gi = lane; gi < ng; gi += 32) {
-                        if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
-                        else item_q8_0<MT>(rowA, rowB, gi, g0 + gi, xa, acc);
-                    }
-                }
-            }
-            __syncwarp();  // every lane has read its part of the slot
-            // The lanes' reads of the slot are ordered before the refill by the warp barrier above and
-            // program order in lane 0, like a consumer-release / producer-acquire pair on an mbarrier.
-            if (live && iss_k < n_steps) issue_next();
-            if (++slot == p.n_stages) {
-                slot = 0;
-                phase ^= 1;
-            }
-        }
-        // the rows' partial sums live in this warp's lanes: lanes 0..15 finish the first
-        // row of the pair, lanes 16..31 the second (five shuffles for both), then write
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            const bool up = lane >= 16;
-            float s = (up ? acc[1][m] : acc[0][m]) + __shfl_xor_sync(0xffffffffu, up ? acc[0][m] : acc[1][m], 16);
-#pragma unroll
-            for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-            acc[0][m] = acc[1][m] = 0.f;
-            const int rr = up ? 1 : 0;
-            if ((lane & 15) == 0 && rr < cnt && m < p.M && live && !*(volatile int*)&abort_flag) {
-                const int n = tr.row0 + rr;
-                if (tr.bias) {
-                    if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(tr.bias)[n];
-                    else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(tr.bias)[n]);
-                    else s += __bfloat162float(static_cast<const __nv_bfloat16*>(tr.bias)[n]);
-                }
-                const size_t o = (size_t)m * tr.N + n;
-                if (p.sh_world > 0) {
-                    // sharded output: into this rank's own result vector first (which of the two
-                    // vectors is this launch's parity); the CTA forwards its rows to the peers below
-                    p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
-                } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(tr.Y)[o] = s;
-                else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(tr.Y)[o] = __float2half_rn(s);
-                else static_cast<__nv_bfloat16*>(tr.Y)[o] = __float2bfloat16_rn(s);
-            }
-        }
-    }
-    if (p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, nthreads);
-}
-
 // ---- host side ------------------------------------------------------------------------
 
 static int g_opt_groups = 2;
@@ -940,112 +818,6 @@ static int launch_dp_g(const StreamParams& p, int ng, int rp, int grid, size_t s
 }
 
 
-// ---- self-feeding form: plan and launch -------------------------------------------------
-// 0 (default): the producer-warp kernel above; 1: the self-feeding kernel where its ring fits
-static int g_opt_self = 0;
-static int g_opt_self_warps = 0;  // 0: the most warps (16, 12, 8) whose private rings are at least two slots deep
-void dp_set_self(int v) { g_opt_self = v ? 1 : 0; }
-void dp_set_self_warps(int v) { g_opt_self_warps = (v == 8 || v == 12 || v == 16) ? v : 0; }
-
-template <int FMT>
-static bool plan_dpw(int M, int N, int K, int sms, size_t smem_max, StreamParams& p, int& grid, int& warps, size_t& smem) {
-    if (K % Chunk<FMT>::elems != 0 || M > 4) return false;
-    p.M = M; p.N = N; p.K = K;
-    p.row_bytes = (K / Blk<FMT>::elems) * Blk<FMT>::bytes;
-    p.chunks_per_row = K / Chunk<FMT>::elems;
-    size_t off = 0;
-    p.off_xhi = (int)off; off += ((size_t)kXGroupStride * (K / 128) * M + 127) & ~size_t(127);  // int16 activations
-    p.off_xlo = (int)off; off += (((size_t)4 * (K / 128) * M) + 127) & ~size_t(127);            // per-group 2^-e
-    const size_t sums = FMT == kQ4_K ? (size_t)4 * (K / 32) * M : FMT == kQ6_K ? (size_t)4 * (K / 16) * M : 0;
-    p.off_sxhi = (int)off; off += (sums + 127) & ~size_t(127);
-    p.off_sxlo = p.off_red = (int)off;
-    p.off_stage = (int)off;
-    if (off + 128 + 4096 > smem_max) return false;
-    const size_t avail = smem_max - off - 128;
-    // A slot holds one slice of a row pair. A lane works on one 128-element group (Q6_K: half of
-    // one), so a slice should hold a multiple of 32 (16) groups per row; among those take the
-    // largest within the per-row target, else the smallest, then the most warps whose rings are
-    // two slots deep.
-    constexpr int gpc = Chunk<FMT>::elems / 128;
-    constexpr int glanes = FMT == kQ6_K ? 16 : 32;
-    const int cpr = p.chunks_per_row;
-    const size_t target_row = (size_t)stream_get_option(2) * 1024 / kTileRows;
-    int want = stream_get_option(0);
-    want = want < 2 ? 2 : (want > kMaxStages ? kMaxStages : want);
-    auto stride_of = [](int sc) {
-        int rs = sc * Chunk<FMT>::bytes;
-        return rs + ((16 - (rs % 128)) + 128) % 128;  // 16 (mod 128): the two rows of a pair start in different banks
-    };
-    int best = 0;
-    for (int sc = 1; sc <= cpr; ++sc) {
-        if ((sc * gpc) % glanes != 0 && sc != cpr) continue;
-        if (best && (size_t)stride_of(sc) > target_row) break;
-        best = sc;
-        if ((size_t)stride_of(sc) > target_row) break;  // the smallest qualifying slice is already past the target
-    }
-    if (!best) return false;
-    const int rs = stride_of(best);
-    static const int kWarpChoices[3] = {16, 12, 8};
-    warps = 0;
-    for (int w : kWarpChoices) {
-        if (g_opt_self_warps && w != g_opt_self_warps) continue;
-        if ((size_t)w * 2 * rs * 2 <= avail) { warps = w; break; }
-    }
-    if (!warps) return false;
-    p.slice_chunks = best;
-    p.row_stride = rs;
-    p.n_slices = (cpr + best - 1) / best;
-    int ns = (int)(avail / ((size_t)warps * 2 * rs));
-    if (ns > want) ns = want;
-    const int vpairs = (N + 1) / 2;
-    grid = stream_get_option(3) > 0 ? stream_get_option(3) : sms;
-    if (grid > vpairs) grid = vpairs;
-    // a ring deeper than the steps a warp will ever see only takes shared memory away from the
-    // next kernel's CTAs
-    const int pairs_per_cta = (vpairs + grid - 1) / grid;
-    const int steps_seen = ((pairs_per_cta + warps - 1) / warps) * p.n_slices;
-    if (ns > steps_seen) ns = steps_seen < 1 ? 1 : steps_seen;
-    p.n_stages = ns;
-    p.n_tiles_total = 0;
-    p.split_full = 0;
-    smem = off + (size_t)ns * warps * 2 * rs + 128;
-    return true;
-}
-
-template <int FMT, int MT>
-static int launch_dpw_k(const StreamParams& p, int grid, int warps, size_t smem, cudaStream_t st) {
-    auto kern = gemv_dpw_kernel<FMT, MT>;
-    static bool configured[64] = {};
-    int dev = 0;
-    B200Q_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
-        B200Q_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
-        if (dev >= 0 && dev < 64) configured[dev] = true;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((unsigned)warps * 32);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = stream_get_option(1) ? 1 : 0;
-    B200Q_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p));
-    return B200Q_OK;
-}
-
-template <int FMT>
-static int launch_dpw_m(const StreamParams& p, int grid, int warps, size_t smem, cudaStream_t st) {
-    switch (p.M) {
-        case 1: return launch_dpw_k<FMT, 1>(p, grid, warps, smem, st);
-        case 2: return launch_dpw_k<FMT, 2>(p, grid, warps, smem, st);
-        case 3: return launch_dpw_k<FMT, 3>(p, grid, warps, smem, st);
-        default: return launch_dpw_k<FMT, 4>(p, grid, warps, smem, st);
-    }
-}
-
 template <int FMT>
 static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N,
                        int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh) {
@@ -1056,14 +828,11 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
     // two pipelines with 16-row tiles, one pipeline with 16-row tiles.
     int ng = g_opt_groups, rp = 1;
     *taken = false;
-    int warps = 0;
-    const bool self = g_opt_self && plan_dpw<FMT>(M, N, K, sms, smem_max, p, grid, warps, smem);
-    if (self) *taken = true;
     // Measured on B200: with two pipelines of 16-row tiles available, 32-row tiles in one pipeline
     // make no difference (Q4_K, Q8_0) or lose (Q6_K in half-group units: LM head 94 % vs 70 % of
     // the HBM copy rate), so they are only taken on request.
     const bool tall = g_opt_tile_pairs == 2;
-    if (!*taken && tall && N >= 32 * sms / 2) {
+    if (tall && N >= 32 * sms / 2) {
         ng = 1; rp = 2;
         *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, rp, p, grid, smem);
     }
@@ -1094,7 +863,6 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
         }
         p.sh_state = sh->state;
     }
-    if (self) return launch_dpw_m<FMT>(p, grid, warps, smem, st);
     switch (M) {
         case 1: return launch_dp_g<FMT, 1>(p, ng, rp, grid, smem, st);
         case 2: return launch_dp_g<FMT, 2>(p, ng, rp, grid, smem, st);
@@ -1133,20 +901,8 @@ static int launch_dp_multi_f(int n_seg, const void* const* W, const int* N, void
         tiles += (N[s] + kTileRows - 1) / kTileRows;
     }
     p.seg_tile0[n_seg] = tiles;
-    int grid = 0, ng = g_opt_groups, warps = 0;
+    int grid = 0, ng = g_opt_groups;
     size_t smem = 0;
-    if (g_opt_self && plan_dpw<FMT>(1, kTileRows * tiles, K, sms, smem_max, p, grid, warps, smem)) {
-        *taken = true;
-        p.n_seg = n_seg;
-        p.W = p.seg_W[0];
-        p.Y = p.seg_Y[0];
-        p.bias = p.seg_bias[0];
-        p.X = X;
-        p.status = status;
-        p.x_dtype = x_dtype;
-        p.y_dtype = y_dtype;
-        return launch_dpw_m<FMT>(p, grid, warps, smem, st);
-    }
     *taken = plan_dp<FMT>(1, kTileRows * tiles, K, sms, smem_max, ng, 1, p, grid, smem);
     if (!*taken && ng == 2) {
         ng = 1;
