@@ -158,6 +158,30 @@ int b200q_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows
     return launch_dequant(fmt, W, out, out_dtype, rows, K, static_cast<cudaStream_t>(stream));
 }
 
+// The streaming kernel for a decode GEMV of M <= 8 rows, by measurement on B200 (14336 x 4096 and
+// 4096 x 14336, us per launch): integer dot products win for one and two rows (Q4_K 8.1 / 14.0
+// against 16.7 / 18.3 with warp MMA), warp MMA from three rows on (Q4_K 19.9 / 21.3 against 22.9 /
+// 28.9 at three / four rows; Q6_K from four rows on), and is the only one for five to eight rows.
+// *taken = false when neither kernel takes the shape.
+static int gemv_streaming(DevInfo* d, int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y,
+                          int y_dtype, int M, int N, int K, cudaStream_t st, bool* taken) {
+    *taken = false;
+    const size_t smem = d->smem_optin - 1024;
+    const bool mma_first = M >= (fmt == kQ6_K ? 4 : 3);
+    if (mma_first) {
+        if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, smem, d->status, st, taken)) return rc;
+        if (*taken) return B200Q_OK;
+    }
+    if (M <= 4) {
+        if (int rc = launch_gemv_dp(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, smem, d->status, st, taken, nullptr)) return rc;
+        if (*taken) return B200Q_OK;
+    }
+    if (!mma_first) {
+        if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, smem, d->status, st, taken)) return rc;
+    }
+    return B200Q_OK;
+}
+
 int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M,
                int N, int K, void* stream) {
     if (int rc = check_linear_args("gemv", fmt, W, X, x_dtype, Y, y_dtype, M, N, K)) return rc;
@@ -167,21 +191,38 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
     if (int rc = dev_info(&d)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // 0 = automatic, 1 = plain-load kernel, 2 = warp-MMA streaming kernel, 3 = integer-dot streaming kernel
-    if (g_opt_gemv_path == 0 || g_opt_gemv_path == 3) {
+    if (g_opt_gemv_path == 0) {
+        bool taken = false;
+        if (int rc = gemv_streaming(d, fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, st, &taken)) return rc;
+        if (taken) return B200Q_OK;
+        if (M > 4) {
+            // Eight activation rows of a long K do not fit beside the weight ring (K = 14336): two
+            // passes of up to four rows through the streaming kernels still read the weights at
+            // the stream rate, which the plain-load kernel does not.
+            if (int rc = gemv_streaming(d, fmt, W, X, x_dtype, bias, Y, y_dtype, 4, N, K, st, &taken)) return rc;
+            if (taken) {
+                const size_t xs = (size_t)K * dt_size(x_dtype), ys = (size_t)N * dt_size(y_dtype);
+                const void* X2 = static_cast<const uint8_t*>(X) + 4 * xs;
+                void* Y2 = static_cast<uint8_t*>(Y) + 4 * ys;
+                if (int rc = gemv_streaming(d, fmt, W, X2, x_dtype, bias, Y2, y_dtype, M - 4, N, K, st, &taken)) return rc;
+                if (taken) return B200Q_OK;
+                return launch_gemv_simple(fmt, W, X2, x_dtype, bias, Y2, y_dtype, M - 4, N, K, st);
+            }
+        }
+    }
+    if (g_opt_gemv_path == 3) {
         bool taken = false;
         if (int rc = launch_gemv_dp(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->smem_optin - 1024, d->status, st, &taken, nullptr))
             return rc;
         if (taken) return B200Q_OK;
-        if (g_opt_gemv_path == 3)
-            return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the integer-dot kernel", M, N, K, fmt);
+        return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the integer-dot kernel", M, N, K, fmt);
     }
-    if (g_opt_gemv_path == 0 || g_opt_gemv_path == 2) {
+    if (g_opt_gemv_path == 2) {
         bool taken = false;
         if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->smem_optin - 1024, d->status, st, &taken))
             return rc;
         if (taken) return B200Q_OK;
-        if (g_opt_gemv_path == 2)
-            return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the streaming kernel", M, N, K, fmt);
+        return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the streaming kernel", M, N, K, fmt);
     }
     return launch_gemv_simple(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
 }

@@ -159,6 +159,22 @@ def test_gemv_matches_oracle(fmt, name, M, path, cpu_oracle):
         assert e < REL_L2, f"N={N} K={K} M={M} rel_l2={e}"
 
 
+@pytest.mark.parametrize("fmt,name", FMTS)
+@pytest.mark.parametrize("M", [3, 4, 5, 7, 8])
+def test_gemv_long_rows_several_activation_rows(fmt, name, M, cpu_oracle):
+    """K = 14336 (down_proj): eight activation rows do not fit beside the weight ring, so the
+    automatic route runs two passes of up to four rows; three and four rows take the warp-MMA kernel."""
+    N, K = 40, 14336
+    Wh = synth.make_blocks(fmt, N, K, seed=11)
+    Xh = synth.make_activations(M, K, seed=M)
+    bias = np.linspace(-1.0, 1.0, N).astype(np.float32)
+    want = cpu_oracle.matmul(fmt, Wh, Xh, threads=8) + bias[None, :]
+    got = ops.gemv(fmt, dev(Wh), dev(Xh), N, bias=dev(bias))
+    e = oracle.rel_l2(host_f32(got), want)
+    assert e < REL_L2, f"M={M} rel_l2={e}"
+    assert ops.device_status() == 0
+
+
 @pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("fmt,name", FMTS)
 @pytest.mark.parametrize("xdt,ydt", [("f16", "f16"), ("bf16", "f32"), ("f32", "bf16"), ("bf16", "bf16"), ("f16", "f32")])
