@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(PKG, "lib", "libb200q.so")
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = 1, 2, 3, 4, 5
 Q8_0, Q4_K, Q6_K = 14, 22, 24
+Q6_K_R8 = 124  # Q6_K regrouped by field in runs of eight blocks (b200q_repack)
 F32, F16, BF16 = 0, 1, 4
 
 # Every symbol include/b200q.h declares: (name, restype, argtypes)
@@ -25,6 +26,9 @@ SYMBOLS = [
     ("b200q_block_elems", _i, [_i]),
     ("b200q_block_bytes", _i, [_i]),
     ("b200q_packed_bytes", _sz, [_i, _i64, _i]),
+    ("b200q_repacked_fmt", _i, [_i, _i]),
+    ("b200q_repack", _i, [_i, _vp, _vp, _i64, _i, _vp]),
+    ("b200q_unpack", _i, [_i, _vp, _vp, _i64, _i, _vp]),
     ("b200q_dequant", _i, [_i, _vp, _vp, _i, _i64, _i, _vp]),
     ("b200q_gemv", _i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     ("b200q_gemv_multi", _i, [_i, _i, C.POINTER(_vp), C.POINTER(_i), C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _i, _vp]),

@@ -12,6 +12,7 @@
 namespace b200q {
 
 int launch_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows, int K, cudaStream_t st);
+int launch_repack(int fmt, const void* src, void* dst, int64_t rows, int K, bool to_runs, cudaStream_t st);
 int launch_gemv_simple(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
                        int M, int N, int K, cudaStream_t st);
 int launch_gemv_stream(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
@@ -64,7 +65,7 @@ struct DevInfo {
 static DevInfo g_dev[kMaxDev];
 static std::mutex g_dev_mu;
 
-static int fmt_slot(int fmt) { return fmt == kQ4_K ? 0 : fmt == kQ6_K ? 1 : fmt == kQ8_0 ? 2 : -1; }
+static int fmt_slot(int fmt) { return fmt == kQ4_K ? 0 : (fmt == kQ6_K || fmt == kQ6_KP) ? 1 : fmt == kQ8_0 ? 2 : -1; }
 
 static int dev_info(DevInfo** out) {
     int dev = -1;
@@ -106,9 +107,10 @@ static int check_linear_args(const char* op, int fmt, const void* W, const void*
     if (!dt_ok(x_dtype) || !dt_ok(y_dtype)) return fail(B200Q_ERR_BAD_ARG, "%s: unknown dtype (x %d, y %d)", op, x_dtype, y_dtype);
     if (M < 0 || N < 0 || K <= 0) return fail(B200Q_ERR_BAD_ARG, "%s: negative shape (M %d, N %d, K %d)", op, M, N, K);
     if (K % be) return fail(B200Q_ERR_BAD_ARG, "%s: K (%d) must be a multiple of %d", op, K, be);
+    if (fmt == kQ6_KP && K % kQ6RunElems) return fail(B200Q_ERR_BAD_ARG, "%s: K (%d) must be a multiple of %d for repacked Q6_K", op, K, kQ6RunElems);
     if (M == 0 || N == 0) return B200Q_OK;
     if (!W || !X || !Y) return fail(B200Q_ERR_BAD_ARG, "%s: null pointer", op);
-    if (!aligned(W, fmt == kQ4_K ? 4 : 2)) return fail(B200Q_ERR_BAD_ARG, "%s: W is not aligned to its block header", op);
+    if (!aligned(W, fmt == kQ6_KP ? 16 : fmt == kQ4_K ? 4 : 2)) return fail(B200Q_ERR_BAD_ARG, "%s: W is not aligned to its block header", op);
     if (!aligned(X, 16)) return fail(B200Q_ERR_BAD_ARG, "%s: X must be 16-byte aligned", op);
     if (!aligned(Y, (size_t)dt_size(y_dtype))) return fail(B200Q_ERR_BAD_ARG, "%s: Y is not aligned to its element size", op);
     return B200Q_OK;
@@ -136,12 +138,37 @@ const char* b200q_status_str(int s) {
 
 const char* b200q_last_error(void) { return g_err; }
 
-int b200q_block_elems(int fmt) { return fmt == kQ8_0 ? 32 : (fmt == kQ4_K || fmt == kQ6_K) ? 256 : 0; }
-int b200q_block_bytes(int fmt) { return fmt == kQ8_0 ? 34 : fmt == kQ4_K ? 144 : fmt == kQ6_K ? 210 : 0; }
+int b200q_block_elems(int fmt) { return fmt == kQ8_0 ? 32 : (fmt == kQ4_K || fmt == kQ6_K || fmt == kQ6_KP) ? 256 : 0; }
+int b200q_block_bytes(int fmt) { return fmt == kQ8_0 ? 34 : fmt == kQ4_K ? 144 : (fmt == kQ6_K || fmt == kQ6_KP) ? 210 : 0; }
 size_t b200q_packed_bytes(int fmt, int64_t rows, int K) {
     const int be = b200q_block_elems(fmt);
     if (!be || rows < 0 || K < 0 || K % be) return 0;
     return (size_t)rows * (size_t)(K / be) * (size_t)b200q_block_bytes(fmt);
+}
+
+int b200q_repacked_fmt(int fmt, int K) { return (fmt == kQ6_K && K > 0 && K % kQ6RunElems == 0) ? kQ6_KP : fmt; }
+
+static int repack_common(const char* op, int fmt, const void* src, void* dst, int64_t rows, int K, bool to_runs, void* stream) {
+    const int be = (fmt == kQ6_KP) ? 0 : b200q_block_elems(fmt);
+    if (!be) return fail(B200Q_ERR_BAD_ARG, "%s: fmt (%d) must be a raw block format", op, fmt);
+    if (rows < 0 || K <= 0 || K % be) return fail(B200Q_ERR_BAD_ARG, "%s: K (%d) must be a positive multiple of %d", op, K, be);
+    if (rows == 0) return B200Q_OK;
+    if (!src || !dst) return fail(B200Q_ERR_BAD_ARG, "%s: null pointer", op);
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (b200q_repacked_fmt(fmt, K) != fmt) {
+        if (!aligned(src, 2) || !aligned(dst, 2)) return fail(B200Q_ERR_BAD_ARG, "%s: pointers must be 2-byte aligned", op);
+        return launch_repack(fmt, src, dst, rows, K, to_runs, st);
+    }
+    if (src != dst) B200Q_CUDA_TRY(cudaMemcpyAsync(dst, src, b200q_packed_bytes(fmt, rows, K), cudaMemcpyDeviceToDevice, st));
+    return B200Q_OK;
+}
+int b200q_repack(int fmt, const void* src, void* dst, int64_t rows, int K, void* stream) {
+    return repack_common("repack", fmt, src, dst, rows, K, true, stream);
+}
+int b200q_unpack(int fmt, const void* src, void* dst, int64_t rows, int K, void* stream) {
+    return repack_common("unpack", fmt, src, dst, rows, K, false, stream);
 }
 
 int b200q_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows, int K, void* stream) {
@@ -149,9 +176,10 @@ int b200q_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows
     if (!be) return fail(B200Q_ERR_BAD_ARG, "dequant: unknown block format %d", fmt);
     if (!dt_ok(out_dtype)) return fail(B200Q_ERR_BAD_ARG, "dequant: unknown output dtype %d", out_dtype);
     if (rows < 0 || K <= 0 || K % be) return fail(B200Q_ERR_BAD_ARG, "dequant: K (%d) must be a positive multiple of %d", K, be);
+    if (fmt == kQ6_KP && K % kQ6RunElems) return fail(B200Q_ERR_BAD_ARG, "dequant: K (%d) must be a multiple of %d for repacked Q6_K", K, kQ6RunElems);
     if (rows == 0) return B200Q_OK;
     if (!W || !out) return fail(B200Q_ERR_BAD_ARG, "dequant: null pointer");
-    if (!aligned(W, fmt == kQ4_K ? 4 : 2)) return fail(B200Q_ERR_BAD_ARG, "dequant: W is not aligned to its block header");
+    if (!aligned(W, fmt == kQ6_KP ? 16 : fmt == kQ4_K ? 4 : 2)) return fail(B200Q_ERR_BAD_ARG, "dequant: W is not aligned to its block header");
     if (!aligned(out, 16)) return fail(B200Q_ERR_BAD_ARG, "dequant: output must be 16-byte aligned");
     DevInfo* d;
     if (int rc = dev_info(&d)) return rc;
@@ -167,7 +195,7 @@ static int gemv_streaming(DevInfo* d, int fmt, const void* W, const void* X, int
                           int y_dtype, int M, int N, int K, cudaStream_t st, bool* taken) {
     *taken = false;
     const size_t smem = d->smem_optin - 1024;
-    const bool mma_first = M >= (fmt == kQ6_K ? 4 : 3);
+    const bool mma_first = M >= ((fmt == kQ6_K || fmt == kQ6_KP) ? 4 : 3);
     if (mma_first) {
         if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, smem, d->status, st, taken)) return rc;
         if (*taken) return B200Q_OK;

@@ -20,6 +20,8 @@ namespace b200q {
 constexpr int kQ8_0 = B200Q_FMT_Q8_0;
 constexpr int kQ4_K = B200Q_FMT_Q4_K;
 constexpr int kQ6_K = B200Q_FMT_Q6_K;
+constexpr int kQ6_KP = B200Q_FMT_Q6_K_R8;  // Q6_K regrouped by field in runs of eight blocks
+constexpr int kQ6RunBytes = 1680, kQ6RunElems = 2048;
 
 // Device status codes written by kernels whose bounded waits run out.
 constexpr int kDevTimeoutFull = 101;   // consumer gave up waiting for a filled stage
@@ -39,6 +41,11 @@ struct Blk<kQ4_K> {
 template <>
 struct Blk<kQ6_K> {
     static constexpr int elems = 256, bytes = 210, align = 2;
+    static constexpr int chunk_blocks = 8;
+};
+template <>
+struct Blk<kQ6_KP> {  // per block the same 210 bytes; addressable only in whole runs of eight
+    static constexpr int elems = 256, bytes = 210, align = 16;
     static constexpr int chunk_blocks = 8;
 };
 template <>
@@ -139,6 +146,32 @@ __device__ __forceinline__ void decode8<kQ6_K>(const uint8_t* __restrict__ row, 
     const uint32_t scd = ld_nc_u16(blk + 192 + (sb & ~1));
     const int sc = (int)(signed char)((scd >> ((sb & 1) * 8)) & 0xFFu);
     const float ds = h2f(ld_nc_u16(blk + 208)) * (float)sc;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int v0 = (int)(((a0 >> (8 * k)) & 0xFu) | (((h0 >> (8 * k)) & 3u) << 4)) - 32;
+        const int v1 = (int)(((a1 >> (8 * k)) & 0xFu) | (((h1 >> (8 * k)) & 3u) << 4)) - 32;
+        w[k] = ds * (float)v0;
+        w[4 + k] = ds * (float)v1;
+    }
+}
+
+template <>
+__device__ __forceinline__ void decode8<kQ6_KP>(const uint8_t* __restrict__ row, int u, float w[8]) {
+    const int b = u >> 5;  // block along the row; run b >> 3, slot b & 7
+    const uint8_t* run = row + (size_t)(b >> 3) * kQ6RunBytes;
+    const int s = b & 7;
+    const int i = u & 31, group = i >> 4, quad = (i & 15) >> 2, l0 = (i & 3) * 8;
+    const int sb = group * 8 + quad * 2 + (l0 >> 4);
+    const uint2 a = __ldg(reinterpret_cast<const uint2*>(run + s * 128 + group * 64 + (quad & 1) * 32 + l0));
+    const uint2 h = __ldg(reinterpret_cast<const uint2*>(run + 1024 + s * 64 + group * 32 + l0));
+    uint32_t a0 = a.x, a1 = a.y;
+    const uint32_t h0 = h.x >> (quad * 2), h1 = h.y >> (quad * 2);
+    if (quad >= 2) {
+        a0 >>= 4;
+        a1 >>= 4;
+    }
+    const int sc = (int)(signed char)__ldg(run + 1536 + s * 16 + sb);
+    const float ds = h2f(ld_nc_u16(run + 1664 + 2 * s)) * (float)sc;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         const int v0 = (int)(((a0 >> (8 * k)) & 0xFu) | (((h0 >> (8 * k)) & 3u) << 4)) - 32;

@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(256) dequant_q4k_f16_kernel(const uint8_t* __r
 // each of the half's four 32-element quarters - so four 16-byte stores, and the loads and the scale
 // work of the generic path are shared by four times as many outputs. Blocks are 2-byte aligned only;
 // all loads are 16-bit pairs. d * sc * (q - 32) is exact in FP32 (11 + 7 + 6 bits), one rounding to FP16.
+template <bool RUNS>  // RUNS: the layout regrouped by field in runs of eight blocks (16-byte aligned fields)
 __global__ void __launch_bounds__(256) dequant_q6k_f16_kernel(const uint8_t* __restrict__ W, __half* __restrict__ out,
                                                               long long total_units, int units_per_row, int row_bytes, int K) {
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -96,14 +97,29 @@ __global__ void __launch_bounds__(256) dequant_q6k_f16_kernel(const uint8_t* __r
         const long long r = id / units_per_row;
         const int u = (int)(id - r * units_per_row);  // eight units per block
         const int b = u >> 3, n = (u >> 2) & 1, l0 = (u & 3) * 8;
-        const uint8_t* blk = W + (size_t)r * row_bytes + (size_t)b * 210;
-        const uint8_t* ql = blk + n * 64 + l0;
-        const uint8_t* qh = blk + 128 + n * 32 + l0;
-        const uint32_t a[2][2] = {{ld_nc_u32_a2(ql), ld_nc_u32_a2(ql + 4)}, {ld_nc_u32_a2(ql + 32), ld_nc_u32_a2(ql + 36)}};
-        const uint32_t h[2] = {ld_nc_u32_a2(qh), ld_nc_u32_a2(qh + 4)};
-        // the half's eight sub-block scales; quarter q of positions l0.. uses scale (l0 >> 4) + 2 q
-        const uint8_t* sp = blk + 192 + n * 8 + (l0 >> 4);
-        const float d = h2f(ld_nc_u16(blk + 208));
+        uint32_t a[2][2], h[2];
+        const uint8_t* sp;  // the half's eight sub-block scales; quarter q of positions l0.. uses scale (l0 >> 4) + 2 q
+        float d;
+        if constexpr (RUNS) {
+            const uint8_t* run = W + (size_t)r * row_bytes + (size_t)(b >> 3) * kQ6RunBytes;
+            const int s = b & 7;
+            const uint2 a0 = __ldg(reinterpret_cast<const uint2*>(run + s * 128 + n * 64 + l0));
+            const uint2 a1 = __ldg(reinterpret_cast<const uint2*>(run + s * 128 + n * 64 + 32 + l0));
+            const uint2 hh = __ldg(reinterpret_cast<const uint2*>(run + 1024 + s * 64 + n * 32 + l0));
+            a[0][0] = a0.x; a[0][1] = a0.y; a[1][0] = a1.x; a[1][1] = a1.y;
+            h[0] = hh.x; h[1] = hh.y;
+            sp = run + 1536 + s * 16 + n * 8 + (l0 >> 4);
+            d = h2f(ld_nc_u16(run + 1664 + 2 * s));
+        } else {
+            const uint8_t* blk = W + (size_t)r * row_bytes + (size_t)b * 210;
+            const uint8_t* ql = blk + n * 64 + l0;
+            const uint8_t* qh = blk + 128 + n * 32 + l0;
+            a[0][0] = ld_nc_u32_a2(ql); a[0][1] = ld_nc_u32_a2(ql + 4);
+            a[1][0] = ld_nc_u32_a2(ql + 32); a[1][1] = ld_nc_u32_a2(ql + 36);
+            h[0] = ld_nc_u32_a2(qh); h[1] = ld_nc_u32_a2(qh + 4);
+            sp = blk + 192 + n * 8 + (l0 >> 4);
+            d = h2f(ld_nc_u16(blk + 208));
+        }
         __half* o = out + (size_t)r * K + (size_t)b * 256 + n * 128 + l0;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -145,12 +161,12 @@ static int launch_dequant_fmt(const void* W, void* out, int out_dtype, int64_t r
             return B200Q_OK;
         }
     }
-    if constexpr (FMT == kQ6_K) {
+    if constexpr (FMT == kQ6_K || FMT == kQ6_KP) {
         if (out_dtype == B200Q_DT_F16 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && K % 8 == 0) {
             const long long total_units = (long long)rows * (K / 32);
             long long nb = (total_units + 255) / 256;
             if (nb > cap) nb = cap;
-            dequant_q6k_f16_kernel<<<(unsigned)nb, 256, 0, st>>>(w, (__half*)out, total_units, K / 32, row_bytes, K);
+            dequant_q6k_f16_kernel<FMT == kQ6_KP><<<(unsigned)nb, 256, 0, st>>>(w, (__half*)out, total_units, K / 32, row_bytes, K);
             B200Q_CUDA_TRY(cudaGetLastError());
             return B200Q_OK;
         }
@@ -177,6 +193,7 @@ int launch_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t row
     switch (fmt) {
         case kQ4_K: return launch_dequant_fmt<kQ4_K>(W, out, out_dtype, rows, K, st);
         case kQ6_K: return launch_dequant_fmt<kQ6_K>(W, out, out_dtype, rows, K, st);
+        case kQ6_KP: return launch_dequant_fmt<kQ6_KP>(W, out, out_dtype, rows, K, st);
         case kQ8_0: return launch_dequant_fmt<kQ8_0>(W, out, out_dtype, rows, K, st);
     }
     return fail(B200Q_ERR_BAD_ARG, "dequant: unknown block format %d", fmt);

@@ -209,6 +209,7 @@ static bool gemm_tc_takes(int fmt, const void* W, int M, int K) {
     if (M <= 8) return false;                 // small batches stream the weight through the decode GEMV
     if (K % 256 != 0) return false;
     if ((reinterpret_cast<uintptr_t>(W) & 15) != 0) return false;  // the producers load aligned words / 16-byte blocks
+    if (fmt == kQ6_KP) return K % kQ6RunElems == 0;
     return fmt == kQ4_K || fmt == kQ6_K || fmt == kQ8_0;
 }
 
@@ -284,6 +285,7 @@ int launch_gemm_tc(int fmt, const void* W, const void* X, int x_dtype, const voi
         int rc;
         if (fmt == kQ4_K) rc = launch_gemm_fmt<kQ4_K>(p, smem, st);
         else if (fmt == kQ6_K) rc = launch_gemm_fmt<kQ6_K>(p, smem, st);
+        else if (fmt == kQ6_KP) rc = launch_gemm_fmt<kQ6_KP>(p, smem, st);
         else rc = launch_gemm_fmt<kQ8_0>(p, smem, st);
         if (rc) return rc;
     }

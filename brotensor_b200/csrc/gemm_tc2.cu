@@ -329,6 +329,19 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
         uint32_t s6 = 0, d6 = 0, f6 = 0, s6n = 0, d6n = 0, f6n = 0;
         auto q6_load = [&](int kbb, uint4 (&L)[3], uint4 (&Hh)[3], uint32_t& S, uint32_t& D, uint32_t& F) {
             const int blk = kbb >> 2, P = kbb & 3, grp = P >> 1, quad = 2 * (P & 1) + H;
+            if constexpr (FMT == kQ6_KP) {
+                // regrouped by field in runs of eight blocks: both 32-byte pieces are 16-byte aligned
+                const uint8_t* run = rowp + (size_t)(blk >> 3) * kQ6RunBytes;
+                const int s = blk & 7;
+                const uint4* al = reinterpret_cast<const uint4*>(run + s * 128 + 64 * grp + 32 * H);
+                const uint4* ah = reinterpret_cast<const uint4*>(run + 1024 + s * 64 + 32 * grp);
+                L[0] = __ldg(al); L[1] = __ldg(al + 1);
+                Hh[0] = __ldg(ah); Hh[1] = __ldg(ah + 1);
+                S = __ldg(reinterpret_cast<const unsigned short*>(run + 1536 + s * 16 + grp * 8 + quad * 2));
+                D = __ldg(reinterpret_cast<const unsigned short*>(run + 1664 + 2 * s));
+                F = 0;
+                return;
+            }
             const uint8_t* b0 = rowp + (size_t)blk * 210;
             F = (uint32_t)(reinterpret_cast<uintptr_t>(b0) & 15u);
             const uint4* al = reinterpret_cast<const uint4*>(b0 - F);
@@ -341,9 +354,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
         };
 #pragma unroll
         for (int i = 0; i < 3; ++i) l6[i] = h6[i] = l6n[i] = h6n[i] = make_uint4(0, 0, 0, 0);
-        if constexpr (FMT == kQ6_K) q6_load(0, l6n, h6n, s6n, d6n, f6n);
+        if constexpr (FMT == kQ6_K || FMT == kQ6_KP) q6_load(0, l6n, h6n, s6n, d6n, f6n);
         for (int kb = 0; kb < n_kb; ++kb) {
-            if constexpr (FMT == kQ6_K) {
+            if constexpr (FMT == kQ6_K || FMT == kQ6_KP) {
 #pragma unroll
                 for (int i = 0; i < 3; ++i) { l6[i] = l6n[i]; h6[i] = h6n[i]; }
                 s6 = s6n; d6 = d6n; f6 = f6n;
@@ -399,6 +412,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                     // switch (the same for every lane when rows are a multiple of 16 bytes), two bytes by the shift
                     const uint32_t bits = (f6 & 2u) * 8u;
                     uint32_t ql[8], qh[8];
+                    if constexpr (FMT == kQ6_KP) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) { ql[i] = wl[i]; qh[i] = wh[i]; }
+                    } else
                     switch (f6 >> 2) {
                         case 0: for (int i = 0; i < 8; ++i) { ql[i] = __funnelshift_r(wl[i], wl[i + 1], bits); qh[i] = __funnelshift_r(wh[i], wh[i + 1], bits); } break;
                         case 1: for (int i = 0; i < 8; ++i) { ql[i] = __funnelshift_r(wl[1 + i], wl[2 + i], bits); qh[i] = __funnelshift_r(wh[1 + i], wh[2 + i], bits); } break;
@@ -524,6 +541,7 @@ int launch_gemm_pair_pass(int fmt, const void* W, const uint8_t* Xp, int tok_str
     const size_t smem = (size_t)p.n_a * kb_a + (size_t)p.n_b * p.b_bytes + 1024;
     if (fmt == kQ4_K) return launch_pair_fmt<kQ4_K>(p, smem, st);
     if (fmt == kQ6_K) return launch_pair_fmt<kQ6_K>(p, smem, st);
+    if (fmt == kQ6_KP) return launch_pair_fmt<kQ6_KP>(p, smem, st);
     return launch_pair_fmt<kQ8_0>(p, smem, st);
 }
 

@@ -116,7 +116,7 @@ __device__ __forceinline__ void x_store_seg(const StreamParams& p, uint32_t sbas
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         if ((i & 3) == 0) sts32(sbase + p.off_sxhi + (uint32_t)(m * (p.K >> 5) + (seg >> 2)) * 4, (uint32_t)sum);
-    } else if constexpr (FMT == kQ6_K) {  // sums over 16 elements = 2 segments
+    } else if constexpr (FMT == kQ6_K || FMT == kQ6_KP) {  // sums over 16 elements = 2 segments
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         if ((i & 1) == 0) sts32(sbase + p.off_sxhi + (uint32_t)(m * (p.K >> 4) + (seg >> 1)) * 4, (uint32_t)sum);
     }
@@ -417,6 +417,52 @@ __device__ __forceinline__ void item_q6k_half(uint32_t rowA, uint32_t rowB, int 
     }
 }
 
+// The same half-group item on the layout regrouped by field in runs of eight blocks (b200q_repack):
+// every field sits on a 16-byte boundary, so the item's bytes come in three 16-byte loads, one
+// 8-byte load and one word per row instead of nineteen words and fourteen funnel shifts.
+template <int MT>
+__device__ __forceinline__ void item_q6kp_half(uint32_t rowA, uint32_t rowB, int gi, int H, int gg, const XAddr& xa,
+                                               float (&acc)[2][MT]) {
+    const int run = gi >> 4, bi = (gi >> 1) & 7, G = gi & 1;  // sixteen groups per run; block slot; half of the block
+    uint32_t ql[2][8], qh[2][4], su[2][2];
+    float d[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint32_t R = (r ? rowB : rowA) + (uint32_t)(run * kQ6RunBytes);
+        // The two 16-byte pieces sit 32 bytes apart and groups 64 bytes apart, so with every lane
+        // reading its first piece first a warp would touch four of the eight 16-byte bank groups;
+        // lanes of odd blocks read the second piece first and swap afterwards.
+        const uint32_t sw = (uint32_t)(bi & 1);
+        const uint32_t pa = R + (uint32_t)(bi * 128 + 64 * G + 16 * H);
+        const uint4 t0 = lds128i<0>(pa + 32u * sw), t1 = lds128i<0>(pa + 32u * (sw ^ 1u));
+        const uint4 a = sw ? t1 : t0, b = sw ? t0 : t1;
+        const uint4 h = lds128i<1024>(R + (uint32_t)(bi * 64 + 32 * G + 16 * H));
+        const uint2 sc = lds64(R + (uint32_t)(1536 + bi * 16 + 8 * G));
+        const uint32_t dw = lds32i<1664>(R + (uint32_t)((bi >> 1) * 4));
+        ql[r][0] = a.x; ql[r][1] = a.y; ql[r][2] = a.z; ql[r][3] = a.w;
+        ql[r][4] = b.x; ql[r][5] = b.y; ql[r][6] = b.z; ql[r][7] = b.w;
+        qh[r][0] = h.x; qh[r][1] = h.y; qh[r][2] = h.z; qh[r][3] = h.w;
+        su[r][0] = sc.x ^ 0x80808080u;
+        su[r][1] = sc.y ^ 0x80808080u;
+        d[r] = h2f((dw >> ((bi & 1) * 16)) & 0xFFFFu);
+    }
+    float accg[2][MT];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) accg[r][m] = 0.f;
+    q6_sub_h<MT, 0>(ql, qh, su, H, gg, xa, accg);
+    q6_sub_h<MT, 1>(ql, qh, su, H, gg, xa, accg);
+    q6_sub_h<MT, 2>(ql, qh, su, H, gg, xa, accg);
+    q6_sub_h<MT, 3>(ql, qh, su, H, gg, xa, accg);
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const float xs = __uint_as_float(lds32i<0>(xa.xsc + (uint32_t)(m * xa.groups + gg) * 4u));
+#pragma unroll
+        for (int r = 0; r < 2; ++r) acc[r][m] = fmaf(d[r] * xs, accg[r][m], acc[r][m]);
+    }
+}
+
 // Sharded epilogue, run by all `nthreads` consumer threads of a CTA (thread ids 0 .. nthreads-1) after
 // they have stored the CTA's rows [row_begin, row_end) into this rank's result vector.
 __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_begin, int row_end, unsigned int sh_epoch,
@@ -628,11 +674,14 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                     rowA[pi] = ring + (uint32_t)(slot * stage_bytes + ra * p.row_stride);
                     rowB[pi] = (ra + 1 < nrows) ? rowA[pi] + (uint32_t)p.row_stride : rowA[pi];
                 }
-                if constexpr (FMT == kQ6_K) {
+                if constexpr (FMT == kQ6_K || FMT == kQ6_KP) {
                     // half-group units: lanes 0..15 take H = 0 of sixteen groups, lanes 16..31 H = 1
                     for (int gi = (lane & 15); gi < ng; gi += 16) {
 #pragma unroll
-                        for (int pi = 0; pi < RP; ++pi) item_q6k_half<MT>(rowA[pi], rowB[pi], gi, lane >> 4, g0 + gi, xa, acc[pi]);
+                        for (int pi = 0; pi < RP; ++pi) {
+                            if constexpr (FMT == kQ6_K) item_q6k_half<MT>(rowA[pi], rowB[pi], gi, lane >> 4, g0 + gi, xa, acc[pi]);
+                            else item_q6kp_half<MT>(rowA[pi], rowB[pi], gi, lane >> 4, g0 + gi, xa, acc[pi]);
+                        }
                     }
                 } else {
                     // (half-group units were measured for Q4_K as well: its items are cheap enough that
@@ -714,7 +763,7 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
     size_t off = 0;
     p.off_xhi = (int)off; off += ((size_t)kXGroupStride * (K / 128) * M + 127) & ~size_t(127);  // int16 activations
     p.off_xlo = (int)off; off += (((size_t)4 * (K / 128) * M) + 127) & ~size_t(127);            // per-group 2^-e
-    const size_t sums = FMT == kQ4_K ? (size_t)4 * (K / 32) * M : FMT == kQ6_K ? (size_t)4 * (K / 16) * M : 0;
+    const size_t sums = FMT == kQ4_K ? (size_t)4 * (K / 32) * M : (FMT == kQ6_K || FMT == kQ6_KP) ? (size_t)4 * (K / 16) * M : 0;
     p.off_sxhi = (int)off; off += (sums + 127) & ~size_t(127);
     p.off_sxlo = p.off_red = (int)off;
     p.off_stage = (int)off;
@@ -729,7 +778,7 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
     int want = stream_get_option(0);
     want = want < 2 ? 2 : (want > kMaxStages ? kMaxStages : want);
     int best = 0;
-    constexpr int glanes = FMT == kQ6_K ? 16 : 32;  // groups that keep a warp's 32 lanes busy (Q6_K: half-group units)
+    constexpr int glanes = (FMT == kQ6_K || FMT == kQ6_KP) ? 16 : 32;  // groups that keep a warp's 32 lanes busy (Q6_K: half-group units)
     for (int sc = 1; sc <= cpr; ++sc) {
         const int groups = sc * gpc;
         if (groups % glanes != 0 && sc != cpr && groups < glanes) continue;
@@ -781,7 +830,7 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
     // measured on B200: Q4_K and Q8_0 gain at every stream length (14336 x 4096 Q4_K 8.75 -> 8.0 us,
     // 128256 x 4096 48.5 -> 46.5 us); Q6_K gains on short whole-row streams only
     p.split_full = g_opt_split_full >= 0 ? g_opt_split_full
-                   : FMT != kQ6_K        ? 1
+                   : (FMT != kQ6_K && FMT != kQ6_KP) ? 1
                                          : (p.n_slices == 1 && stages_seen <= kSplitFullMaxStages ? 1 : 0);
     smem = off + (size_t)ns * ng * sb + 128;
     return true;
@@ -880,6 +929,7 @@ int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const voi
     switch (fmt) {
         case kQ4_K: return launch_dp_f<kQ4_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
         case kQ6_K: return launch_dp_f<kQ6_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
+        case kQ6_KP: return launch_dp_f<kQ6_KP>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
         case kQ8_0: return launch_dp_f<kQ8_0>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
     }
     return fail(B200Q_ERR_BAD_ARG, "gemv: unknown block format %d", fmt);
@@ -934,6 +984,7 @@ int launch_gemv_dp_multi(int fmt, int n_seg, const void* const* W, const int* N,
     switch (fmt) {
         case kQ4_K: return launch_dp_multi_f<kQ4_K>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);
         case kQ6_K: return launch_dp_multi_f<kQ6_K>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);
+        case kQ6_KP: return launch_dp_multi_f<kQ6_KP>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);
         case kQ8_0: return launch_dp_multi_f<kQ8_0>(n_seg, W, N, Y, bias, X, x_dtype, y_dtype, K, sms, smem_max, status, st, taken);
     }
     return fail(B200Q_ERR_BAD_ARG, "gemv_multi: unknown block format %d", fmt);

@@ -637,6 +637,7 @@ static int launch_stream_f(const void* W, const void* X, int x_dtype, const void
 int launch_gemv_stream(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
                        int M, int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken) {
     *taken = false;
+    if (fmt == kQ6_KP) return B200Q_OK;  // the regrouped Q6_K layout is read by the integer-dot kernel only
     if ((reinterpret_cast<uintptr_t>(W) & 15) != 0) return B200Q_OK;  // bulk copies need 16-byte aligned rows
     switch (fmt) {
         case kQ4_K: return launch_stream_f<kQ4_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken);

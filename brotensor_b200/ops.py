@@ -28,6 +28,29 @@ def _check_w(fmt: int, W: torch.Tensor, N: int, K: int) -> None:
         raise ValueError(f"W holds {W.numel()} bytes, ({N}, {K}) needs {need}")
 
 
+def repacked_fmt(fmt: int, K: int) -> int:
+    """Format code of the device-side repacked form of raw format `fmt` for rows of K elements (`fmt` itself: none)."""
+    return capi.lib().b200q_repacked_fmt(fmt, K)
+
+
+def repack(fmt: int, W: torch.Tensor, N: int, K: int, inplace: bool = False) -> torch.Tensor:
+    """Raw GGUF rows -> the layout the kernels read fastest (same size, bit-identical content)."""
+    _check_w(fmt, W, N, K)
+    out = W if inplace else torch.empty_like(W)
+    with torch.cuda.device(W.device):
+        capi.check(capi.lib().b200q_repack(fmt, W.data_ptr(), out.data_ptr(), N, K, _stream()))
+    return out
+
+
+def unpack(fmt: int, W: torch.Tensor, N: int, K: int, inplace: bool = False) -> torch.Tensor:
+    """Inverse of repack; `fmt` is the raw format."""
+    _check_w(fmt, W, N, K)
+    out = W if inplace else torch.empty_like(W)
+    with torch.cuda.device(W.device):
+        capi.check(capi.lib().b200q_unpack(fmt, W.data_ptr(), out.data_ptr(), N, K, _stream()))
+    return out
+
+
 def dequant(fmt: int, W: torch.Tensor, N: int, K: int, out_dtype=torch.float16) -> torch.Tensor:
     _check_w(fmt, W, N, K)
     out = torch.empty((N, K), dtype=out_dtype, device=W.device)

@@ -11,9 +11,10 @@ from __future__ import annotations
 import numpy as np
 
 Q8_0, Q4_K, Q6_K = 14, 22, 24
-BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q6_K: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210}
-FMT_NAME = {Q8_0: "q8_0", Q4_K: "q4k", Q6_K: "q6k"}
+Q6_K_R8 = 124  # device-side regrouped form of Q6_K (same bytes per block; see include/b200q.h)
+BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q6_K: 256, Q6_K_R8: 256}
+BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210, Q6_K_R8: 210}
+FMT_NAME = {Q8_0: "q8_0", Q4_K: "q4k", Q6_K: "q6k", Q6_K_R8: "q6k_r8"}
 
 
 def packed_bytes(fmt: int, rows: int, K: int) -> int:

@@ -40,6 +40,14 @@ extern "C" {
 #define B200Q_FMT_Q8_0 14 /*  32 elements /  34 B: fp16 d, int8 qs[32]                       */
 #define B200Q_FMT_Q4_K 22 /* 256 elements / 144 B: fp16 d, fp16 dmin, u8 scales[12], u8 qs[128] */
 #define B200Q_FMT_Q6_K 24 /* 256 elements / 210 B: u8 ql[128], u8 qh[64], i8 scales[16], fp16 d */
+/*
+ * Q6_K repacked on the device in runs of eight blocks (b200q_repack): the same 1680 bytes per run,
+ * regrouped by field - ql[8][128] @0, qh[8][64] @1024, scales[8][16] @1536, fp16 d[8] @1664 - so that
+ * every field starts on a 16-byte boundary (raw Q6_K blocks are only 2-byte aligned). Content is
+ * bit-identical (a byte permutation inside each run; b200q_unpack inverts it); K must be a multiple
+ * of 2048. Accepted wherever B200Q_FMT_Q6_K is, except that W must be 16-byte aligned.
+ */
+#define B200Q_FMT_Q6_K_R8 124
 
 /* Activation / output element types; the values are brotensor's Dtype tags. */
 #define B200Q_DT_F32 0
@@ -53,6 +61,20 @@ const char* b200q_last_error(void);
 int b200q_block_elems(int fmt);                          /* 0 for an unknown format */
 int b200q_block_bytes(int fmt);                          /* 0 for an unknown format */
 size_t b200q_packed_bytes(int fmt, int64_t rows, int K); /* 0 if K is not a multiple of the block */
+
+/*
+ * Device-side repack of uploaded GGUF rows into the layout the kernels read fastest, and its inverse.
+ * b200q_repacked_fmt: the format code of the repacked form of `fmt` for rows of K elements - Q6_K ->
+ * Q6_K_R8 when K is a multiple of 2048; Q4_K and Q8_0 (whose bulk-copy granules are 16-byte aligned
+ * as stored) and every other case return `fmt` itself, i.e. nothing to do. b200q_repack / b200q_unpack
+ * move rows x K from `src` to `dst` (same byte count, b200q_packed_bytes; `dst == src` is allowed: a
+ * run is read completely before it is written), `fmt` being the RAW format in both calls; with
+ * nothing to do they copy (or return at once in place). No counterpart in the reference, which keeps
+ * the raw layout (its kernels read Q6_K with 16-bit loads, src/cuda/detail/load_align.cuh:21-25).
+ */
+int b200q_repacked_fmt(int fmt, int K);
+int b200q_repack(int fmt, const void* src, void* dst, int64_t rows, int K, void* stream);
+int b200q_unpack(int fmt, const void* src, void* dst, int64_t rows, int K, void* stream);
 
 /*
  * Block decode. W: rows x K quantized, row-major [rows][K/elems][block bytes];

@@ -410,3 +410,58 @@ def test_grouped_gemv_argument_checks():
     x = torch.zeros(K, device="cuda")
     with pytest.raises(Exception):
         ops.gemv_multi(fmt, [W] * 5, x, [16] * 5)       # more than four matrices
+
+
+# ---- device-side repack (Q6_K regrouped by field in runs of eight blocks) ------------------------
+
+def _q6_runs_on_host(raw: np.ndarray) -> np.ndarray:
+    """The regrouped layout restated with numpy: per run of eight 210-byte blocks,
+    ql[8][128] | qh[8][64] | scales[8][16] | d[8][2]."""
+    b = raw.reshape(-1, 8, 210)
+    return np.concatenate([b[:, :, :128].reshape(-1, 1024), b[:, :, 128:192].reshape(-1, 512),
+                           b[:, :, 192:208].reshape(-1, 128), b[:, :, 208:210].reshape(-1, 16)], axis=1).reshape(-1)
+
+
+@pytest.mark.parametrize("N,K", [(1, 2048), (37, 4096), (300, 14336)])
+def test_repack_q6k_is_a_permutation_and_round_trips(N, K):
+    raw = synth.make_blocks(synth.Q6_K, N, K, seed=N + K)
+    assert ops.repacked_fmt(synth.Q6_K, K) == synth.Q6_K_R8
+    packed = ops.repack(synth.Q6_K, dev(raw), N, K)
+    assert np.array_equal(packed.cpu().numpy(), _q6_runs_on_host(raw))
+    back = ops.unpack(synth.Q6_K, packed, N, K)
+    assert np.array_equal(back.cpu().numpy(), raw)
+    # in place, both directions
+    w = dev(raw).clone()
+    ops.repack(synth.Q6_K, w, N, K, inplace=True)
+    assert np.array_equal(w.cpu().numpy(), _q6_runs_on_host(raw))
+    ops.unpack(synth.Q6_K, w, N, K, inplace=True)
+    assert np.array_equal(w.cpu().numpy(), raw)
+
+
+def test_repack_without_a_regrouped_form_copies():
+    for fmt, K in ((synth.Q4_K, 1024), (synth.Q8_0, 256), (synth.Q6_K, 768)):
+        assert ops.repacked_fmt(fmt, K) == fmt
+        raw = synth.make_blocks(fmt, 9, K, seed=3)
+        assert np.array_equal(ops.repack(fmt, dev(raw), 9, K).cpu().numpy(), raw)
+        assert np.array_equal(ops.unpack(fmt, dev(raw), 9, K).cpu().numpy(), raw)
+
+
+@pytest.mark.parametrize("N,K", [(40, 2048), (1000, 4096), (148 * 16 + 3, 2048), (64, 14336)])
+def test_repacked_q6k_gives_the_same_bits(N, K, cpu_oracle):
+    """Every op on the regrouped layout equals the op on the raw layout bit for bit: decode,
+    decode GEMV (1..8 rows), sharded-form arguments aside, and the prefill GEMM."""
+    raw = synth.make_blocks(synth.Q6_K, N, K, seed=N * 3 + K)
+    Wr = dev(raw)
+    Wp = ops.repack(synth.Q6_K, Wr, N, K)
+    for dt in (torch.float16, torch.float32, torch.bfloat16):
+        assert torch.equal(ops.dequant(synth.Q6_K_R8, Wp, N, K, out_dtype=dt), ops.dequant(synth.Q6_K, Wr, N, K, out_dtype=dt))
+    for M in (1, 2, 4, 8):
+        X = dev(synth.make_activations(M, K, seed=M))
+        got = ops.gemv(synth.Q6_K_R8, Wp, X, N)
+        want = cpu_oracle.matmul(synth.Q6_K, raw, X.cpu().numpy(), threads=8)
+        assert oracle.rel_l2(host_f32(got), want) < REL_L2
+        if M <= 2:  # the same kernel and the same order of arithmetic on both layouts
+            assert torch.equal(got, ops.gemv(synth.Q6_K, Wr, X, N))
+    X = dev(synth.make_activations(48, K, seed=7))
+    assert torch.equal(ops.gemm(synth.Q6_K_R8, Wp, X, N), ops.gemm(synth.Q6_K, Wr, X, N))
+    assert ops.device_status() == 0
