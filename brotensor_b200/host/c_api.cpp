@@ -12,6 +12,7 @@
 #include "brotensor_b200/gguf.h"
 #include "brotensor_b200/ops/quant.h"
 #include "brotensor_b200/runtime.h"
+#include "brotensor_b200/repack.h"
 #include "brotensor_b200/sharded_head.h"
 
 using namespace brotensor_b200;
@@ -71,6 +72,18 @@ void* b200h_weight_view(int fmt, void* dev_bytes, int rows, int cols, int device
     return t;
 }
 void b200h_tensor_free(void* t) { delete static_cast<Tensor*>(t); }
+// repack_weights / unpack_weights / is_repacked on a weight handle (include/brotensor_b200/repack.h).
+// b200h_weight_repack returns 1 when the weight is in the regrouped layout afterwards, 0 when its
+// format has none, -1 on error.
+int b200h_weight_repack(void* t) {
+    int r = 0;
+    if (guarded([&] { r = repack_weights(*static_cast<Tensor*>(t)) ? 1 : 0; })) return -1;
+    return r;
+}
+int b200h_weight_unpack(void* t) {
+    return guarded([&] { unpack_weights(*static_cast<Tensor*>(t)); });
+}
+int b200h_weight_is_repacked(void* t) { return is_repacked(*static_cast<Tensor*>(t)) ? 1 : 0; }
 void* b200h_tensor_data(void* t) { return static_cast<Tensor*>(t)->data; }
 int b200h_tensor_rows(void* t) { return static_cast<Tensor*>(t)->rows; }
 int b200h_tensor_cols(void* t) { return static_cast<Tensor*>(t)->cols; }

@@ -12,6 +12,7 @@
 #include "b200q.h"
 #include "brotensor_b200/detail/dispatch.h"
 #include "brotensor_b200/runtime.h"
+#include "brotensor_b200/repack.h"
 
 namespace brotensor_b200::detail {
 
@@ -148,13 +149,19 @@ void* scratch_for(int dev, std::size_t need) {
     return s.p;
 }
 
+// The format code the kernels get: the raw one, or the regrouped one when W's storage is recorded as
+// repacked (repack_weights).
+int layout_fmt(int fmt, const Tensor& W) {
+    return (fmt == B200Q_FMT_Q6_K && is_repacked(W)) ? B200Q_FMT_Q6_K_R8 : fmt;
+}
+
 void dequant_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op, const Tensor& W, Tensor& out) {
     check_w(W, wdt, dname, block, op);
     // keep a pre-sized FP32 / BF16 destination, otherwise FP16 as in the reference
     const bool keep = out.rows == W.rows && out.cols == W.cols && act_dtype(out.dtype) && out.data;
     if (!keep) out.resize(W.rows, W.cols, Dtype::FP16);
     if (W.rows == 0) return;
-    check_status(b200q_dequant(fmt, W.data, out.data, static_cast<int>(out.dtype), W.rows, W.cols,
+    check_status(b200q_dequant(layout_fmt(fmt, W), W.data, out.data, static_cast<int>(out.dtype), W.rows, W.cols,
                                cuda_current_stream(W.device.index)), op);
 }
 
@@ -172,7 +179,7 @@ void gemv_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op,
     if (!keep) y.resize(out, 1, x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
     if (out == 0) return;
     const void* b = (bias && bias->size() > 0) ? bias->data : nullptr;
-    check_status(b200q_gemv(fmt, W.data, x.data, static_cast<int>(x.dtype), b, y.data, static_cast<int>(y.dtype), 1, out,
+    check_status(b200q_gemv(layout_fmt(fmt, W), W.data, x.data, static_cast<int>(x.dtype), b, y.data, static_cast<int>(y.dtype), 1, out,
                             K, cuda_current_stream(W.device.index)), op);
 }
 
@@ -202,12 +209,13 @@ void group_impl(const Tensor* const* W, const Tensor* const* bias, int n, const 
         }
         const bool keep = y[s]->rows == out && y[s]->cols == 1 && y[s]->dtype == ydt && y[s]->data;
         if (!keep) y[s]->resize(out, 1, ydt);
+        if (is_repacked(*W[s]) != is_repacked(*W[0])) op_fail(op, "all matrices must be in the same layout (repack_weights on all or none)");
         Wp[s] = W[s]->data;
         Yp[s] = y[s]->data;
         Bp[s] = (b && b->size() > 0) ? b->data : nullptr;
         Np[s] = out;
     }
-    check_status(b200q_gemv_multi(static_cast<int>(wdt), n, Wp, Np, Yp, Bp, x.data, static_cast<int>(x.dtype), static_cast<int>(ydt), K,
+    check_status(b200q_gemv_multi(layout_fmt(static_cast<int>(wdt), *W[0]), n, Wp, Np, Yp, Bp, x.data, static_cast<int>(x.dtype), static_cast<int>(ydt), K,
                                   cuda_current_stream(W[0]->device.index)), op);
 }
 
@@ -227,9 +235,10 @@ void batched_impl(int fmt, Dtype wdt, const char* dname, int block, const char* 
     if (B == 0 || out == 0) return;
     const void* b = (bias && bias->size() > 0) ? bias->data : nullptr;
     const int dev = W.device.index;
-    std::size_t need = B > 8 ? b200q_gemm_workspace_bytes(fmt, static_cast<int>(X.dtype), B, out, K) : 0;
+    const int lf = layout_fmt(fmt, W);
+    std::size_t need = B > 8 ? b200q_gemm_workspace_bytes(lf, static_cast<int>(X.dtype), B, out, K) : 0;
     void* ws = scratch_for(dev, need);
-    check_status(b200q_linear(fmt, W.data, X.data, static_cast<int>(X.dtype), b, Y.data, static_cast<int>(Y.dtype), B,
+    check_status(b200q_linear(lf, W.data, X.data, static_cast<int>(X.dtype), b, Y.data, static_cast<int>(Y.dtype), B,
                               out, K, ws, need, cuda_current_stream(dev)), op);
 }
 

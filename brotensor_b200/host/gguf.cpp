@@ -8,6 +8,7 @@
 // asynchronous copies, so reading the file overlaps the transfer, and a contiguous row
 // range of a tensor can be uploaded on its own (the shard of a row-sharded weight).
 #include "brotensor_b200/gguf.h"
+#include "brotensor_b200/repack.h"
 
 #include <cuda_runtime_api.h>
 #include <fcntl.h>
@@ -354,6 +355,11 @@ void upload_rows(const TensorInfo& info, int rows, int cols, int row_begin, int 
     }
     dst = Tensor::empty_on(target, n, cols, info.dtype);
     if (nbytes) staged_upload(dst.data, src, nbytes, target.index);
+}
+
+void upload_rows_repacked(const TensorInfo& info, int rows, int cols, int row_begin, int row_end, Device target, Tensor& dst) {
+    upload_rows(info, rows, cols, row_begin, row_end, target, dst);
+    if (target.is_cuda() && dtype_is_quant(dst.dtype)) (void)repack_weights(dst);
 }
 
 void upload_raw(const TensorInfo& info, int rows, int cols, Tensor& dst) {

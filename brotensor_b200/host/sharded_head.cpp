@@ -1,5 +1,6 @@
 // ShardedHead: exchange-memory set-up over CUDA IPC and the one-kernel forward.
 #include "brotensor_b200/sharded_head.h"
+#include "brotensor_b200/repack.h"
 
 #include <cuda_runtime_api.h>
 
@@ -94,7 +95,8 @@ void ShardedHead::forward_with(const Tensor& W, const Tensor& x, const Tensor* b
     if (bias_shard && (bias_shard->dtype != x.dtype || bias_shard->rows * bias_shard->cols != W_->rows))
         throw std::runtime_error("brotensor: sharded_head: bias must hold this shard's rows in x's dtype");
     cuda_check(cudaSetDevice(W_->device.index), "cudaSetDevice");
-    const int rc = b200q_gemv_shard(static_cast<int>(W.dtype), W.data, x.data, dt_code(x.dtype),
+    const int wfmt = (W.dtype == Dtype::Q6_K && is_repacked(W)) ? B200Q_FMT_Q6_K_R8 : static_cast<int>(W.dtype);
+    const int rc = b200q_gemv_shard(wfmt, W.data, x.data, dt_code(x.dtype),
                                     bias_shard ? bias_shard->data : nullptr, W_->rows, W_->cols, row_offset_, total_rows_,
                                     rank_, world_, peer_out_.data(), peer_flags_.data(), state_, cuda_current_stream());
     if (rc != B200Q_OK) throw std::runtime_error(std::string("brotensor: sharded_head: ") + b200q_last_error());

@@ -8,6 +8,7 @@
 #include <utility>
 
 #include "brotensor_b200/detail/dispatch.h"
+#include "brotensor_b200/repack.h"
 #include "brotensor_b200/runtime.h"
 
 namespace brotensor_b200 {
@@ -71,7 +72,10 @@ std::string to_string(Device d) {
 // ---- lifecycle ---------------------------------------------------------------------
 
 void Tensor::release_() {
-    if (owns_ && data) detail::alloc_for(device).free(data, device.index);
+    if (owns_ && data) {
+        detail::forget_repacked(data);  // a later allocation at this address starts in the GGUF layout
+        detail::alloc_for(device).free(data, device.index);
+    }
     data = nullptr;
     owns_ = false;
     cap_bytes_ = 0;
@@ -163,6 +167,8 @@ Tensor Tensor::to(Device target) const {
     else if (target.is_cpu()) detail::alloc_for(device).memcpy_d2h(t.data, data, n, device.index);
     else if (device == target) detail::alloc_for(device).memcpy_d2d(t.data, data, n, device.index);
     else detail::alloc_for(device).memcpy_peer(t.data, target.index, data, device.index, n);
+    // a byte copy of a whole regrouped weight is a regrouped weight
+    if (dtype_is_quant(dtype) && detail::repacked_ptr(data)) detail::mark_repacked(t.data, n);
     return t;
 }
 

@@ -28,6 +28,10 @@ def lib() -> C.CDLL:
         L.b200h_tensor_free.argtypes = [C.c_void_p]
         L.b200h_weight_view.restype = C.c_void_p
         L.b200h_weight_view.argtypes = [C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        L.b200h_weight_repack.argtypes = [C.c_void_p]
+        L.b200h_weight_unpack.argtypes = [C.c_void_p]
+        L.b200h_weight_is_repacked.argtypes = [C.c_void_p]
+        L.b200h_tensor_to_host.argtypes = [C.c_void_p, C.c_void_p]
         L.b200h_tensor_data.restype = C.c_void_p
         L.b200h_tensor_data.argtypes = [C.c_void_p]
         L.b200h_dequant.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
@@ -95,6 +99,27 @@ class Weight:
         _check(bool(self.h))
         self.fmt, self.rows, self.cols = fmt, rows, cols
         return self
+
+    def repack(self) -> bool:
+        """brotensor_b200::repack_weights: regroup the device bytes in place for aligned loads
+        (bit-identical content). True when the weight is in that layout afterwards."""
+        r = lib().b200h_weight_repack(self.h)
+        _check(r >= 0)
+        return bool(r)
+
+    def unpack(self) -> None:
+        _check(lib().b200h_weight_unpack(self.h) == 0)
+
+    @property
+    def repacked(self) -> bool:
+        return bool(lib().b200h_weight_is_repacked(self.h))
+
+    def raw_bytes(self) -> np.ndarray:
+        """The tensor's device bytes as they are stored."""
+        from .synth import packed_bytes
+        out = np.empty(packed_bytes(self.fmt, self.rows, self.cols), np.uint8)
+        _check(lib().b200h_tensor_to_host(self.h, out.ctypes.data) == 0)
+        return out
 
     def dequant(self, out_dtype: int = 1) -> np.ndarray:
         out = np.empty((self.rows, self.cols), _NP[out_dtype])

@@ -94,4 +94,9 @@ void upload_raw(const TensorInfo& info, int rows, int cols, Tensor& dst);
 // weight needs no re-quantisation and each shard's content is bit-identical.
 void upload_rows(const TensorInfo& info, int rows, int cols, int row_begin, int row_end, Device target, Tensor& dst);
 
+// upload_rows followed by repack_weights (include/brotensor_b200/repack.h) on the target's current
+// stream: the copy stays one contiguous byte range of the file, the regrouping happens on the
+// device and is bit-identical in content. Opt-in: the ops take either layout.
+void upload_rows_repacked(const TensorInfo& info, int rows, int cols, int row_begin, int row_end, Device target, Tensor& dst);
+
 }  // namespace brotensor_b200::gguf

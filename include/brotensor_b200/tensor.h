@@ -84,6 +84,7 @@ struct Tensor {
     int size() const { return rows * cols; }
     std::size_t bytes() const;
     bool empty() const { return data == nullptr || size() == 0; }
+    bool owns_storage() const { return owns_; }  // false for Tensor::view results (not in brotensor)
 
     std::vector<float> to_host_vector() const;                // FP32 only
     std::vector<std::uint16_t> to_host_vector_fp16() const;   // FP16 only

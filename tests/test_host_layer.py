@@ -244,3 +244,46 @@ def test_layer_set_one_copy_in_one_copy_out(built):
             assert np.array_equal(got, s.run(v).reshape(-1)), f"replay {rep}"
     g.close()
     L.close()
+
+
+@pytest.mark.gpu
+def test_repack_weights_keeps_every_op_bit_identical(built):
+    """brotensor_b200::repack_weights regroups a Q6_K weight on the device in place: the ops
+    find the layout through the storage record and return the raw layout's bits; unpack_weights
+    restores the GGUF bytes; formats without a regrouped form are left alone."""
+    from brotensor_b200 import hostapi
+    hostapi.init()
+    N, K = 320, 4096
+    blocks = synth.make_blocks(synth.Q6_K, N, K, seed=5)
+    w = hostapi.Weight(synth.Q6_K, blocks, N, K, 0)
+    assert not w.repacked
+    x1 = synth.make_activations(1, K, seed=1)
+    x4 = synth.make_activations(4, K, seed=2)
+    x40 = synth.make_activations(40, K, seed=3)
+    s1, s40 = hostapi.Session(w, 1, 0, 0), hostapi.Session(w, 40, 0, 0)
+    raw = dict(deq=w.dequant(1).copy(), y1=s1.run(x1).copy(), y40=s40.run(x40).copy())
+    assert w.repack() is True and w.repacked
+    assert not np.array_equal(w.raw_bytes(), blocks)          # the bytes moved ...
+    assert np.array_equal(np.sort(w.raw_bytes()), np.sort(blocks))  # ... and none was lost
+    assert np.array_equal(w.dequant(1), raw["deq"])
+    assert np.array_equal(s1.run(x1), raw["y1"])
+    assert np.array_equal(s40.run(x40), raw["y40"])
+    s4 = hostapi.Session(w, 4, 0, 0)
+    y4 = s4.run(x4).copy()
+    assert w.repack() is True                                  # a second call changes nothing
+    assert np.array_equal(s1.run(x1), raw["y1"])
+    w.unpack()
+    assert not w.repacked and np.array_equal(w.raw_bytes(), blocks)
+    assert np.array_equal(s1.run(x1), raw["y1"])
+    ref4 = s4.run(x4)
+    assert np.abs(ref4 - y4).max() <= 2e-3 * np.abs(ref4).max()  # four rows: different kernels per layout
+    for s in (s1, s4, s40):
+        s.close()
+    w.close()
+    # a weight that reuses the freed storage starts in the GGUF layout; Q4_K has no regrouped form
+    w2 = hostapi.Weight(synth.Q6_K, blocks, N, K, 0)
+    assert not w2.repacked
+    w2.close()
+    w3 = hostapi.Weight(synth.Q4_K, synth.make_blocks(synth.Q4_K, 64, 512, seed=1), 64, 512, 0)
+    assert w3.repack() is False and not w3.repacked
+    w3.close()
