@@ -226,6 +226,41 @@ def grouped_layer_set(stream, peak_gbs, R=8, n_steps=24):
                     "because that is the reference's op interface"}
 
 
+def repack_case(stream, peak_gbs, N=4096, K=14336, R=12):
+    """Q6_K down_proj in the GGUF layout against the device-side regrouped one (b200q_repack):
+    the repack pass itself, the decode GEMV and the decode to FP16 on both layouts."""
+    from . import _capi
+    fmt, pf = synth.Q6_K, synth.Q6_K_R8
+    base = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=9)).cuda()
+    raw = [base] + [torch.roll(base, 1680 * 97 * (i + 1)).contiguous() for i in range(R - 1)]
+    packed = [ops.repack(fmt, w, N, K) for w in raw]
+    nbytes = synth.packed_bytes(fmt, N, K)
+    assert torch.equal(ops.unpack(fmt, packed[1], N, K), raw[1])
+    x = torch.from_numpy(synth.make_activations(1, K, seed=2)).cuda()
+    y = torch.empty((1, N), dtype=torch.float32, device="cuda")
+    res = {"fmt": "q6k", "N": N, "K": K, "round_trip_bit_identical": True}
+    for name, f, ws in (("gguf_layout", fmt, raw), ("regrouped", pf, packed)):
+        def gv(i):
+            ops.gemv(f, ws[i % R], x, N, out=y)
+        for i in range(3):
+            gv(i)
+        med, _ = _time_graph(gv, 48, stream)
+        res["gemv_us_" + name] = med * 1e3
+    assert torch.equal(ops.gemv(pf, packed[0], x, N), ops.gemv(fmt, raw[0], x, N))
+    scratch = torch.empty_like(base)
+
+    def rp(i):
+        _capi.check(_capi.lib().b200q_repack(fmt, raw[i % R].data_ptr(), scratch.data_ptr(), N, K, torch.cuda.current_stream().cuda_stream))
+    for i in range(3):
+        rp(i)
+    med, _ = _time_graph(rp, 12, stream)
+    res["repack_us"] = med * 1e3
+    res["repack_GBps_read_plus_written"] = 2 * nbytes / (med * 1e-3) / 1e9
+    res["note"] = ("opt-in at load (brotensor_b200::repack_weights, gguf::upload_rows_repacked); the prefill GEMM is "
+                   "faster on the GGUF layout, so the loader keeps it unless asked")
+    return res
+
+
 def run(rank, world, peaks, stream):
     out = {}
     if world == 1:
@@ -238,5 +273,6 @@ def run(rank, world, peaks, stream):
         out["prefill_other_formats_512"] = [gemm_case(f, 14336, 4096, 512, torch.float32, stream, peaks) for f in (synth.Q6_K, synth.Q8_0)]
         out["layer_set_grouped"] = grouped_layer_set(stream, peaks["hbm_gbs"])
         out["dequant_to_fp16_4096x4096"] = [dequant_case(f, 4096, 4096, stream, peaks["hbm_gbs"]) for f in (synth.Q4_K, synth.Q6_K, synth.Q8_0)]
+        out["repack_q6k_down_proj"] = repack_case(stream, peaks["hbm_gbs"])
     out["lm_head"] = lm_head_case(rank, world, stream, peaks["hbm_gbs"])
     return out
