@@ -22,6 +22,7 @@
 #include "brotensor_b200/detail/dispatch.h"
 #include "brotensor_b200/gguf.h"
 #include "brotensor_b200/ops/quant.h"
+#include "brotensor_b200/repack.h"
 #include "brotensor_b200/runtime.h"
 
 namespace bt = brotensor_b200;
@@ -412,6 +413,65 @@ static void test_gpu_group_op() {
     CHECK(threw);
 }
 
+static void test_gpu_repack_weights() {
+    std::printf("test_gpu_repack_weights\n");
+    // a Q6_K weight regrouped in place gives every op's raw-layout bits; views, copies and freed
+    // storage follow the record; unpack restores the GGUF bytes
+    FmtCase c{"q6k", B200Q_FMT_Q6_K, Dtype::Q6_K, 256, 210, nullptr, nullptr, nullptr, nullptr};
+    const int OUT = 72, IN = 4096;
+    std::vector<uint8_t> blocks = make_blocks(c, OUT, IN);
+    Tensor W = Tensor::from_raw_bytes_on(Device::CUDA, blocks.data(), OUT, IN, Dtype::Q6_K, blocks.size());
+    std::vector<float> xh(IN);
+    for (int i = 0; i < IN; ++i) xh[i] = 0.02f * (float)((i * 53) % 47 - 23);
+    Tensor x = Tensor::from_host_on(Device::CUDA, xh.data(), IN, 1);
+    Tensor y_raw, d_raw, y_pk, d_pk, y_view, y_clone;
+    bt::linear_forward_q6k_fp16(W, nullptr, x, y_raw);
+    bt::dequant_q6k_to_fp16(W, d_raw);
+    CHECK(!bt::is_repacked(W));
+    CHECK(bt::repack_weights(W) && bt::is_repacked(W));
+    std::vector<uint8_t> moved(blocks.size());
+    W.copy_raw_to_host(moved.data());
+    CHECK(moved != blocks);
+    bt::linear_forward_q6k_fp16(W, nullptr, x, y_pk);
+    bt::dequant_q6k_to_fp16(W, d_pk);
+    CHECK(y_pk.to_host_vector() == y_raw.to_host_vector());
+    CHECK(d_pk.to_host_vector_fp16() == d_raw.to_host_vector_fp16());
+    // rows [24, 72) as a non-owning view (what a row-sharded head passes)
+    const std::size_t row_bytes = blocks.size() / OUT;
+    Tensor Wv = Tensor::view(Device::CUDA, static_cast<char*>(W.data) + 24 * row_bytes, OUT - 24, IN, Dtype::Q6_K);
+    CHECK(bt::is_repacked(Wv));
+    bt::linear_forward_q6k_fp16(Wv, nullptr, x, y_view);
+    {
+        const std::vector<float> a = y_view.to_host_vector(), b = y_raw.to_host_vector();
+        CHECK(std::vector<float>(b.begin() + 24, b.end()) == a);
+    }
+    bool threw = false;
+    try {
+        bt::repack_weights(Wv);  // already regrouped: fine
+        bt::unpack_weights(Wv);  // a view may not change the layout
+    } catch (const std::runtime_error& e) {
+        threw = std::string(e.what()).find("brotensor: unpack_weights:") == 0;
+    }
+    CHECK(threw);
+    Tensor Wc = W.clone();
+    CHECK(bt::is_repacked(Wc));
+    bt::linear_forward_q6k_fp16(Wc, nullptr, x, y_clone);
+    CHECK(y_clone.to_host_vector() == y_raw.to_host_vector());
+    bt::unpack_weights(W);
+    CHECK(!bt::is_repacked(W) && bt::is_repacked(Wc));
+    W.copy_raw_to_host(moved.data());
+    CHECK(moved == blocks);
+    // formats and shapes without a regrouped form
+    FmtCase c4{"q4k", B200Q_FMT_Q4_K, Dtype::Q4_K, 256, 144, nullptr, nullptr, nullptr, nullptr};
+    std::vector<uint8_t> b4 = make_blocks(c4, 8, 512);
+    Tensor W4 = Tensor::from_raw_bytes_on(Device::CUDA, b4.data(), 8, 512, Dtype::Q4_K, b4.size());
+    CHECK(!bt::repack_weights(W4) && !bt::is_repacked(W4));
+    std::vector<uint8_t> b6 = make_blocks(c, 8, 768);
+    Tensor W6 = Tensor::from_raw_bytes_on(Device::CUDA, b6.data(), 8, 768, Dtype::Q6_K, b6.size());
+    CHECK(!bt::repack_weights(W6) && !bt::is_repacked(W6));
+    bt::sync_all();
+}
+
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "cpu";
     bt::init();
@@ -434,6 +494,7 @@ int main(int argc, char** argv) {
         for (const auto& c : cases) run_fmt(c);
         test_gpu_large_rows_and_views();
         test_gpu_group_op();
+        test_gpu_repack_weights();
         int st = 0;
         CHECK(b200q_device_status(&st) == B200Q_OK && st == 0);
     }
