@@ -221,7 +221,30 @@ def grouped_layer_set(stream, peak_gbs, R=8, n_steps=24):
     med, mn = _time_graph(step, n_steps, stream)
     nbytes = sum(synth.packed_bytes(f, n, k) for _, f, n, k in specs)
     gbs = nbytes / (med * 1e-3) / 1e9
+    # the gate / up pair alone: two launches, one grouped launch, one launch with the SwiGLU gate folded in
+    ig, iu = idx["gate_proj"], idx["up_proj"]
+    fmt_g, n_g = specs[ig][1], specs[ig][2]
+    act = torch.empty((1, n_g), dtype=torch.float32, device="cuda")
+
+    def two(r):
+        ops.gemv(fmt_g, reps[r % R][ig], x4, n_g, out=outs[ig])
+        ops.gemv(fmt_g, reps[r % R][iu], x4, n_g, out=outs[iu])
+
+    def one(r):
+        ops.gemv_multi(fmt_g, [reps[r % R][ig], reps[r % R][iu]], x4, [n_g, n_g], outs=[outs[ig], outs[iu]])
+
+    def gated(r):
+        ops.gemv_swiglu(fmt_g, reps[r % R][ig], reps[r % R][iu], x4, n_g, out=act)
+
+    pair = {}
+    for name, f in (("two_launches_us", two), ("grouped_us", one), ("swiglu_fused_us", gated)):
+        for i in range(3):
+            f(i)
+        pair[name] = _time_graph(f, n_steps, stream)[0] * 1e3
+    pair["packed_bytes"] = 2 * synth.packed_bytes(fmt_g, n_g, 4096)
+    pair["swiglu_fused_GBps"] = pair["packed_bytes"] / (pair["swiglu_fused_us"] * 1e-6) / 1e9
     return {"launches_per_step": 4, "us_per_step": med * 1e3, "GBps": gbs, "frac_of_hbm_peak": gbs / peak_gbs,
+            "gate_up_pair": pair,
             "note": "same seven matrix-vector products as the headline; the headline keeps one launch per op "
                     "because that is the reference's op interface"}
 

@@ -22,6 +22,8 @@ int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const voi
 int launch_gemv_dp_multi(int fmt, int n_seg, const void* const* W, const int* N, void* const* Y, const void* const* bias,
                          const void* X, int x_dtype, int y_dtype, int K, int sms, size_t smem_max, int* status, cudaStream_t st,
                          bool* taken);
+int launch_gemv_dp_swiglu(int fmt, const void* Wg, const void* Wu, const void* X, int x_dtype, void* Y, int y_dtype, int N, int K,
+                          int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken);
 void stream_set_option(int which, int value);
 void gemm_set_pair(int v);
 int gemm_get_pair();
@@ -253,6 +255,22 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
         return fail(B200Q_ERR_UNSUPPORTED, "gemv: shape (M %d, N %d, K %d, fmt %d) is outside the streaming kernel", M, N, K, fmt);
     }
     return launch_gemv_simple(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
+}
+
+int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void* x, int x_dtype, void* y, int y_dtype,
+                      int N, int K, void* stream) {
+    if (int rc = check_linear_args("gemv_swiglu", fmt, W_gate, x, x_dtype, y, y_dtype, 1, N, K)) return rc;
+    if (int rc = check_linear_args("gemv_swiglu", fmt, W_up, x, x_dtype, y, y_dtype, 1, N, K)) return rc;
+    if (N == 0) return B200Q_OK;
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    bool taken = false;
+    if (int rc = launch_gemv_dp_swiglu(fmt, W_gate, W_up, x, x_dtype, y, y_dtype, N, K, d->sms, d->smem_optin - 1024, d->status,
+                                       static_cast<cudaStream_t>(stream), &taken))
+        return rc;
+    if (!taken)
+        return fail(B200Q_ERR_UNSUPPORTED, "gemv_swiglu: shape (N %d, K %d, fmt %d) or weight alignment is outside the streaming kernel", N, K, fmt);
+    return B200Q_OK;
 }
 
 int b200q_gemv_multi(int fmt, int n, const void* const* W, const int* N, void* const* Y, const void* const* bias,

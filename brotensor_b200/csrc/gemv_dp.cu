@@ -611,7 +611,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 }
                 __syncwarp();
                 if (lane < nrows) {
-                    const uint8_t* src = tr.W + (size_t)(row0 + lane) * p.row_bytes + (size_t)c0 * Chunk<FMT>::bytes;
+                    const uint8_t* src = (p.W_up ? (((lane & 1) ? p.W_up : tr.W) + (size_t)((row0 + lane) >> 1) * p.row_bytes)
+                                                 : (tr.W + (size_t)(row0 + lane) * p.row_bytes)) +
+                                         (size_t)c0 * Chunk<FMT>::bytes;
                     bulk_g2s(ring + slot * stage_bytes + lane * p.row_stride, src, bytes,
                              p.split_full ? full + 8u * ((lane >> 1) & (kConsumerWarps - 1)) : full);
                 }
@@ -714,6 +716,18 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                 acc[pi][0][m] = acc[pi][1][m] = 0.f;
                 const int rr = 2 * (wl + kConsumerWarps * pi) + (up ? 1 : 0);
+                if (p.W_up) {
+                    // lanes 0..15 hold the gate row's sum, lanes 16..31 the up row's
+                    const float u = __shfl_xor_sync(0xffffffffu, s, 16);
+                    if (lane == 0 && rr < nrows && m == 0 && !*(volatile int*)&abort_flag) {
+                        const float v = s / (1.0f + expf(-s)) * u;  // silu(gate) * up
+                        const size_t o = (size_t)((row0 + rr) >> 1);
+                        if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(tr.Y)[o] = v;
+                        else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(tr.Y)[o] = __float2half_rn(v);
+                        else static_cast<__nv_bfloat16*>(tr.Y)[o] = __float2bfloat16_rn(v);
+                    }
+                    continue;
+                }
                 if ((lane & 15) == 0 && rr < nrows && m < p.M && !*(volatile int*)&abort_flag) {
                     const int n = row0 + rr;
                     if (tr.bias) {
@@ -933,6 +947,49 @@ int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const voi
         case kQ8_0: return launch_dp_f<kQ8_0>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, smem_max, status, st, taken, sh);
     }
     return fail(B200Q_ERR_BAD_ARG, "gemv: unknown block format %d", fmt);
+}
+
+// Gate and up projection with the SwiGLU gate applied in the epilogue: one launch over the two
+// matrices' interleaved rows instead of two GEMVs and an elementwise kernel.
+template <int FMT>
+static int launch_dp_swiglu_f(const void* Wg, const void* Wu, const void* X, int x_dtype, void* Y, int y_dtype, int N, int K,
+                              int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken) {
+    StreamParams p = {};
+    int grid = 0, ng = g_opt_groups;
+    size_t smem = 0;
+    const int vrows = 2 * N;
+    *taken = plan_dp<FMT>(1, vrows, K, sms, smem_max, ng, 1, p, grid, smem);
+    if (!*taken && ng == 2) {
+        ng = 1;
+        *taken = plan_dp<FMT>(1, vrows, K, sms, smem_max, ng, 1, p, grid, smem);
+    }
+    if (!*taken) return B200Q_OK;
+    if (p.n_tiles_total == 0) {  // whole tiles per CTA, so that every CTA starts on a gate row
+        p.n_tiles_total = (vrows + kTileRows - 1) / kTileRows;
+        if (grid > p.n_tiles_total) grid = p.n_tiles_total;
+    }
+    p.W = static_cast<const uint8_t*>(Wg);
+    p.W_up = static_cast<const uint8_t*>(Wu);
+    p.X = X;
+    p.Y = Y;
+    p.status = status;
+    p.x_dtype = x_dtype;
+    p.y_dtype = y_dtype;
+    return launch_dp_g<FMT, 1>(p, ng, 1, grid, smem, st);
+}
+
+int launch_gemv_dp_swiglu(int fmt, const void* Wg, const void* Wu, const void* X, int x_dtype, void* Y, int y_dtype, int N, int K,
+                          int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken) {
+    *taken = false;
+    if (((reinterpret_cast<uintptr_t>(Wg) | reinterpret_cast<uintptr_t>(Wu)) & 15) != 0) return B200Q_OK;
+    smem_max -= 1024;  // the kernel's barriers are static shared memory
+    switch (fmt) {
+        case kQ4_K: return launch_dp_swiglu_f<kQ4_K>(Wg, Wu, X, x_dtype, Y, y_dtype, N, K, sms, smem_max, status, st, taken);
+        case kQ6_K: return launch_dp_swiglu_f<kQ6_K>(Wg, Wu, X, x_dtype, Y, y_dtype, N, K, sms, smem_max, status, st, taken);
+        case kQ6_KP: return launch_dp_swiglu_f<kQ6_KP>(Wg, Wu, X, x_dtype, Y, y_dtype, N, K, sms, smem_max, status, st, taken);
+        case kQ8_0: return launch_dp_swiglu_f<kQ8_0>(Wg, Wu, X, x_dtype, Y, y_dtype, N, K, sms, smem_max, status, st, taken);
+    }
+    return fail(B200Q_ERR_BAD_ARG, "gemv_swiglu: unknown block format %d", fmt);
 }
 
 // Several matrices of one format and K against one activation vector (M = 1) in one launch: the

@@ -35,6 +35,10 @@ struct StreamParams {
     // Several weight matrices of one format and K that share the activation vector (n_seg > 1):
     // segment s occupies the virtual rows [16 * seg_tile0[s], 16 * seg_tile0[s] + seg_rows[s]) of the
     // launch; W / Y / bias / N above describe segment 0 when n_seg <= 1.
+    // Gate/up pair with a SwiGLU epilogue (W_up != nullptr, M = 1): the launch's virtual rows interleave
+    // the two matrices - row 2i is gate row i (in W), row 2i + 1 is up row i (in W_up) - so one warp's
+    // row pair is exactly what output i = silu(gate_i . x) * (up_i . x) needs; N counts virtual rows.
+    const uint8_t* W_up;
     int n_seg;
     int seg_rows[kMaxSegments];
     int seg_tile0[kMaxSegments + 1];

@@ -219,6 +219,26 @@ void group_impl(const Tensor* const* W, const Tensor* const* bias, int n, const 
                                   cuda_current_stream(W[0]->device.index)), op);
 }
 
+void swiglu_impl(const Tensor& Wg, const Tensor& Wu, const Tensor& x, Tensor& y) {
+    const char* op = "linear_forward_swiglu_fp16";
+    const Dtype wdt = Wg.dtype;
+    const int block = wdt == Dtype::Q8_0 ? 32 : 256;
+    const char* dname = wdt == Dtype::Q4_K ? "Q4_K" : wdt == Dtype::Q6_K ? "Q6_K" : wdt == Dtype::Q8_0 ? "Q8_0" : nullptr;
+    if (!dname) op_fail(op, "W must be Dtype::Q4_K, Q6_K or Q8_0");
+    check_w(Wg, wdt, dname, block, op);
+    check_w(Wu, wdt, dname, block, op);
+    if (Wu.rows != Wg.rows || Wu.cols != Wg.cols) op_fail(op, "W_gate and W_up must have the same shape");
+    if (is_repacked(Wg) != is_repacked(Wu)) op_fail(op, "both matrices must be in the same layout (repack_weights on both or neither)");
+    if (!act_dtype(x.dtype)) op_fail(op, "x must be FP16 (FP32 and BF16 are accepted as well)");
+    const int out = Wg.rows, K = Wg.cols;
+    if (x.rows != K || x.cols != 1) op_fail(op, "x shape must be (in, 1)");
+    const bool keep = y.rows == out && y.cols == 1 && act_dtype(y.dtype) && y.data;
+    if (!keep) y.resize(out, 1, x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    if (out == 0) return;
+    check_status(b200q_gemv_swiglu(layout_fmt(static_cast<int>(wdt), Wg), Wg.data, Wu.data, x.data, static_cast<int>(x.dtype), y.data,
+                                   static_cast<int>(y.dtype), out, K, cuda_current_stream(Wg.device.index)), op);
+}
+
 void batched_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op, const Tensor& W, const Tensor* bias,
                   const Tensor& X, Tensor& Y) {
     check_w(W, wdt, dname, block, op);
@@ -260,6 +280,7 @@ B200_FMT_OPS(q8_0, B200Q_FMT_Q8_0, Dtype::Q8_0, "Q8_0", 32)
 // (src/cuda/concat.cu:359-372) for the same nine slots.
 void fill_cuda_tables(OpsVTable& ops, AllocVTable& alloc) {
     ops.linear_forward_group_fp16 = group_impl;
+    ops.linear_forward_swiglu_fp16 = swiglu_impl;
     ops.dequant_q4k_to_fp16 = dequant_q4k;
     ops.linear_forward_q4k_fp16 = gemv_q4k;
     ops.linear_forward_batched_q4k_fp16 = batched_q4k;

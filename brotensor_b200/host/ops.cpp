@@ -52,4 +52,11 @@ void linear_forward_group_fp16(const Tensor* const* W, const Tensor* const* bias
     v.linear_forward_group_fp16(W, bias, n, x, y);
 }
 
+void linear_forward_swiglu_fp16(const Tensor& W_gate, const Tensor& W_up, const Tensor& x, Tensor& y) {
+    const detail::OpsVTable& v = detail::dispatch_with_opts(W_gate, {&W_up, &x, &y});
+    if (!v.linear_forward_swiglu_fp16) detail::throw_not_implemented("linear_forward_swiglu_fp16", W_gate.device);
+    detail::adopt_output(y, W_gate.device);
+    v.linear_forward_swiglu_fp16(W_gate, W_up, x, y);
+}
+
 }  // namespace brotensor_b200

@@ -94,6 +94,20 @@ def gemv(fmt, W, X, N, bias=None, out=None, out_dtype=None):
     return _linear("gemv", fmt, W, X, N, bias, out, out_dtype, None)
 
 
+def gemv_swiglu(fmt, W_gate, W_up, x, N, out=None, out_dtype=None):
+    """y(1, N) = silu(x @ decode(W_gate).T) * (x @ decode(W_up).T) in one launch."""
+    x = x.reshape(1, -1)
+    K = x.shape[1]
+    _check_w(fmt, W_gate, N, K)
+    _check_w(fmt, W_up, N, K)
+    if out is None:
+        out = torch.empty((1, N), dtype=out_dtype or (torch.float16 if x.dtype == torch.float16 else torch.float32), device=x.device)
+    with torch.cuda.device(x.device):
+        capi.check(capi.lib().b200q_gemv_swiglu(fmt, W_gate.data_ptr(), W_up.data_ptr(), x.data_ptr(), _DT[x.dtype],
+                                               out.data_ptr(), _DT[out.dtype], N, K, _stream()))
+    return out
+
+
 def gemv_multi(fmt, Ws, x, Ns, outs=None, biases=None):
     """Several matrices against one activation vector in one launch; returns the list of (1, N_s) results."""
     import ctypes as C

@@ -113,6 +113,16 @@ int b200q_gemv_multi(int fmt, int n, const void* const* W, const int* N, void* c
                      const void* x, int x_dtype, int y_dtype, int K, void* stream);
 
 /*
+ * Gate and up projection of a gated FFN in one launch, M = 1: y[i] = silu(W_gate[i] . x) * (W_up[i] . x),
+ * silu(v) = v / (1 + exp(-v)) (brotensor's swiglu_forward, src/cuda/swiglu.cu:27-46, applied to the two
+ * GEMV results without writing them out). W_gate and W_up: N x K of the same format, 16-byte aligned;
+ * y: N elements. No bias. brotensor runs two linear_forward_q4k_fp16 calls and swiglu_forward.
+ * Shapes outside the streaming kernel return B200Q_ERR_UNSUPPORTED.
+ */
+int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void* x, int x_dtype, void* y, int y_dtype,
+                      int N, int K, void* stream);
+
+/*
  * Row-sharded decode GEMV for one rank of a multi-GPU LM head (M = 1):
  * this rank owns rows [row_offset, row_offset + rows) of a matrix of total_rows
  * rows; W_shard is the byte range of those rows, x is replicated. The kernel

@@ -28,6 +28,8 @@ struct OpsVTable {
     LinearFn linear_forward_batched_q6k_fp16 = nullptr;
     // Extension, not in brotensor's table: several matrices against one activation vector.
     GroupFn linear_forward_group_fp16 = nullptr;
+    // Extension: gate and up projection with the SwiGLU gate applied in the kernel's epilogue.
+    void (*linear_forward_swiglu_fp16)(const Tensor& W_gate, const Tensor& W_up, const Tensor& x, Tensor& y) = nullptr;
 };
 
 struct AllocVTable {

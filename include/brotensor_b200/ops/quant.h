@@ -37,4 +37,10 @@ void linear_forward_batched_q6k_fp16(const Tensor& W_q6k, const Tensor* bias, co
 // to n separate calls. `bias` may be null or hold null entries.
 void linear_forward_group_fp16(const Tensor* const* W, const Tensor* const* bias, int n, const Tensor& x, Tensor* const* y);
 
+// Extension (brotensor: two linear_forward_q4k_fp16 calls, a concat and swiglu_forward,
+// include/brotensor/ops/activation.h:130-133): y (out, 1) = silu(W_gate x) * (W_up x) in one launch,
+// silu(v) = v / (1 + exp(-v)). W_gate and W_up: (out, in) of one quant dtype; x (in, 1). y keeps a
+// pre-sized FP32 / FP16 / BF16 dtype, else FP16 for FP16 x and FP32 otherwise.
+void linear_forward_swiglu_fp16(const Tensor& W_gate, const Tensor& W_up, const Tensor& x, Tensor& y);
+
 }  // namespace brotensor_b200

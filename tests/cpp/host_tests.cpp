@@ -8,6 +8,7 @@
 //                    tests/test_q8_0_parity.cpp H)
 #include <cuda_runtime_api.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
@@ -472,6 +473,41 @@ static void test_gpu_repack_weights() {
     bt::sync_all();
 }
 
+static void test_gpu_swiglu_op() {
+    std::printf("test_gpu_swiglu_op\n");
+    // silu(W_gate x) * (W_up x) in one launch against the two GEMVs and the gate on the host
+    FmtCase c{"q4k", B200Q_FMT_Q4_K, Dtype::Q4_K, 256, 144, nullptr, nullptr, nullptr, nullptr};
+    const int OUT = 200, IN = 1024;
+    std::vector<uint8_t> bg = make_blocks(c, OUT, IN), bu = make_blocks(c, OUT, IN);
+    for (std::size_t i = 0; i < bu.size(); i += 7) bu[i] ^= 0x5a;
+    Tensor Wg = Tensor::from_raw_bytes_on(Device::CUDA, bg.data(), OUT, IN, Dtype::Q4_K, bg.size());
+    Tensor Wu = Tensor::from_raw_bytes_on(Device::CUDA, bu.data(), OUT, IN, Dtype::Q4_K, bu.size());
+    std::vector<float> xh(IN);
+    for (int i = 0; i < IN; ++i) xh[i] = 0.03f * (float)((i * 29) % 41 - 20);
+    Tensor x = Tensor::from_host_on(Device::CUDA, xh.data(), IN, 1);
+    Tensor y, g, u;
+    bt::linear_forward_swiglu_fp16(Wg, Wu, x, y);
+    bt::linear_forward_q4k_fp16(Wg, nullptr, x, g);
+    bt::linear_forward_q4k_fp16(Wu, nullptr, x, u);
+    bt::sync_all();
+    CHECK(y.rows == OUT && y.cols == 1 && y.dtype == Dtype::FP32);
+    const std::vector<float> yv = y.to_host_vector(), gv = g.to_host_vector(), uv = u.to_host_vector();
+    double worst = 0;
+    for (int i = 0; i < OUT; ++i) {
+        const double want = (double)gv[i] / (1.0 + std::exp(-(double)gv[i])) * (double)uv[i];
+        worst = std::max(worst, std::fabs((double)yv[i] - want) / (std::fabs(want) + 1e-30));
+    }
+    CHECK(worst < 4e-6);
+    bool threw = false;
+    try {
+        Tensor W2 = Tensor::from_raw_bytes_on(Device::CUDA, bu.data(), OUT / 2, IN, Dtype::Q4_K, bu.size() / 2);
+        bt::linear_forward_swiglu_fp16(Wg, W2, x, y);
+    } catch (const std::runtime_error& e) {
+        threw = std::string(e.what()).find("brotensor: linear_forward_swiglu_fp16:") == 0;
+    }
+    CHECK(threw);
+}
+
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "cpu";
     bt::init();
@@ -495,6 +531,7 @@ int main(int argc, char** argv) {
         test_gpu_large_rows_and_views();
         test_gpu_group_op();
         test_gpu_repack_weights();
+        test_gpu_swiglu_op();
         int st = 0;
         CHECK(b200q_device_status(&st) == B200Q_OK && st == 0);
     }

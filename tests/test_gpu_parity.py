@@ -465,3 +465,25 @@ def test_repacked_q6k_gives_the_same_bits(N, K, cpu_oracle):
     X = dev(synth.make_activations(48, K, seed=7))
     assert torch.equal(ops.gemm(synth.Q6_K_R8, Wp, X, N), ops.gemm(synth.Q6_K, Wr, X, N))
     assert ops.device_status() == 0
+
+
+# ---- gate / up projection with the SwiGLU gate in the epilogue -----------------------------------
+
+@pytest.mark.parametrize("fmt,N,K", [(synth.Q4_K, 14336, 4096), (synth.Q4_K, 100, 512), (synth.Q4_K, 7, 256), (synth.Q6_K, 333, 2048),
+                                     (synth.Q8_0, 1000, 1024), (synth.Q4_K, 148 * 8 + 3, 1024)])
+def test_gemv_swiglu_equals_two_gemvs_and_the_gate(fmt, N, K, cpu_oracle):
+    """silu(gate . x) * (up . x) from one launch: the two dot products are the separate launches'
+    bits, the gate follows brotensor's swiglu_forward (v / (1 + exp(-v)) * u)."""
+    Wg, Wu = synth.make_blocks(fmt, N, K, seed=N + 1), synth.make_blocks(fmt, N, K, seed=N + 2)
+    x = synth.make_activations(1, K, seed=K)
+    xd = dev(x)
+    got = host_f32(ops.gemv_swiglu(fmt, dev(Wg), dev(Wu), xd, N))
+    g = host_f32(ops.gemv(fmt, dev(Wg), xd, N)).astype(np.float64)
+    u = host_f32(ops.gemv(fmt, dev(Wu), xd, N)).astype(np.float64)
+    same_sums = g / (1.0 + np.exp(-g)) * u
+    assert np.allclose(got, same_sums, rtol=2e-6, atol=1e-30)
+    wg, wu = cpu_oracle.matmul(fmt, Wg, x, threads=8).astype(np.float64), cpu_oracle.matmul(fmt, Wu, x, threads=8).astype(np.float64)
+    assert oracle.rel_l2(got, (wg / (1.0 + np.exp(-wg)) * wu).astype(np.float32)) < REL_L2
+    h = host_f32(ops.gemv_swiglu(fmt, dev(Wg), dev(Wu), xd.half(), N, out_dtype=torch.float16))
+    assert oracle.rel_l2(h, got) < 2e-3
+    assert ops.device_status() == 0
