@@ -189,15 +189,16 @@ int b200q_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows
 }
 
 // The streaming kernel for a decode GEMV of M <= 8 rows, by measurement on B200 (14336 x 4096 and
-// 4096 x 14336, us per launch): integer dot products win for one and two rows (Q4_K 8.1 / 14.0
-// against 16.7 / 18.3 with warp MMA), warp MMA from three rows on (Q4_K 19.9 / 21.3 against 22.9 /
-// 28.9 at three / four rows; Q6_K from four rows on), and is the only one for five to eight rows.
+// 4096 x 14336, us per launch): the integer-dot kernel's work grows with M, the warp-MMA kernel's
+// hardly does - Q4_K 8.1 / 12.8 / 16.1 / 21.9 at one to four rows against 16.7 / 18.3 / 19.9 / 21.3
+// with warp MMA, Q8_0 11.7 / 16.3 / 19.4 / 23.5 against 18.6 / 18.7 / 19.0 / 19.8 - so warp MMA takes
+// over at four rows (Q8_0: three) and is the only one for five to eight.
 // *taken = false when neither kernel takes the shape.
 static int gemv_streaming(DevInfo* d, int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y,
                           int y_dtype, int M, int N, int K, cudaStream_t st, bool* taken) {
     *taken = false;
     const size_t smem = d->smem_optin - 1024;
-    const bool mma_first = M >= ((fmt == kQ6_K || fmt == kQ6_KP) ? 4 : 3);
+    const bool mma_first = M >= (fmt == kQ8_0 ? 3 : 4);
     if (mma_first) {
         if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, smem, d->status, st, taken)) return rc;
         if (*taken) return B200Q_OK;

@@ -254,6 +254,73 @@ __device__ __forceinline__ void item_q4k(uint32_t rowA, uint32_t rowB, int gi, i
     }
 }
 
+// The same item for two to four activation rows, ordered for registers instead of load distance:
+// with both chunks' quants and two activation chunks live (item_q4k) the kernel spills under the
+// 96-register cap of an 18-warp CTA; here one chunk of quants (16 registers) and one chunk of one
+// row's activations (32) are live at a time.
+template <int MT>
+__device__ __forceinline__ void item_q4k_rows(uint32_t rowA, uint32_t rowB, int gi, int gg, const XAddr& xa,
+                                              float (&acc)[2][MT]) {
+    const int b = gi >> 1, hb = gi & 1;
+    const uint32_t prA = rowA + (uint32_t)b * 144u, prB = rowB + (uint32_t)b * 144u;
+    const uint32_t qaA = prA + 64u * hb, qaB = prB + 64u * hb;
+    const uint4 hA = lds128i<0>(prA), hB = lds128i<0>(prB);
+    uint32_t scw[2], mw[2];
+    float d[2], dm[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const uint4 h = r ? hB : hA;
+        const uint32_t sclo = h.y & 0x3f3f3f3fu, schi = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
+        const uint32_t mlo = h.z & 0x3f3f3f3fu, mhi = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
+        scw[r] = hb ? schi : sclo;
+        mw[r] = hb ? mhi : mlo;
+        d[r] = h2f(h.x & 0xFFFFu);
+        dm[r] = h2f(h.x >> 16);
+    }
+    int isum[2][MT];
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) isum[r][m] = 0;
+    {
+        const uint4 a0 = lds128i<16>(qaA), a1 = lds128i<32>(qaA), b0 = lds128i<16>(qaB), b1 = lds128i<32>(qaB);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            uint4 x[8];
+            q4k_load_x<0>(x_group(xa, m, gg), x);
+            int cl, ch;
+            q4k_dot(a0, a1, x, cl, ch);
+            isum[0][m] = (int)(scw[0] & 0xFFu) * cl + (int)((scw[0] >> 8) & 0xFFu) * ch;
+            q4k_dot(b0, b1, x, cl, ch);
+            isum[1][m] = (int)(scw[1] & 0xFFu) * cl + (int)((scw[1] >> 8) & 0xFFu) * ch;
+        }
+    }
+    {
+        const uint4 a0 = lds128i<48>(qaA), a1 = lds128i<64>(qaA), b0 = lds128i<48>(qaB), b1 = lds128i<64>(qaB);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            uint4 x[8];
+            q4k_load_x<1>(x_group(xa, m, gg), x);
+            int cl, ch;
+            q4k_dot(a0, a1, x, cl, ch);
+            isum[0][m] += (int)((scw[0] >> 16) & 0xFFu) * cl + (int)(scw[0] >> 24) * ch;
+            q4k_dot(b0, b1, x, cl, ch);
+            isum[1][m] += (int)((scw[1] >> 16) & 0xFFu) * cl + (int)(scw[1] >> 24) * ch;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        const uint4 sv = lds128i<0>(xa.sxi + (uint32_t)(m * (xa.K >> 5) + gg * 4) * 4u);
+        const float xs = __uint_as_float(lds32i<0>(xa.xsc + (uint32_t)(m * xa.groups + gg) * 4u));
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int imin = (int)(mw[r] & 0xFFu) * (int)sv.x + (int)((mw[r] >> 8) & 0xFFu) * (int)sv.y +
+                             (int)((mw[r] >> 16) & 0xFFu) * (int)sv.z + (int)(mw[r] >> 24) * (int)sv.w;
+            acc[r][m] = fmaf(xs, d[r] * (float)isum[r][m] - dm[r] * (float)imin, acc[r][m]);
+        }
+    }
+}
+
 template <int J>
 __device__ __forceinline__ void q8_block_words(uint32_t base, uint32_t (&w)[9]) {
     // block J of the group starts at 34*J: 4-byte aligned for even J, 2 (mod 4) for odd J
@@ -691,7 +758,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                     for (int gi = lane; gi < ng; gi += 32) {
 #pragma unroll
                         for (int pi = 0; pi < RP; ++pi) {
-                            if constexpr (FMT == kQ4_K) item_q4k<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                            if constexpr (FMT == kQ4_K && MT == 1) item_q4k<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
+                            else if constexpr (FMT == kQ4_K) item_q4k_rows<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
                             else item_q8_0<MT>(rowA[pi], rowB[pi], gi, g0 + gi, xa, acc[pi]);
                         }
                     }

@@ -163,7 +163,7 @@ def test_gemv_matches_oracle(fmt, name, M, path, cpu_oracle):
 @pytest.mark.parametrize("M", [3, 4, 5, 7, 8])
 def test_gemv_long_rows_several_activation_rows(fmt, name, M, cpu_oracle):
     """K = 14336 (down_proj): eight activation rows do not fit beside the weight ring, so the
-    automatic route runs two passes of up to four rows; three and four rows take the warp-MMA kernel."""
+    automatic route runs two passes of up to four rows; four rows take the warp-MMA kernel."""
     N, K = 40, 14336
     Wh = synth.make_blocks(fmt, N, K, seed=11)
     Xh = synth.make_activations(M, K, seed=M)
