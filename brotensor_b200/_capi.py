@@ -31,6 +31,7 @@ SYMBOLS = [
     ("b200q_unpack", _i, [_i, _vp, _vp, _i64, _i, _vp]),
     ("b200q_dequant", _i, [_i, _vp, _vp, _i, _i64, _i, _vp]),
     ("b200q_gemv", _i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    ("b200q_gemv_multi_rmsnorm", _i, [_i, _i, C.POINTER(_vp), C.POINTER(_i), C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _vp, C.c_float, _i, _i, _vp]),
     ("b200q_gemv_swiglu", _i, [_i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
     ("b200q_gemv_multi", _i, [_i, _i, C.POINTER(_vp), C.POINTER(_i), C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _i, _vp]),
     ("b200q_gemv_shard", _i, [_i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), _vp, _vp]),

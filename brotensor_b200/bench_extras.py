@@ -241,10 +241,24 @@ def grouped_layer_set(stream, peak_gbs, R=8, n_steps=24):
         for i in range(3):
             f(i)
         pair[name] = _time_graph(f, n_steps, stream)[0] * 1e3
+    # q / k / v grouped, without and with the RMSNorm of their input folded into the launch
+    iq = [idx["q_proj"], idx["k_proj"], idx["v_proj"]]
+    gamma = torch.ones(4096, dtype=torch.float32, device="cuda")
+
+    def qkv(r):
+        ops.gemv_multi(specs[iq[0]][1], [reps[r % R][i] for i in iq], x4, [specs[i][2] for i in iq], outs=[outs[i] for i in iq])
+
+    def qkv_norm(r):
+        ops.gemv_multi_rmsnorm(specs[iq[0]][1], [reps[r % R][i] for i in iq], x4, gamma, 1e-5, [specs[i][2] for i in iq], outs=[outs[i] for i in iq])
+
+    for name, f in (("qkv_grouped_us", qkv), ("qkv_grouped_rmsnorm_folded_us", qkv_norm)):
+        for i in range(3):
+            f(i)
+        pair[name] = _time_graph(f, n_steps, stream)[0] * 1e3
     pair["packed_bytes"] = 2 * synth.packed_bytes(fmt_g, n_g, 4096)
     pair["swiglu_fused_GBps"] = pair["packed_bytes"] / (pair["swiglu_fused_us"] * 1e-6) / 1e9
     return {"launches_per_step": 4, "us_per_step": med * 1e3, "GBps": gbs, "frac_of_hbm_peak": gbs / peak_gbs,
-            "gate_up_pair": pair,
+            "fused_pieces": pair,
             "note": "same seven matrix-vector products as the headline; the headline keeps one launch per op "
                     "because that is the reference's op interface"}
 

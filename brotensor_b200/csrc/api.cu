@@ -21,7 +21,7 @@ int launch_gemv_dp(int fmt, const void* W, const void* X, int x_dtype, const voi
                    int N, int K, int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken, const ShardOut* sh);
 int launch_gemv_dp_multi(int fmt, int n_seg, const void* const* W, const int* N, void* const* Y, const void* const* bias,
                          const void* X, int x_dtype, int y_dtype, int K, int sms, size_t smem_max, int* status, cudaStream_t st,
-                         bool* taken);
+                         bool* taken, const void* gamma, float eps);
 int launch_gemv_dp_swiglu(int fmt, const void* Wg, const void* Wu, const void* X, int x_dtype, void* Y, int y_dtype, int N, int K,
                           int sms, size_t smem_max, int* status, cudaStream_t st, bool* taken);
 void stream_set_option(int which, int value);
@@ -287,13 +287,34 @@ int b200q_gemv_multi(int fmt, int n, const void* const* W, const int* N, void* c
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (n > 1 && (g_opt_gemv_path == 0 || g_opt_gemv_path == 3)) {
         bool taken = false;
-        if (int rc = launch_gemv_dp_multi(fmt, n, W, N, Y, bias, x, x_dtype, y_dtype, K, d->sms, d->smem_optin - 1024, d->status, st, &taken))
+        if (int rc = launch_gemv_dp_multi(fmt, n, W, N, Y, bias, x, x_dtype, y_dtype, K, d->sms, d->smem_optin - 1024, d->status, st, &taken, nullptr, 0.f))
             return rc;
         if (taken) return B200Q_OK;
     }
     // shapes the grouped kernel does not take: one launch per matrix
     for (int s = 0; s < n; ++s)
         if (int rc = b200q_gemv(fmt, W[s], x, x_dtype, bias ? bias[s] : nullptr, Y[s], y_dtype, 1, N[s], K, stream)) return rc;
+    return B200Q_OK;
+}
+
+int b200q_gemv_multi_rmsnorm(int fmt, int n, const void* const* W, const int* N, void* const* Y, const void* const* bias,
+                             const void* x, int x_dtype, const void* gamma, float eps, int y_dtype, int K, void* stream) {
+    if (n < 1 || n > kMaxSegments) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: %d matrices (1..%d)", n, kMaxSegments);
+    if (!W || !N || !Y) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: null table");
+    if (!gamma || !aligned(gamma, 16)) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: gamma must be a 16-byte aligned vector of K elements");
+    if (!(eps >= 0.f)) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: eps must not be negative");
+    for (int s = 0; s < n; ++s) {
+        if (N[s] <= 0) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: matrix %d has %d rows", s, N[s]);
+        if (int rc = check_linear_args("gemv_multi_rmsnorm", fmt, W[s], x, x_dtype, Y[s], y_dtype, 1, N[s], K)) return rc;
+    }
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    bool taken = false;
+    if (int rc = launch_gemv_dp_multi(fmt, n, W, N, Y, bias, x, x_dtype, y_dtype, K, d->sms, d->smem_optin - 1024, d->status,
+                                      static_cast<cudaStream_t>(stream), &taken, gamma, eps))
+        return rc;
+    if (!taken)
+        return fail(B200Q_ERR_UNSUPPORTED, "gemv_multi_rmsnorm: shape (K %d, fmt %d) or weight alignment is outside the streaming kernel", K, fmt);
     return B200Q_OK;
 }
 

@@ -39,6 +39,10 @@ struct StreamParams {
     // the two matrices - row 2i is gate row i (in W), row 2i + 1 is up row i (in W_up) - so one warp's
     // row pair is exactly what output i = silu(gate_i . x) * (up_i . x) needs; N counts virtual rows.
     const uint8_t* W_up;
+    // RMSNorm folded into the activation staging (norm_gamma != nullptr, M = 1): the kernel stages
+    // x[j] * gamma[j] * rsqrt(mean_j x[j]^2 + norm_eps) instead of x; gamma has X's dtype and K elements.
+    const void* norm_gamma;
+    float norm_eps;
     int n_seg;
     int seg_rows[kMaxSegments];
     int seg_tile0[kMaxSegments + 1];

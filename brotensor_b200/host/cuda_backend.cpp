@@ -219,6 +219,38 @@ void group_impl(const Tensor* const* W, const Tensor* const* bias, int n, const 
                                   cuda_current_stream(W[0]->device.index)), op);
 }
 
+void group_rmsnorm_impl(const Tensor* const* W, int n, const Tensor& x, const Tensor& gamma, float eps, Tensor* const* y) {
+    const char* op = "linear_forward_group_rmsnorm_fp16";
+    if (n > 4) op_fail(op, "at most four matrices per call");
+    const Dtype wdt = W[0]->dtype;
+    const int block = wdt == Dtype::Q8_0 ? 32 : 256;
+    const char* dname = wdt == Dtype::Q4_K ? "Q4_K" : wdt == Dtype::Q6_K ? "Q6_K" : wdt == Dtype::Q8_0 ? "Q8_0" : nullptr;
+    if (!dname) op_fail(op, "W must be Dtype::Q4_K, Q6_K or Q8_0");
+    if (!act_dtype(x.dtype)) op_fail(op, "x must be FP16 (FP32 and BF16 are accepted as well)");
+    const int K = W[0]->cols;
+    if (x.rows != K || x.cols != 1) op_fail(op, "x shape must be (in, 1)");
+    if (gamma.dtype != x.dtype) op_fail(op, "gamma must have x's dtype");
+    if (gamma.rows != K || gamma.cols != 1) op_fail(op, "gamma shape must be (in, 1)");
+    if (!(eps >= 0.f)) op_fail(op, "eps must not be negative");
+    const void* Wp[4];
+    void* Yp[4];
+    int Np[4];
+    const Dtype ydt = (y[0]->data && act_dtype(y[0]->dtype)) ? y[0]->dtype : (x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    for (int s = 0; s < n; ++s) {
+        check_w(*W[s], wdt, dname, block, op);
+        if (W[s]->cols != K) op_fail(op, "all matrices must have the same number of columns");
+        if (is_repacked(*W[s]) != is_repacked(*W[0])) op_fail(op, "all matrices must be in the same layout (repack_weights on all or none)");
+        const int out = W[s]->rows;
+        const bool keep = y[s]->rows == out && y[s]->cols == 1 && y[s]->dtype == ydt && y[s]->data;
+        if (!keep) y[s]->resize(out, 1, ydt);
+        Wp[s] = W[s]->data;
+        Yp[s] = y[s]->data;
+        Np[s] = out;
+    }
+    check_status(b200q_gemv_multi_rmsnorm(layout_fmt(static_cast<int>(wdt), *W[0]), n, Wp, Np, Yp, nullptr, x.data, static_cast<int>(x.dtype),
+                                          gamma.data, eps, static_cast<int>(ydt), K, cuda_current_stream(W[0]->device.index)), op);
+}
+
 void swiglu_impl(const Tensor& Wg, const Tensor& Wu, const Tensor& x, Tensor& y) {
     const char* op = "linear_forward_swiglu_fp16";
     const Dtype wdt = Wg.dtype;
@@ -281,6 +313,7 @@ B200_FMT_OPS(q8_0, B200Q_FMT_Q8_0, Dtype::Q8_0, "Q8_0", 32)
 void fill_cuda_tables(OpsVTable& ops, AllocVTable& alloc) {
     ops.linear_forward_group_fp16 = group_impl;
     ops.linear_forward_swiglu_fp16 = swiglu_impl;
+    ops.linear_forward_group_rmsnorm_fp16 = group_rmsnorm_impl;
     ops.dequant_q4k_to_fp16 = dequant_q4k;
     ops.linear_forward_q4k_fp16 = gemv_q4k;
     ops.linear_forward_batched_q4k_fp16 = batched_q4k;

@@ -1,6 +1,7 @@
 // Public op wrappers: resolve the device, refuse a null slot, pin an unsized output to
 // the op's device, call the backend (brotensor src/ops.cpp:2049-2125).
 #include <stdexcept>
+#include <string>
 
 #include "brotensor_b200/detail/dispatch.h"
 #include "brotensor_b200/ops/quant.h"
@@ -50,6 +51,21 @@ void linear_forward_group_fp16(const Tensor* const* W, const Tensor* const* bias
         detail::adopt_output(*y[s], dev);
     }
     v.linear_forward_group_fp16(W, bias, n, x, y);
+}
+
+void linear_forward_group_rmsnorm_fp16(const Tensor* const* W, int n, const Tensor& x, const Tensor& gamma, float eps,
+                                       Tensor* const* y) {
+    const char* op = "linear_forward_group_rmsnorm_fp16";
+    if (n <= 0 || !W || !y || !W[0] || !y[0]) throw std::runtime_error(std::string("brotensor: ") + op + ": no matrices");
+    const detail::OpsVTable& v = detail::dispatch_with_opts(*W[0], {&x, &gamma, y[0]});
+    const Device dev = W[0]->device;
+    if (!v.linear_forward_group_rmsnorm_fp16) detail::throw_not_implemented(op, dev);
+    for (int s = 0; s < n; ++s) {
+        if (!W[s] || !y[s]) throw std::runtime_error(std::string("brotensor: ") + op + ": null tensor");
+        if (W[s]->device != dev) throw std::runtime_error(std::string("brotensor: ") + op + ": matrices on different devices");
+        detail::adopt_output(*y[s], dev);
+    }
+    v.linear_forward_group_rmsnorm_fp16(W, n, x, gamma, eps, y);
 }
 
 void linear_forward_swiglu_fp16(const Tensor& W_gate, const Tensor& W_up, const Tensor& x, Tensor& y) {

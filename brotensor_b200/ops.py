@@ -127,6 +127,27 @@ def gemv_multi(fmt, Ws, x, Ns, outs=None, biases=None):
     return outs
 
 
+def gemv_multi_rmsnorm(fmt, Ws, x, gamma, eps, Ns, outs=None):
+    """gemv_multi on rms_norm(x) * gamma, the normalisation folded into the kernel."""
+    import ctypes as C
+    n = len(Ws)
+    K = x.numel()
+    for W, N in zip(Ws, Ns):
+        _check_w(fmt, W, N, K)
+    if gamma.dtype != x.dtype or gamma.numel() != K:
+        raise ValueError("gamma must have K elements of x's dtype")
+    if outs is None:
+        outs = [torch.empty((1, N), dtype=torch.float32, device=x.device) for N in Ns]
+    Wp = (C.c_void_p * n)(*[W.data_ptr() for W in Ws])
+    Yp = (C.c_void_p * n)(*[y.data_ptr() for y in outs])
+    Np = (C.c_int * n)(*Ns)
+    with torch.cuda.device(x.device):
+        rc = capi.lib().b200q_gemv_multi_rmsnorm(fmt, n, Wp, Np, Yp, None, x.data_ptr(), _DT[x.dtype], gamma.data_ptr(), float(eps),
+                                                 _DT[outs[0].dtype], K, _stream())
+    capi.check(rc)
+    return outs
+
+
 def gemm(fmt, W, X, N, bias=None, out=None, out_dtype=None, ws=None):
     """Prefill GEMM on the tensor cores, any M."""
     return _linear("gemm", fmt, W, X, N, bias, out, out_dtype, ws)

@@ -113,6 +113,17 @@ int b200q_gemv_multi(int fmt, int n, const void* const* W, const int* N, void* c
                      const void* x, int x_dtype, int y_dtype, int K, void* stream);
 
 /*
+ * b200q_gemv_multi with brotensor's rms_norm_forward (include/brotensor/ops/norm.h:136-140,
+ * src/cuda/rms_norm.cu:56-75) folded into the kernel's activation staging: the n <= 4 matrices are
+ * multiplied by x[j] * gamma[j] * rsqrt(mean_j x[j]^2 + eps), computed in FP32 by every CTA from the K
+ * values of x, so the normalised vector is never written and the normalisation costs no launch.
+ * gamma: K elements of x's dtype, 16-byte aligned. n = 1 is allowed. Shapes outside the streaming
+ * kernel return B200Q_ERR_UNSUPPORTED (no fallback: the unfused form is rms_norm + b200q_gemv_multi).
+ */
+int b200q_gemv_multi_rmsnorm(int fmt, int n, const void* const* W, const int* N, void* const* Y, const void* const* bias,
+                             const void* x, int x_dtype, const void* gamma, float eps, int y_dtype, int K, void* stream);
+
+/*
  * Gate and up projection of a gated FFN in one launch, M = 1: y[i] = silu(W_gate[i] . x) * (W_up[i] . x),
  * silu(v) = v / (1 + exp(-v)) (brotensor's swiglu_forward, src/cuda/swiglu.cu:27-46, applied to the two
  * GEMV results without writing them out). W_gate and W_up: N x K of the same format, 16-byte aligned;

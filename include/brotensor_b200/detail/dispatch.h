@@ -30,6 +30,9 @@ struct OpsVTable {
     GroupFn linear_forward_group_fp16 = nullptr;
     // Extension: gate and up projection with the SwiGLU gate applied in the kernel's epilogue.
     void (*linear_forward_swiglu_fp16)(const Tensor& W_gate, const Tensor& W_up, const Tensor& x, Tensor& y) = nullptr;
+    // Extension: the grouped op on rms_norm(x) * gamma, the normalisation folded into the launch.
+    void (*linear_forward_group_rmsnorm_fp16)(const Tensor* const* W, int n, const Tensor& x, const Tensor& gamma, float eps,
+                                              Tensor* const* y) = nullptr;
 };
 
 struct AllocVTable {

@@ -43,4 +43,10 @@ void linear_forward_group_fp16(const Tensor* const* W, const Tensor* const* bias
 // pre-sized FP32 / FP16 / BF16 dtype, else FP16 for FP16 x and FP32 otherwise.
 void linear_forward_swiglu_fp16(const Tensor& W_gate, const Tensor& W_up, const Tensor& x, Tensor& y);
 
+// Extension (brotensor: rms_norm_forward, include/brotensor/ops/norm.h:136-140, then one GEMV per
+// projection): y[s] = W[s] * (x * gamma * rsqrt(mean(x^2) + eps)) for n <= 4 matrices of one quant
+// dtype in a single launch; gamma (in, 1) of x's dtype. No bias. y as in linear_forward_group_fp16.
+void linear_forward_group_rmsnorm_fp16(const Tensor* const* W, int n, const Tensor& x, const Tensor& gamma, float eps,
+                                       Tensor* const* y);
+
 }  // namespace brotensor_b200

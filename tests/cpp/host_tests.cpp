@@ -508,6 +508,52 @@ static void test_gpu_swiglu_op() {
     CHECK(threw);
 }
 
+static void test_gpu_group_rmsnorm_op() {
+    std::printf("test_gpu_group_rmsnorm_op\n");
+    // two Q4_K matrices on rms_norm(x) * gamma in one launch == the grouped op on the host-normalised vector
+    FmtCase c{"q4k", B200Q_FMT_Q4_K, Dtype::Q4_K, 256, 144, nullptr, nullptr, nullptr, nullptr};
+    const int IN = 1024, outs[2] = {80, 33};
+    const float eps = 1e-5f;
+    std::vector<Tensor> W(2), yf(2), yr(2);
+    for (int i = 0; i < 2; ++i) {
+        std::vector<uint8_t> b = make_blocks(c, outs[i], IN);
+        b[11 * (i + 1)] ^= 0x21;
+        W[i] = Tensor::from_raw_bytes_on(Device::CUDA, b.data(), outs[i], IN, Dtype::Q4_K, b.size());
+    }
+    std::vector<float> xh(IN), gh(IN), xn(IN);
+    double ss = 0;
+    for (int i = 0; i < IN; ++i) {
+        xh[i] = 0.05f * (float)((i * 31) % 53 - 26);
+        gh[i] = 1.0f + 0.01f * (float)(i % 17);
+        ss += (double)xh[i] * xh[i];
+    }
+    const double rr = 1.0 / std::sqrt(ss / IN + eps);
+    for (int i = 0; i < IN; ++i) xn[i] = (float)(xh[i] * rr * gh[i]);
+    Tensor x = Tensor::from_host_on(Device::CUDA, xh.data(), IN, 1), g = Tensor::from_host_on(Device::CUDA, gh.data(), IN, 1);
+    Tensor xnd = Tensor::from_host_on(Device::CUDA, xn.data(), IN, 1);
+    const Tensor* Wp[2] = {&W[0], &W[1]};
+    Tensor* yfp[2] = {&yf[0], &yf[1]};
+    Tensor* yrp[2] = {&yr[0], &yr[1]};
+    bt::linear_forward_group_rmsnorm_fp16(Wp, 2, x, g, eps, yfp);
+    bt::linear_forward_group_fp16(Wp, nullptr, 2, xnd, yrp);
+    bt::sync_all();
+    for (int i = 0; i < 2; ++i) {
+        const std::vector<float> a = yf[i].to_host_vector(), b = yr[i].to_host_vector();
+        CHECK((int)a.size() == outs[i]);
+        double num = 0, den = 0;
+        for (std::size_t k = 0; k < a.size(); ++k) { num += ((double)a[k] - b[k]) * ((double)a[k] - b[k]); den += (double)b[k] * b[k]; }
+        CHECK(std::sqrt(num / (den + 1e-30)) < 2e-4);
+    }
+    bool threw = false;
+    try {
+        Tensor g2 = Tensor::from_host_on(Device::CUDA, gh.data(), IN / 2, 1);
+        bt::linear_forward_group_rmsnorm_fp16(Wp, 2, x, g2, eps, yfp);
+    } catch (const std::runtime_error& e) {
+        threw = std::string(e.what()).find("brotensor: linear_forward_group_rmsnorm_fp16:") == 0;
+    }
+    CHECK(threw);
+}
+
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "cpu";
     bt::init();
@@ -532,6 +578,7 @@ int main(int argc, char** argv) {
         test_gpu_group_op();
         test_gpu_repack_weights();
         test_gpu_swiglu_op();
+        test_gpu_group_rmsnorm_op();
         int st = 0;
         CHECK(b200q_device_status(&st) == B200Q_OK && st == 0);
     }

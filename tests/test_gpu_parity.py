@@ -487,3 +487,29 @@ def test_gemv_swiglu_equals_two_gemvs_and_the_gate(fmt, N, K, cpu_oracle):
     h = host_f32(ops.gemv_swiglu(fmt, dev(Wg), dev(Wu), xd.half(), N, out_dtype=torch.float16))
     assert oracle.rel_l2(h, got) < 2e-3
     assert ops.device_status() == 0
+
+
+# ---- RMSNorm folded into the GEMV's activation staging --------------------------------------------
+
+@pytest.mark.parametrize("fmt,K,Ns", [(synth.Q4_K, 4096, [4096, 1024, 1024]), (synth.Q4_K, 4096, [14336, 14336]), (synth.Q6_K, 2048, [50]),
+                                      (synth.Q8_0, 1024, [100, 7]), (synth.Q6_K, 14336, [64])])
+@pytest.mark.parametrize("xdt", [torch.float32, torch.float16])
+def test_rmsnorm_folded_into_grouped_gemv(fmt, K, Ns, xdt, cpu_oracle):
+    """y_s = W_s (x * gamma * rsqrt(mean x^2 + eps)): brotensor's rms_norm_forward followed by its
+    GEMVs, in one launch; compared with the oracle on the host-normalised vector."""
+    eps = 1e-5
+    x = (synth.make_activations(1, K, seed=K + len(Ns)) * 3.0).astype(np.float32)
+    gamma = (1.0 + 0.1 * synth.make_activations(1, K, seed=7)).astype(np.float32)
+    xd, gd = dev(x).to(xdt).view(-1), dev(gamma).to(xdt).view(-1)
+    xh, gh = xd.float().cpu().numpy().astype(np.float64), gd.float().cpu().numpy().astype(np.float64)
+    xn = (xh * gh / np.sqrt(np.mean(xh * xh) + eps)).astype(np.float32).reshape(1, K)
+    Ws = [synth.make_blocks(fmt, N, K, seed=N + i) for i, N in enumerate(Ns)]
+    got = ops.gemv_multi_rmsnorm(fmt, [dev(W) for W in Ws], xd, gd, eps, Ns)
+    for W, N, y in zip(Ws, Ns, got):
+        want = cpu_oracle.matmul(fmt, W, xn, threads=8)
+        assert oracle.rel_l2(host_f32(y), want) < REL_L2, f"N={N}"
+    # the same launch without the fold on the host-normalised vector: equal up to the rounding of xn
+    plain = [ops.gemv(fmt, dev(W), dev(xn), N) for W, N in zip(Ws, Ns)]
+    for a, b in zip(got, plain):
+        assert oracle.rel_l2(host_f32(a), host_f32(b)) < 2e-4
+    assert ops.device_status() == 0
