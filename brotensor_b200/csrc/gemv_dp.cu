@@ -633,8 +633,12 @@ struct TileRef {
     int N;     // rows of that matrix (leading dimension of its Y)
     int row0;  // first row of the tile inside that matrix
 };
+// Bits of the kernel's EXT template argument (see gemv_dp_kernel).
+constexpr int kExtSeg = 1, kExtShard = 2, kExtNorm = 4, kExtSwiglu = 8;
+
+template <int EXT>
 __device__ __forceinline__ TileRef tile_ref(const StreamParams& p, int vrow) {
-    if (p.n_seg <= 1) return {p.W, p.Y, p.bias, p.N, vrow};
+    if (!(EXT & kExtSeg) || p.n_seg <= 1) return {p.W, p.Y, p.bias, p.N, vrow};
     int s = 0;
 #pragma unroll
     for (int i = 1; i < kMaxSegments; ++i)
@@ -645,9 +649,12 @@ __device__ __forceinline__ TileRef tile_ref(const StreamParams& p, int vrow) {
 // RP = row pairs per consumer warp and tile: a tile has 16 * RP rows. Two pairs per warp double
 // the bytes a tile moves per barrier round trip (what the per-tile overheads are paid on) and
 // give every lane two independent chains of work.
-// EXT = 1 adds the fused forms (RMSNorm folded into the staging, gate / up pairs with a SwiGLU
-// epilogue) as a separate instantiation, so that the plain GEMV carries none of their branches:
-// with them in one kernel the seven-launch layer set measured 49.2 instead of 44.0 us.
+// EXT is a mask of what a launch does beyond the plain GEMV: several matrices per launch, the
+// row-sharded epilogue, RMSNorm folded into the staging, a gate / up pair with a SwiGLU epilogue.
+// Each used combination is its own instantiation, so that no kernel carries code it does not run:
+// a chain that alternates between kernels pays for every kernel's size at each switch (with the
+// two fused forms compiled into the plain GEMV the seven-launch layer set took 49.2 instead of
+// 44.0 us; with everything in one extended kernel the four-launch set took 40.9 instead of 35.6 us).
 template <int FMT, int MT, int NG, int RP, int EXT = 0>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_kernel(const StreamParams p) {
     constexpr int TR = kTileRows * RP;
@@ -665,7 +672,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x;
     // virtual rows of the launch: the matrix's rows, or with several matrices their tile-padded concatenation
-    const int vrows = p.n_seg > 1 ? kTileRows * p.seg_tile0[p.n_seg] : p.N;
+    const int vrows = ((EXT & kExtSeg) && p.n_seg > 1) ? kTileRows * p.seg_tile0[p.n_seg] : p.N;
     const int row_begin = p.n_tiles_total > 0 ? min(vrows, TR * (int)((long long)p.n_tiles_total * blockIdx.x / G))
                                               : (int)((long long)vrows * blockIdx.x / G);
     const int row_end = p.n_tiles_total > 0 ? min(vrows, TR * (int)((long long)p.n_tiles_total * (blockIdx.x + 1) / G))
@@ -695,7 +702,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         int slot = 0;
         uint32_t phase = 0;
         for (int tile = g; tile < n_tiles; tile += NG) {
-            const TileRef tr = tile_ref(p, row_begin + tile * TR);
+            const TileRef tr = tile_ref<EXT>(p, row_begin + tile * TR);
             const int row0 = tr.row0;
             const int nrows = min(min(TR, row_end - (row_begin + tile * TR)), tr.N - row0);
             for (int slice = 0; slice < p.n_slices; ++slice) {
@@ -714,7 +721,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 }
                 __syncwarp();
                 if (lane < nrows) {
-                    const uint8_t* src = ((EXT && p.W_up) ? (((lane & 1) ? p.W_up : tr.W) + (size_t)((row0 + lane) >> 1) * p.row_bytes)
+                    const uint8_t* src = (((EXT & kExtSwiglu) && p.W_up) ? (((lane & 1) ? p.W_up : tr.W) + (size_t)((row0 + lane) >> 1) * p.row_bytes)
                                                           : (tr.W + (size_t)(row0 + lane) * p.row_bytes)) +
                                          (size_t)c0 * Chunk<FMT>::bytes;
                     bulk_g2s(ring + slot * stage_bytes + lane * p.row_stride, src, bytes,
@@ -732,9 +739,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     // ---- consumers
     grid_dep_wait();  // activations (and Y) belong to the stream-ordered predecessor
     // launch counter of the sharded form: stable while this launch runs (only its last CTA bumps it)
-    const unsigned int sh_epoch = p.sh_world > 0 ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
+    const unsigned int sh_epoch = ((EXT & kExtShard) && p.sh_world > 0) ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
     const unsigned int sh_buf = (sh_epoch + 1u) & 1u;
-    if (EXT && MT == 1 && p.norm_gamma) {
+    if ((EXT & kExtNorm) && MT == 1 && p.norm_gamma) {
         if (p.x_dtype == B200Q_DT_F32) stage_x16_norm<FMT, float>(p, sbase, tid, kConsumers * 32, norm_red);
         else if (p.x_dtype == B200Q_DT_F16) stage_x16_norm<FMT, __half>(p, sbase, tid, kConsumers * 32, norm_red);
         else stage_x16_norm<FMT, __nv_bfloat16>(p, sbase, tid, kConsumers * 32, norm_red);
@@ -759,7 +766,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
             for (int m = 0; m < MT; ++m) acc[pi][r][m] = 0.f;
 
     for (int tile = g; tile < n_tiles; tile += NG) {
-        const TileRef tr = tile_ref(p, row_begin + tile * TR);
+        const TileRef tr = tile_ref<EXT>(p, row_begin + tile * TR);
         const int row0 = tr.row0;
         const int nrows = min(min(TR, row_end - (row_begin + tile * TR)), tr.N - row0);
         for (int slice = 0; slice < p.n_slices; ++slice) {
@@ -824,7 +831,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                 acc[pi][0][m] = acc[pi][1][m] = 0.f;
                 const int rr = 2 * (wl + kConsumerWarps * pi) + (up ? 1 : 0);
-                if (EXT && p.W_up) {
+                if ((EXT & kExtSwiglu) && p.W_up) {
                     // lanes 0..15 hold the gate row's sum, lanes 16..31 the up row's
                     const float u = __shfl_xor_sync(0xffffffffu, s, 16);
                     if (lane == 0 && rr < nrows && m == 0 && !*(volatile int*)&abort_flag) {
@@ -844,7 +851,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                         else s += __bfloat162float(static_cast<const __nv_bfloat16*>(tr.bias)[n]);
                     }
                     const size_t o = (size_t)m * tr.N + n;
-                    if (p.sh_world > 0) {
+                    if ((EXT & kExtShard) && p.sh_world > 0) {
                         // sharded output: into this rank's own result vector first (which of the two
                         // vectors is this launch's parity); the CTA forwards its rows to the peers below
                         p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
@@ -855,7 +862,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
             }
         }
     }
-    if (p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32);
+    if ((EXT & kExtShard) && p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32);
 }
 
 // ---- host side ------------------------------------------------------------------------
@@ -985,8 +992,22 @@ static int launch_dp_k(const StreamParams& p, int grid, size_t smem, cudaStream_
 template <int FMT, int MT>
 static int launch_dp_g(const StreamParams& p, int ng, int rp, int grid, size_t smem, cudaStream_t st) {
     if constexpr (MT == 1) {
-        if (p.W_up || p.norm_gamma)  // the fused forms: one activation row, 16-row tiles
-            return ng == 2 ? launch_dp_k<FMT, 1, 2, 1, 1>(p, grid, smem, st) : launch_dp_k<FMT, 1, 1, 1, 1>(p, grid, smem, st);
+        // grouped, sharded and fused forms: one activation row, 16-row tiles
+        const int ext = (p.n_seg > 1 ? kExtSeg : 0) | (p.sh_world > 0 ? kExtShard : 0) | (p.norm_gamma ? (kExtNorm | kExtSeg) : 0) |
+                        (p.W_up ? kExtSwiglu : 0);
+        switch (ext) {
+            case 0: break;
+            case kExtSeg:
+                return ng == 2 ? launch_dp_k<FMT, 1, 2, 1, kExtSeg>(p, grid, smem, st) : launch_dp_k<FMT, 1, 1, 1, kExtSeg>(p, grid, smem, st);
+            case kExtShard:
+                return ng == 2 ? launch_dp_k<FMT, 1, 2, 1, kExtShard>(p, grid, smem, st) : launch_dp_k<FMT, 1, 1, 1, kExtShard>(p, grid, smem, st);
+            case kExtNorm | kExtSeg:
+                return ng == 2 ? launch_dp_k<FMT, 1, 2, 1, kExtNorm | kExtSeg>(p, grid, smem, st)
+                               : launch_dp_k<FMT, 1, 1, 1, kExtNorm | kExtSeg>(p, grid, smem, st);
+            case kExtSwiglu:
+                return ng == 2 ? launch_dp_k<FMT, 1, 2, 1, kExtSwiglu>(p, grid, smem, st) : launch_dp_k<FMT, 1, 1, 1, kExtSwiglu>(p, grid, smem, st);
+            default: return fail(B200Q_ERR_UNSUPPORTED, "gemv: this combination of grouped / sharded / fused forms (%d) is not built", ext);
+        }
     }
     if (ng == 2) return launch_dp_k<FMT, MT, 2, 1>(p, grid, smem, st);
     return rp == 2 ? launch_dp_k<FMT, MT, 1, 2>(p, grid, smem, st) : launch_dp_k<FMT, MT, 1, 1>(p, grid, smem, st);
@@ -1007,7 +1028,7 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
     // make no difference (Q4_K, Q8_0) or lose (Q6_K in half-group units: LM head 94 % vs 70 % of
     // the HBM copy rate), so they are only taken on request.
     const bool tall = g_opt_tile_pairs == 2;
-    if (tall && N >= 32 * sms / 2) {
+    if (tall && !sh && N >= 32 * sms / 2) {
         ng = 1; rp = 2;
         *taken = plan_dp<FMT>(M, N, K, sms, smem_max, ng, rp, p, grid, smem);
     }
