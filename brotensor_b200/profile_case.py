@@ -1,6 +1,6 @@
 """Runs a handful of launches of one decode-GEMV / prefill-GEMM shape, for profilers.
 
-    python -m brotensor_b200.profile_case <fmt q4k|q6k|q8_0> <N> <K> <M> [--launches 4] [--path 0] [--op gemv|gemm]
+    python -m brotensor_b200.profile_case <fmt q4k|q6k|q8_0> <N> <K> <M> [--launches 4] [--path 0] [--op gemv|gemm|dequant]
 
 The weights rotate over six replicas so that a captured launch streams from DRAM; the
 device holds a few hundred MB at most. Prints the device status word at the end.
@@ -26,7 +26,7 @@ def main():
     ap.add_argument("M", type=int)
     ap.add_argument("--launches", type=int, default=4)
     ap.add_argument("--path", type=int, default=0)
-    ap.add_argument("--op", default="gemv", choices=["gemv", "gemm"])
+    ap.add_argument("--op", default="gemv", choices=["gemv", "gemm", "dequant"])
     ap.add_argument("--replicas", type=int, default=6)
     a = ap.parse_args()
     fmt = FMT[a.fmt]
@@ -36,6 +36,12 @@ def main():
     Ws = [base] + [torch.roll(base, 1028160 * (i + 1)).contiguous() for i in range(a.replicas - 1)]
     X = torch.from_numpy(synth.make_activations(a.M, a.K, seed=2)).cuda()
     Y = torch.empty((a.M, a.N), dtype=torch.float32, device="cuda")
+    if a.op == "dequant":  # decode to FP16 (M is ignored); the outputs rotate as well
+        for i in range(a.launches):
+            ops.dequant(fmt, Ws[i % len(Ws)], a.N, a.K, torch.float16)
+        torch.cuda.synchronize()
+        print("device status", ops.device_status())
+        return
     f = ops.gemv if a.op == "gemv" else ops.gemm
     for i in range(a.launches):
         f(fmt, Ws[i % len(Ws)], X, a.N, out=Y)
