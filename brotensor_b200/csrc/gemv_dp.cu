@@ -658,6 +658,9 @@ __device__ __forceinline__ TileRef tile_ref(const StreamParams& p, int vrow) {
 template <int FMT, int MT, int NG, int RP, int EXT = 0>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_kernel(const StreamParams p) {
     constexpr int TR = kTileRows * RP;
+    // Q4_K and Q8_0 always run with one full barrier per consumer warp; only Q6_K chooses at run time.
+    constexpr bool kSplitAlways = FMT != kQ6_K && FMT != kQ6_KP;
+    const bool split_full = kSplitAlways || p.split_full != 0;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;  // shared-space address
     // With p.split_full, one full barrier per consumer warp and stage: a warp's rows complete on
@@ -711,7 +714,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
                 const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
                 const uint32_t full = smem_u32(&bar_full[g][slot][0]);
-                if (!p.split_full) {
+                if (!split_full) {
                     if (lane == 0) mbar_arrive_expect_tx(full, bytes * (uint32_t)nrows);
                 } else if (lane < kConsumerWarps) {
                     // rows of consumer warp `lane` in this tile: its pair, and with 32-row tiles a second pair
@@ -725,7 +728,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                                                           : (tr.W + (size_t)(row0 + lane) * p.row_bytes)) +
                                          (size_t)c0 * Chunk<FMT>::bytes;
                     bulk_g2s(ring + slot * stage_bytes + lane * p.row_stride, src, bytes,
-                             p.split_full ? full + 8u * ((lane >> 1) & (kConsumerWarps - 1)) : full);
+                             split_full ? full + 8u * ((lane >> 1) & (kConsumerWarps - 1)) : full);
                 }
                 if (++slot == p.n_stages) {
                     slot = 0;
@@ -772,7 +775,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         for (int slice = 0; slice < p.n_slices; ++slice) {
             if (live) {
                 // keep the decision warp-uniform
-                const bool ok = wait_or_abort(smem_u32(&bar_full[g][slot][p.split_full ? wl : 0]), phase, &abort_flag, p.status, kDevTimeoutFull);
+                const bool ok = wait_or_abort(smem_u32(&bar_full[g][slot][split_full ? wl : 0]), phase, &abort_flag, p.status, kDevTimeoutFull);
                 live = __all_sync(0xffffffffu, ok);
             }
             if (live && 2 * wl < nrows) {
@@ -958,6 +961,7 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
     p.n_stages = ns;
     // measured on B200: Q4_K and Q8_0 gain at every stream length (14336 x 4096 Q4_K 8.75 -> 8.0 us,
     // 128256 x 4096 48.5 -> 46.5 us); Q6_K gains on short whole-row streams only
+    // (the option only reaches Q6_K: the other formats' kernels are compiled with the split form alone)
     p.split_full = g_opt_split_full >= 0 ? g_opt_split_full
                    : (FMT != kQ6_K && FMT != kQ6_KP) ? 1
                                          : (p.n_slices == 1 && stages_seen <= kSplitFullMaxStages ? 1 : 0);

@@ -227,8 +227,8 @@ int b200q_device_status(int* status_out);
  *   "gemv_grid"   CTA count (0 = one per SM)
  *   "pdl"         1 = launch GEMV kernels with programmatic dependent launch
  *   "gemv_groups" pipelines per CTA of the integer-dot kernel (1 or 2); "gemv_tile_pairs" 2 = prefer
- *                 one pipeline with 32-row tiles; "gemv_split_full" -1 = automatic, 0 = one full barrier
- *                 per stage, 1 = one per consumer warp and stage
+ *                 one pipeline with 32-row tiles; "gemv_split_full" (Q6_K only) -1 = automatic, 0 = one full
+ *                 barrier per stage, 1 = one per consumer warp and stage
  *   "gemm_pair"   0 = one-CTA tcgen05 kernel, otherwise the CTA-pair kernel (default)
  * Returns B200Q_ERR_BAD_ARG for an unknown key.
  */
