@@ -50,7 +50,7 @@ from brotensor_b200 import synth  # noqa: E402
 WORKLOAD = "llama3_8b_decode_layer_set_m1"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_dp_kernel<Q4_K> launch on the
 # 14336x4096 shape (profiles/gemv_dp_q4k_14336x4096_m1.md)
-DOMINANT_KERNEL_DRAM_TRAFFIC = 33112320
+DOMINANT_KERNEL_DRAM_TRAFFIC = 33112064
 L2_BYTES = 126 * 1024 * 1024
 
 
