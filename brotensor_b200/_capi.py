@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "lib", "libb200q.so")
+# B200Q_LIB selects another build of the same library (the trace build, `python -m brotensor_b200.build --trace`)
+LIB_PATH = os.environ.get("B200Q_LIB") or os.path.join(PKG, "lib", "libb200q.so")
 
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = 1, 2, 3, 4, 5

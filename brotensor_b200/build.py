@@ -42,19 +42,22 @@ def _run(cmd):
     return r.stdout + r.stderr
 
 
-def build_kernels(force: bool = False, verbose: bool = False) -> str:
+def build_kernels(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """libb200q.so; with `trace`, libb200q_trace.so: the same sources with -DB200Q_TRACE, whose decode GEMV
+    stamps %globaltimer at the phases of a launch (read by `bench.py --phases`)."""
     os.makedirs(LIBDIR, exist_ok=True)
-    os.makedirs(OBJDIR, exist_ok=True)
+    objdir = os.path.join(OBJDIR, "trace") if trace else OBJDIR
+    os.makedirs(objdir, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(ROOT, "include", "b200q.h"))
     objs = []
     procs = []
     for src in KERNEL_SOURCES:
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJDIR, src.replace(".cu", ".o"))
+        o = os.path.join(objdir, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _newer([s] + headers, o):
-            cmd = [NVCC] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [NVCC] + NVCC_FLAGS + (["-DB200Q_TRACE"] if trace else []) + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for cmd, p in procs:
         out, _ = p.communicate()
@@ -63,7 +66,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError("nvcc failed on " + cmd[-3])
         if verbose:
             sys.stderr.write(out)
-    lib = os.path.join(LIBDIR, "libb200q.so")
+    lib = os.path.join(LIBDIR, "libb200q_trace.so" if trace else "libb200q.so")
     if force or procs or _newer(objs, lib):
         _run([NVCC] + ARCH + ["-shared", "-o", lib] + objs + ["-lcudart"])
     return lib
@@ -110,4 +113,6 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
 
 if __name__ == "__main__":
     build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    if "--trace" in sys.argv:
+        build_kernels(force="--force" in sys.argv, trace=True)
     print("built:", ", ".join(sorted(os.listdir(LIBDIR))))

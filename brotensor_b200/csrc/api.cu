@@ -30,6 +30,8 @@ int gemm_get_pair();
 void dp_set_groups(int v);
 void dp_set_tile_pairs(int v);
 void dp_set_split_full(int v);
+void dp_set_wait_limit_us(int v);
+int dp_get_wait_limit_us();
 int dp_get_tile_pairs();
 int dp_get_groups();
 int stream_get_option(int which);
@@ -58,7 +60,7 @@ __device__ int g_dev_status;
 
 constexpr int kMaxDev = 64;
 struct DevInfo {
-    bool ready = false;
+    std::atomic<bool> ready{false};  // set last, with release ordering: a thread that sees it sees the fields below
     int sms = 0;
     size_t smem_optin = 0;
     int* status = nullptr;
@@ -74,9 +76,9 @@ static int dev_info(DevInfo** out) {
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDev) return fail(B200Q_ERR_CUDA, "device ordinal %d out of range", dev);
     DevInfo& d = g_dev[dev];
-    if (!d.ready) {
+    if (!d.ready.load(std::memory_order_acquire)) {
         std::lock_guard<std::mutex> lk(g_dev_mu);
-        if (!d.ready) {
+        if (!d.ready.load(std::memory_order_relaxed)) {
             int sms = 0, smem = 0;
             B200Q_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
             B200Q_CUDA_TRY(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
@@ -86,14 +88,14 @@ static int dev_info(DevInfo** out) {
             d.smem_optin = (size_t)smem;
             d.status = static_cast<int*>(p);
             for (auto& c : d.tc_calls) c.store(0);
-            d.ready = true;
+            d.ready.store(true, std::memory_order_release);
         }
     }
     *out = &d;
     return B200Q_OK;
 }
 
-int* device_status_word(int dev) { return (dev >= 0 && dev < kMaxDev && g_dev[dev].ready) ? g_dev[dev].status : nullptr; }
+int* device_status_word(int dev) { return (dev >= 0 && dev < kMaxDev && g_dev[dev].ready.load(std::memory_order_acquire)) ? g_dev[dev].status : nullptr; }
 
 static int g_opt_gemv_path = 0;
 static int g_opt_gemm_path = 0;
@@ -428,6 +430,7 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "gemv_tile_pairs")) dp_set_tile_pairs(value);
     else if (!strcmp(key, "gemv_split_full")) dp_set_split_full(value);
     else if (!strcmp(key, "gemm_pair")) gemm_set_pair(value);
+    else if (!strcmp(key, "wait_limit_us")) dp_set_wait_limit_us(value);
     else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
     return B200Q_OK;
 }
@@ -442,6 +445,7 @@ int b200q_get_option(const char* key, int* out) {
     else if (!strcmp(key, "gemv_groups")) *out = dp_get_groups();
     else if (!strcmp(key, "gemv_tile_pairs")) *out = dp_get_tile_pairs();
     else if (!strcmp(key, "gemm_pair")) *out = gemm_get_pair();
+    else if (!strcmp(key, "wait_limit_us")) *out = dp_get_wait_limit_us();
     else return fail(B200Q_ERR_BAD_ARG, "get_option: unknown key '%s'", key);
     return B200Q_OK;
 }

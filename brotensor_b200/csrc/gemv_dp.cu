@@ -31,6 +31,19 @@
 
 namespace b200q {
 
+// Trace builds (-DB200Q_TRACE, `python -m brotensor_b200.build --trace`) stamp %globaltimer at the phases of a
+// launch into slot k of the CTA's sixteen-word record; the product build carries none of it.
+#ifdef B200Q_TRACE
+#define TRACE_STAMP(cond, k)                                                               \
+    do {                                                                                   \
+        if (p.trace && (cond)) p.trace[(size_t)blockIdx.x * 16 + (k)] = global_timer_ns(); \
+    } while (0)
+#else
+#define TRACE_STAMP(cond, k) \
+    do {                     \
+    } while (0)
+#endif
+
 __device__ __forceinline__ int dp2a_lo_su(uint32_t x, uint32_t b, int c) {  // signed x pairs, unsigned bytes
     int d;
     asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(b), "r"(c));
@@ -59,30 +72,44 @@ __device__ __forceinline__ int dp2a_hi_ss(uint32_t x, uint32_t b, int c) {
 // traffic below goes through explicit ld.shared / st.shared with 32-bit addresses.
 constexpr int kXGroupStride = 272;
 
-template <typename XT>
-__device__ __forceinline__ void x_load_seg(const void* base, int K, int idx, float (&v)[8]) {
-    const XT* X = static_cast<const XT*>(base);
+// Eight consecutive activations (segment `idx` of the M x K matrix) as floats, whatever the element
+// type: the type is a run-time switch around the load alone, so that the staging code exists once
+// per kernel instead of once per type (it used to be two thirds of the kernel's instructions, all of
+// them fetched cold at every launch).
+__device__ __forceinline__ void x_load_seg(const void* base, int x_dtype, int K, int idx, float (&v)[8]) {
     const int segs = K >> 3;
     const int m = idx / segs, seg = idx - m * segs;
-    if constexpr (sizeof(XT) == 4) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(X + (size_t)m * K) + 2 * seg);
-        const float4 b = __ldg(reinterpret_cast<const float4*>(X + (size_t)m * K) + 2 * seg + 1);
+    if (x_dtype == B200Q_DT_F32) {
+        const float4* X = reinterpret_cast<const float4*>(static_cast<const float*>(base) + (size_t)m * K) + 2 * seg;
+        const float4 a = __ldg(X), b = __ldg(X + 1);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
         v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
     } else {
-        union {
-            uint4 q;
-            XT h[8];
-        } pk;
-        pk.q = __ldg(reinterpret_cast<const uint4*>(X + (size_t)m * K) + seg);
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(base) + (size_t)m * K) + seg);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        if (x_dtype == B200Q_DT_F16) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) v[k] = to_f32<XT>(pk.h[k]);
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+                v[2 * k] = f.x;
+                v[2 * k + 1] = f.y;
+            }
+        } else {  // BF16: the upper half of an FP32
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                v[2 * k] = __uint_as_float(w[k] << 16);
+                v[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+            }
+        }
     }
 }
 
 // One segment (eight consecutive activations) of the staged image; called by whole warps.
+// (Inlined on purpose: as a function of its own it cost every launch close to a microsecond.)
 template <int FMT>
-__device__ __forceinline__ void x_store_seg(const StreamParams& p, uint32_t sbase, int idx, const float (&v)[8]) {
+__device__ __forceinline__ void x_store_seg(
+    const StreamParams& p, uint32_t sbase, int idx, float4 lo, float4 hi) {
+    const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     const int segs = p.K >> 3, groups = p.K >> 7;
     const int m = idx / segs, seg = idx - m * segs;
     const int gg = seg >> 4, i = seg & 15;
@@ -125,14 +152,14 @@ __device__ __forceinline__ void x_store_seg(const StreamParams& p, uint32_t sbas
 // Stages the activations as int16 with one power-of-two scale per 128-element group. A thread's
 // global loads go out four segments at a time before any of them is converted, so a long row
 // (K = 14336: 3.5 segments per thread) costs one load latency instead of one per segment.
-template <int FMT, typename XT>
+template <int FMT>
 __device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase, int tid, int nthreads) {
     const int total = (p.K >> 3) * p.M;  // K % 256 == 0, so a multiple of 32: whole warps are in or out
     if (total <= nthreads) {  // at most one segment per thread (K = 4096, one activation row)
         if (tid < total) {
             float v[8];
-            x_load_seg<XT>(p.X, p.K, tid, v);
-            x_store_seg<FMT>(p, sbase, tid, v);
+            x_load_seg(p.X, p.x_dtype, p.K, tid, v);
+            x_store_seg<FMT>(p, sbase, tid, make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]));
         }
         return;
     }
@@ -140,10 +167,11 @@ __device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase,
         float v[4][8];
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-            if (base + u * nthreads < total) x_load_seg<XT>(p.X, p.K, base + u * nthreads, v[u]);
+            if (base + u * nthreads < total) x_load_seg(p.X, p.x_dtype, p.K, base + u * nthreads, v[u]);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-            if (base + u * nthreads < total) x_store_seg<FMT>(p, sbase, base + u * nthreads, v[u]);
+            if (base + u * nthreads < total)
+                x_store_seg<FMT>(p, sbase, base + u * nthreads, make_float4(v[u][0], v[u][1], v[u][2], v[u][3]), make_float4(v[u][4], v[u][5], v[u][6], v[u][7]));
     }
 }
 
@@ -152,13 +180,13 @@ __device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase,
 // scale itself (K values from L2), so the normalised vector is never written out and the
 // normalisation costs no launch. `red` is 32 floats of shared memory; called by `nthreads`
 // threads that meet on named barrier 1.
-template <int FMT, typename XT>
+template <int FMT>
 __device__ __forceinline__ void stage_x16_norm(const StreamParams& p, uint32_t sbase, int tid, int nthreads, float* red) {
     const int total = p.K >> 3;  // a multiple of 32: whole warps are in or out
     float ss = 0.f;
     for (int idx = tid; idx < total; idx += nthreads) {
         float v[8];
-        x_load_seg<XT>(p.X, p.K, idx, v);
+        x_load_seg(p.X, p.x_dtype, p.K, idx, v);
 #pragma unroll
         for (int k = 0; k < 8; ++k) ss = fmaf(v[k], v[k], ss);
     }
@@ -171,11 +199,11 @@ __device__ __forceinline__ void stage_x16_norm(const StreamParams& p, uint32_t s
     const float rr = rsqrtf(sum / (float)p.K + p.norm_eps);
     for (int idx = tid; idx < total; idx += nthreads) {
         float v[8], w[8];
-        x_load_seg<XT>(p.X, p.K, idx, v);
-        x_load_seg<XT>(p.norm_gamma, p.K, idx, w);  // gamma is read like an activation row
+        x_load_seg(p.X, p.x_dtype, p.K, idx, v);
+        x_load_seg(p.norm_gamma, p.x_dtype, p.K, idx, w);  // gamma is read like an activation row
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = v[k] * rr * w[k];
-        x_store_seg<FMT>(p, sbase, idx, v);
+        x_store_seg<FMT>(p, sbase, idx, make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]));
     }
 }
 
@@ -605,7 +633,7 @@ __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_beg
                     unsigned int v;
                     asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
                     if ((int)(v - epoch) >= 0) break;
-                    if (global_timer_ns() - t0 > 1000000000ull) {  // one second: a peer never arrived
+                    if (global_timer_ns() - t0 > (p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs)) {  // a peer never arrived
                         if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
                         ok = false;
                         break;
@@ -656,7 +684,7 @@ __device__ __forceinline__ TileRef tile_ref(const StreamParams& p, int vrow) {
 // two fused forms compiled into the plain GEMV the seven-launch layer set took 49.2 instead of
 // 44.0 us; with everything in one extended kernel the four-launch set took 40.9 instead of 35.6 us).
 template <int FMT, int MT, int NG, int RP, int EXT = 0>
-__global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_kernel(const StreamParams p) {
+__global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_kernel(const __grid_constant__ StreamParams p) {
     constexpr int TR = kTileRows * RP;
     // Q4_K and Q8_0 always run with one full barrier per consumer warp; only Q6_K chooses at run time.
     constexpr bool kSplitAlways = FMT != kQ6_K && FMT != kQ6_KP;
@@ -673,30 +701,39 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     __shared__ float norm_red[32];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int G = gridDim.x;
     // virtual rows of the launch: the matrix's rows, or with several matrices their tile-padded concatenation
     const int vrows = ((EXT & kExtSeg) && p.n_seg > 1) ? kTileRows * p.seg_tile0[p.n_seg] : p.N;
-    const int row_begin = p.n_tiles_total > 0 ? min(vrows, TR * (int)((long long)p.n_tiles_total * blockIdx.x / G))
-                                              : (int)((long long)vrows * blockIdx.x / G);
-    const int row_end = p.n_tiles_total > 0 ? min(vrows, TR * (int)((long long)p.n_tiles_total * (blockIdx.x + 1) / G))
-                                            : (int)((long long)vrows * (blockIdx.x + 1) / G);
+    // This CTA's share of the launch's units (whole tiles when n_tiles_total > 0, else rows): the
+    // first split_r CTAs have split_q + 1 of them, the others split_q.
+    const int cta = (int)blockIdx.x;
+    const int unit_first = cta * p.split_q + min(cta, p.split_r), unit_count = p.split_q + (cta < p.split_r ? 1 : 0);
+    const int row_begin = p.n_tiles_total > 0 ? min(vrows, TR * unit_first) : unit_first;
+    const int row_end = p.n_tiles_total > 0 ? min(vrows, TR * (unit_first + unit_count)) : unit_first + unit_count;
     const int n_tiles = (row_end - row_begin + TR - 1) / TR;
     const int stage_bytes = TR * p.row_stride;
-
-    if (tid == 0) abort_flag = 0;
-    if (tid < NG * kMaxStages * (kConsumerWarps + 1)) {  // one barrier per thread
-        const int g = tid / (kMaxStages * (kConsumerWarps + 1));
-        const int s = (tid / (kConsumerWarps + 1)) % kMaxStages, j = tid % (kConsumerWarps + 1);
-        if (s < p.n_stages) {
-            if (j < kConsumerWarps) mbar_init(smem_u32(&bar_full[g][s][j]), 1);
-            else mbar_init(smem_u32(&bar_empty[g][s]), kConsumerWarps);
-            fence_mbar_init();
-        }
-    }
-    __syncthreads();
-    grid_dep_launch();
+    const uint64_t wait_limit = p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs;
+    TRACE_STAMP(tid == 0, 0);
 
     constexpr int kConsumers = kConsumerWarps * NG;
+    // Each producer warp sets up its own pipeline's barriers and goes straight on to its first weight
+    // copies; the consumers meet the producers' arrival on named barrier 2 before they touch a barrier.
+    if (warp >= kConsumers) {
+        const int pg = warp - kConsumers;
+        if (lane == 0) abort_flag = 0;  // every producer writes the same value, long before any wait can run out
+        for (int i = lane; i < p.n_stages * (kConsumerWarps + 1); i += 32) {
+            const int st = i / (kConsumerWarps + 1), j = i - st * (kConsumerWarps + 1);
+            if (j < kConsumerWarps) mbar_init(smem_u32(&bar_full[pg][st][j]), 1);
+            else mbar_init(smem_u32(&bar_empty[pg][st]), kConsumerWarps);
+        }
+        fence_mbar_init();
+        __syncwarp();
+        asm volatile("bar.arrive 2, %0;" ::"n"((kConsumers + NG) * 32) : "memory");
+    } else {
+        asm volatile("bar.sync 2, %0;" ::"n"((kConsumers + NG) * 32) : "memory");
+    }
+    grid_dep_launch();
+    TRACE_STAMP(tid == 0, 1);
+
     if (warp >= kConsumers) {
         // ---- producer of pipeline g: weights do not depend on the stream-ordered
         // predecessor, so the copies start before griddepcontrol.wait
@@ -709,7 +746,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
             const int row0 = tr.row0;
             const int nrows = min(min(TR, row_end - (row_begin + tile * TR)), tr.N - row0);
             for (int slice = 0; slice < p.n_slices; ++slice) {
-                if (!wait_or_abort(smem_u32(&bar_empty[g][slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty)) return;
+                if (!wait_or_abort(smem_u32(&bar_empty[g][slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty, wait_limit)) return;
                 const int c0 = slice * p.slice_chunks;
                 const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
                 const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
@@ -730,27 +767,26 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                     bulk_g2s(ring + slot * stage_bytes + lane * p.row_stride, src, bytes,
                              split_full ? full + 8u * ((lane >> 1) & (kConsumerWarps - 1)) : full);
                 }
+                TRACE_STAMP(g == 0 && lane == 0 && tile == 0 && slice == 0, 7);
                 if (++slot == p.n_stages) {
                     slot = 0;
                     phase ^= 1;
                 }
             }
         }
+        TRACE_STAMP(g == 0 && lane == 0, 8);
         return;
     }
 
     // ---- consumers
     grid_dep_wait();  // activations (and Y) belong to the stream-ordered predecessor
+    TRACE_STAMP(tid == 0, 2);
     // launch counter of the sharded form: stable while this launch runs (only its last CTA bumps it)
     const unsigned int sh_epoch = ((EXT & kExtShard) && p.sh_world > 0) ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
     const unsigned int sh_buf = (sh_epoch + 1u) & 1u;
-    if ((EXT & kExtNorm) && MT == 1 && p.norm_gamma) {
-        if (p.x_dtype == B200Q_DT_F32) stage_x16_norm<FMT, float>(p, sbase, tid, kConsumers * 32, norm_red);
-        else if (p.x_dtype == B200Q_DT_F16) stage_x16_norm<FMT, __half>(p, sbase, tid, kConsumers * 32, norm_red);
-        else stage_x16_norm<FMT, __nv_bfloat16>(p, sbase, tid, kConsumers * 32, norm_red);
-    } else if (p.x_dtype == B200Q_DT_F32) stage_x16<FMT, float>(p, sbase, tid, kConsumers * 32);
-    else if (p.x_dtype == B200Q_DT_F16) stage_x16<FMT, __half>(p, sbase, tid, kConsumers * 32);
-    else stage_x16<FMT, __nv_bfloat16>(p, sbase, tid, kConsumers * 32);
+    if ((EXT & kExtNorm) && MT == 1 && p.norm_gamma) stage_x16_norm<FMT>(p, sbase, tid, kConsumers * 32, norm_red);
+    else stage_x16<FMT>(p, sbase, tid, kConsumers * 32);
+    TRACE_STAMP(tid == 0, 3);
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
 
     const XAddr xa = {sbase + (uint32_t)p.off_xhi, sbase + (uint32_t)p.off_xlo, sbase + (uint32_t)p.off_sxhi, p.K >> 7, p.K};
@@ -760,6 +796,10 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     bool live = true;
     int slot = 0;
     uint32_t phase = 0;
+    // Deferred reduction (see the end of the tile loop): sums of the up to three tiles before the current one.
+    constexpr bool kDefer = MT == 1 && RP == 1 && !(EXT & kExtSwiglu);
+    float hold[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+    int held = 0;
     float acc[RP][2][MT];
 #pragma unroll
     for (int pi = 0; pi < RP; ++pi)
@@ -775,9 +815,10 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         for (int slice = 0; slice < p.n_slices; ++slice) {
             if (live) {
                 // keep the decision warp-uniform
-                const bool ok = wait_or_abort(smem_u32(&bar_full[g][slot][split_full ? wl : 0]), phase, &abort_flag, p.status, kDevTimeoutFull);
+                const bool ok = wait_or_abort(smem_u32(&bar_full[g][slot][split_full ? wl : 0]), phase, &abort_flag, p.status, kDevTimeoutFull, wait_limit);
                 live = __all_sync(0xffffffffu, ok);
             }
+            TRACE_STAMP(tid == 0 && tile == 0 && slice == 0, 4);
             if (live && 2 * wl < nrows) {
                 const int c0 = slice * p.slice_chunks;
                 const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
@@ -822,6 +863,50 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                 phase ^= 1;
             }
         }
+        if constexpr (kDefer) {
+            // One activation row, one row pair per warp: the lanes' partial sums of up to four tiles are
+            // kept and reduced together - nine shuffles for eight rows instead of five per tile, and
+            // no tile waits for its own reduction before the warp turns to the next one. Same butterfly
+            // (xor 16, 8, 4, 2, 1), hence the same bits as the per-tile form below.
+            if (++held < 4 && tile + NG < n_tiles) {
+                hold[2][0] = hold[1][0]; hold[2][1] = hold[1][1];
+                hold[1][0] = hold[0][0]; hold[1][1] = hold[0][1];
+                hold[0][0] = acc[0][0][0]; hold[0][1] = acc[0][1][0];
+            } else {
+                const float v[8] = {hold[2][0], hold[2][1], hold[1][0], hold[1][1], hold[0][0], hold[0][1], acc[0][0][0], acc[0][1][0]};
+                const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
+                float w4[4], w2[2];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w4[i] = (h16 ? v[4 + i] : v[i]) + __shfl_xor_sync(0xffffffffu, h16 ? v[i] : v[4 + i], 16);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) w2[i] = (h8 ? w4[2 + i] : w4[i]) + __shfl_xor_sync(0xffffffffu, h8 ? w4[i] : w4[2 + i], 8);
+                float s = (h4 ? w2[1] : w2[0]) + __shfl_xor_sync(0xffffffffu, h4 ? w2[0] : w2[1], 4);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                const int o = (h16 ? 4 : 0) + (h8 ? 2 : 0) + (h4 ? 1 : 0), age = 3 - (o >> 1);  // tiles ago; row of the pair: o & 1
+                if ((lane & 3) == 0 && age < held && !*(volatile int*)&abort_flag) {
+                    const int vr = row_begin + (tile - age * NG) * TR;
+                    const TileRef t2 = tile_ref<EXT>(p, vr);
+                    const int nr = min(min(TR, row_end - vr), t2.N - t2.row0), rr = 2 * wl + (o & 1);
+                    if (rr < nr) {
+                        const int n = t2.row0 + rr;
+                        if (t2.bias) {
+                            if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(t2.bias)[n];
+                            else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(t2.bias)[n]);
+                            else s += __bfloat162float(static_cast<const __nv_bfloat16*>(t2.bias)[n]);
+                        }
+                        if ((EXT & kExtShard) && p.sh_world > 0) p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
+                        else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(t2.Y)[n] = s;
+                        else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(t2.Y)[n] = __float2half_rn(s);
+                        else static_cast<__nv_bfloat16*>(t2.Y)[n] = __float2bfloat16_rn(s);
+                    }
+                }
+                held = 0;
+                hold[0][0] = hold[0][1] = hold[1][0] = hold[1][1] = hold[2][0] = hold[2][1] = 0.f;
+            }
+            acc[0][0][0] = acc[0][1][0] = 0.f;
+            continue;
+        }
         // the rows' partial sums live in this warp's lanes: lanes 0..15 finish the first
         // row of the pair, lanes 16..31 the second (five shuffles for both), then write
 #pragma unroll
@@ -865,6 +950,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
             }
         }
     }
+    TRACE_STAMP((tid & 31) == 0, 5 + (warp >= kConsumerWarps ? 1 : 0));  // last writer of each pipeline wins: about its end
     if ((EXT & kExtShard) && p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32);
 }
 
@@ -883,6 +969,21 @@ static int g_opt_split_full = -1;
 void dp_set_split_full(int v) { g_opt_split_full = v < 0 ? -1 : (v ? 1 : 0); }
 void dp_set_groups(int v) { g_opt_groups = v < 1 ? 1 : (v > 2 ? 2 : v); }
 int dp_get_groups() { return g_opt_groups; }
+// Bound of the kernels' mbarrier and peer-arrival waits in microseconds; 0: one second.
+static int g_opt_wait_limit_us = 0;
+void dp_set_wait_limit_us(int v) { g_opt_wait_limit_us = v < 0 ? 0 : v; }
+int dp_get_wait_limit_us() { return g_opt_wait_limit_us; }
+#ifdef B200Q_TRACE
+static unsigned long long* g_trace_buf = nullptr;
+static int g_trace_cap = 0, g_trace_idx = 0;
+constexpr int kTraceCtas = 160;
+// Trace builds only: the next `launches` GEMV launches write their stamps to buf[launch][160 CTAs][16].
+extern "C" void b200q_trace_set(void* buf, int launches) {
+    g_trace_buf = static_cast<unsigned long long*>(buf);
+    g_trace_cap = launches;
+    g_trace_idx = 0;
+}
+#endif
 
 // p.n_stages is the ring depth of ONE pipeline; `ng` pipelines share the shared memory.
 template <int FMT>
@@ -970,8 +1071,19 @@ static bool plan_dp(int M, int N, int K, int sms, size_t smem_max, int ng, int r
 }
 
 template <int FMT, int MT, int NG, int RP, int EXT = 0>
-static int launch_dp_k(const StreamParams& p, int grid, size_t smem, cudaStream_t st) {
+static int launch_dp_k(const StreamParams& p_in, int grid, size_t smem, cudaStream_t st) {
     auto kern = gemv_dp_kernel<FMT, MT, NG, RP, EXT>;
+    StreamParams p = p_in;
+    {
+        const int vrows = ((EXT & kExtSeg) && p.n_seg > 1) ? kTileRows * p.seg_tile0[p.n_seg] : p.N;
+        const int units = p.n_tiles_total > 0 ? p.n_tiles_total : vrows;
+        p.split_q = units / grid;
+        p.split_r = units % grid;
+    }
+    p.wait_limit_us = (unsigned int)g_opt_wait_limit_us;
+#ifdef B200Q_TRACE
+    p.trace = (g_trace_buf && g_trace_idx < g_trace_cap && grid <= kTraceCtas) ? g_trace_buf + (size_t)(g_trace_idx++) * kTraceCtas * 16 : nullptr;
+#endif
     static bool configured[64] = {};
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));

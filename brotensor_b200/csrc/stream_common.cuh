@@ -30,6 +30,13 @@ struct StreamParams {
     int n_stages;        // ring depth
     int n_tiles_total;   // > 0: CTAs own whole 16-row tiles (tile-balanced grid); 0: rows split evenly
     int split_full;      // 1: one full barrier per consumer warp and stage; 0: one per stage
+    // The launch's units - whole tiles when n_tiles_total > 0, else rows - over the grid: CTA b has
+    // split_q + (b < split_r) of them, starting at b * split_q + min(b, split_r) (no division on the device).
+    int split_q, split_r;
+    unsigned int wait_limit_us;  // bound of the device-side waits in microseconds (0: one second)
+#ifdef B200Q_TRACE
+    unsigned long long* trace;  // trace builds: sixteen %globaltimer stamps per CTA of this launch
+#endif
     // shared-memory offsets (bytes from the 128-byte aligned base)
     int off_xhi, off_xlo, off_sxhi, off_sxlo, off_red, off_stage;
     // Several weight matrices of one format and K that share the activation vector (n_seg > 1):
@@ -75,10 +82,28 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 
 // Bounded mbarrier wait with an abort flag shared by the CTA. Returns false when
 // the wait was abandoned (by this thread's timeout or because another thread of
-// the CTA already gave up).
+// the CTA already gave up). A phase that is complete already costs one try_wait and a branch:
+// the timer is read only when the thread has to wait.
+// (Measured: the waiting part as a function of its own, not inlined, made every decode GEMV 1 to 10 %
+// slower - a kernel with a call in it gets a worse register allocation around its hot loop.)
+__device__ __forceinline__ bool wait_or_abort_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                                   uint64_t limit_ns) {
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > limit_ns) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+constexpr uint64_t kWaitLimitNs = 1000000000ull;  // one second
 template <bool kSpinFirst = false>
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                              int code) {
+                                              int code, uint64_t limit_ns = kWaitLimitNs) {
     // Optional fast path for a single latency-critical thread: non-blocking probes, so a
     // phase that completes soon is seen at once instead of after a parked time slice. Whole
     // warps must not use it: their probes fill the shared-memory pipeline the other warps need.
@@ -86,17 +111,8 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
         for (int i = 0; i < 256; ++i)
             if (mbar_test_wait(bar, parity)) return true;
     }
-    const uint64_t t0 = global_timer_ns();
-    for (;;) {
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > 1000000000ull) {  // one second
-            *abort_flag = 1;
-            if (status) atomicCAS(status, 0, code);
-            return false;
-        }
-    }
+    if (mbar_try_wait(bar, parity)) return true;
+    return wait_or_abort_slow(bar, parity, abort_flag, status, code, limit_ns);
 }
 
 __device__ __forceinline__ void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory"); }

@@ -126,27 +126,31 @@ void check_status(int rc, const char* op) {
     op_fail(op, msg && *msg ? msg : b200q_status_str(rc));
 }
 
-// One scratch buffer per device for the tensor-core GEMM (activations in operand
-// layout). It only grows, outside any stream capture; calls on one device are ordered
-// by the stream they share.
-struct Scratch {
+// Workspace of the tensor-core GEMM (activations in operand layout): allocated per call from the
+// stream-ordered pool on the current stream and released behind the kernel, as brotensor's batched ops
+// do (src/cuda/q4k.cu:395-411). That is legal inside a stream capture (the graph owns the allocation),
+// safe for threads on different streams, and no pointer outlives the call that a later, larger call
+// could free under a captured graph.
+struct StreamScratch {
     void* p = nullptr;
-    std::size_t n = 0;
-};
-Scratch g_scratch[64];
-std::mutex g_scratch_mu;
-void* scratch_for(int dev, std::size_t need) {
-    if (!need) return nullptr;
-    std::lock_guard<std::mutex> lk(g_scratch_mu);
-    Scratch& s = g_scratch[dev & 63];
-    if (s.n < need) {
-        if (s.p) B200_CUDA_CHECK(cudaFree(s.p));
-        s.p = nullptr;
-        s.n = 0;
-        B200_CUDA_CHECK(cudaMalloc(&s.p, need));
-        s.n = need;
+    cudaStream_t st = nullptr;
+    StreamScratch(std::size_t need, cudaStream_t s) : st(s) {
+        if (need) B200_CUDA_CHECK(cudaMallocAsync(&p, need, st));
     }
-    return s.p;
+    ~StreamScratch() {
+        if (p && cudaFreeAsync(p, st) != cudaSuccess) (void)cudaGetLastError();
+    }
+    StreamScratch(const StreamScratch&) = delete;
+    StreamScratch& operator=(const StreamScratch&) = delete;
+};
+
+// Output dtype rule shared by the ops: FP16 activations give FP16 results, always (the reference's
+// contract, src/cuda/q4k.cu:345-347, 391-393: y is retyped to FP16 whatever it held); with FP32 or
+// BF16 activations - which the reference does not accept - a pre-sized FP32 / FP16 / BF16 result of
+// the right shape is kept and anything else becomes FP32.
+bool keep_out(const Tensor& y, int rows, int cols, Dtype x_dtype) {
+    if (y.rows != rows || y.cols != cols || !y.data) return false;
+    return x_dtype == Dtype::FP16 ? y.dtype == Dtype::FP16 : act_dtype(y.dtype);
 }
 
 // The format code the kernels get: the raw one, or the regrouped one when W's storage is recorded as
@@ -175,8 +179,7 @@ void gemv_impl(int fmt, Dtype wdt, const char* dname, int block, const char* op,
         if (bias->dtype != x.dtype) op_fail(op, x.dtype == Dtype::FP16 ? "bias must be FP16" : "bias must have x's dtype");
         if (bias->rows != out || bias->cols != 1) op_fail(op, "bias shape must be (out, 1)");
     }
-    const bool keep = y.rows == out && y.cols == 1 && act_dtype(y.dtype) && y.data;
-    if (!keep) y.resize(out, 1, x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    if (!keep_out(y, out, 1, x.dtype)) y.resize(out, 1, x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
     if (out == 0) return;
     const void* b = (bias && bias->size() > 0) ? bias->data : nullptr;
     check_status(b200q_gemv(layout_fmt(fmt, W), W.data, x.data, static_cast<int>(x.dtype), b, y.data, static_cast<int>(y.dtype), 1, out,
@@ -197,7 +200,7 @@ void group_impl(const Tensor* const* W, const Tensor* const* bias, int n, const 
     void* Yp[4];
     const void* Bp[4];
     int Np[4];
-    const Dtype ydt = (y[0]->data && act_dtype(y[0]->dtype)) ? y[0]->dtype : (x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    const Dtype ydt = x.dtype == Dtype::FP16 ? Dtype::FP16 : (y[0]->data && act_dtype(y[0]->dtype)) ? y[0]->dtype : Dtype::FP32;
     for (int s = 0; s < n; ++s) {
         check_w(*W[s], wdt, dname, block, op);
         if (W[s]->cols != K) op_fail(op, "all matrices must have the same number of columns");
@@ -235,7 +238,7 @@ void group_rmsnorm_impl(const Tensor* const* W, int n, const Tensor& x, const Te
     const void* Wp[4];
     void* Yp[4];
     int Np[4];
-    const Dtype ydt = (y[0]->data && act_dtype(y[0]->dtype)) ? y[0]->dtype : (x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    const Dtype ydt = x.dtype == Dtype::FP16 ? Dtype::FP16 : (y[0]->data && act_dtype(y[0]->dtype)) ? y[0]->dtype : Dtype::FP32;
     for (int s = 0; s < n; ++s) {
         check_w(*W[s], wdt, dname, block, op);
         if (W[s]->cols != K) op_fail(op, "all matrices must have the same number of columns");
@@ -264,8 +267,7 @@ void swiglu_impl(const Tensor& Wg, const Tensor& Wu, const Tensor& x, Tensor& y)
     if (!act_dtype(x.dtype)) op_fail(op, "x must be FP16 (FP32 and BF16 are accepted as well)");
     const int out = Wg.rows, K = Wg.cols;
     if (x.rows != K || x.cols != 1) op_fail(op, "x shape must be (in, 1)");
-    const bool keep = y.rows == out && y.cols == 1 && act_dtype(y.dtype) && y.data;
-    if (!keep) y.resize(out, 1, x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    if (!keep_out(y, out, 1, x.dtype)) y.resize(out, 1, x.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
     if (out == 0) return;
     check_status(b200q_gemv_swiglu(layout_fmt(static_cast<int>(wdt), Wg), Wg.data, Wu.data, x.data, static_cast<int>(x.dtype), y.data,
                                    static_cast<int>(y.dtype), out, K, cuda_current_stream(Wg.device.index)), op);
@@ -282,16 +284,15 @@ void batched_impl(int fmt, Dtype wdt, const char* dname, int block, const char* 
         const bool ok = (bias->rows == out && bias->cols == 1) || (bias->rows == 1 && bias->cols == out);
         if (!ok) op_fail(op, "bias shape must be (out,1) or (1,out)");
     }
-    const bool keep = Y.rows == B && Y.cols == out && act_dtype(Y.dtype) && Y.data;
-    if (!keep) Y.resize(B, out, X.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
+    if (!keep_out(Y, B, out, X.dtype)) Y.resize(B, out, X.dtype == Dtype::FP16 ? Dtype::FP16 : Dtype::FP32);
     if (B == 0 || out == 0) return;
     const void* b = (bias && bias->size() > 0) ? bias->data : nullptr;
     const int dev = W.device.index;
     const int lf = layout_fmt(fmt, W);
-    std::size_t need = B > 8 ? b200q_gemm_workspace_bytes(lf, static_cast<int>(X.dtype), B, out, K) : 0;
-    void* ws = scratch_for(dev, need);
+    const std::size_t need = B > 8 ? b200q_gemm_workspace_bytes(lf, static_cast<int>(X.dtype), B, out, K) : 0;
+    const StreamScratch ws(need, cur_stream(dev));
     check_status(b200q_linear(lf, W.data, X.data, static_cast<int>(X.dtype), b, Y.data, static_cast<int>(Y.dtype), B,
-                              out, K, ws, need, cuda_current_stream(dev)), op);
+                              out, K, ws.p, need, cuda_current_stream(dev)), op);
 }
 
 #define B200_FMT_OPS(tag, FMT, DT, DNAME, BLOCK)                                                                 \
