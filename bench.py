@@ -48,8 +48,8 @@ sys.path.insert(0, ROOT)
 from brotensor_b200 import synth  # noqa: E402
 
 WORKLOAD = "llama3_8b_decode_layer_set_m1"
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_dp_kernel<Q4_K> launch on the
-# 14336x4096 shape (profiles/gemv_dp_q4k_14336x4096_m1.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (the Q4_K decode
+# GEMV on 14336x4096), from an ncu capture of `bench.py --case gemv:q4k:14336:4096:1`
 DOMINANT_KERNEL_DRAM_TRAFFIC = 33112064
 L2_BYTES = 126 * 1024 * 1024
 
@@ -185,6 +185,116 @@ def run_cpu_arm(kind_wanted: str, steps: int, warmup: int, budget_s: float = 20.
             "sample": f"{k} full passes of the 7-GEMV layer set ({nbytes} packed bytes each), {w} warm-up passes"}, k, w, dt / k * 1e3
 
 
+# --------------------------------------------------------------------------- profiling drivers
+
+_FMT = {"q4k": synth.Q4_K, "q6k": synth.Q6_K, "q8_0": synth.Q8_0}
+
+
+def lm_head_summary(extras, world):
+    """Strong-scaling result of the row-sharded LM head (config 4) lifted to the top level of the line:
+    the headline `value` is the layer set run as independent replicas ("scaling": "weak"), which says
+    nothing about sharding; this does."""
+    lh = (extras or {}).get("lm_head") or {}
+    if not lh:
+        return None
+    fused = lh.get("fused") or {}
+    out = {"workload": "Q6_K 128256x4096 LM head, M=1, vocab rows split over the ranks (strong scaling)", "n_gpus": world,
+           "variant": "one kernel: shard GEMV + peer stores + arrival words" if "us_per_token" in fused else "shard GEMV + NCCL all-gather",
+           "us_per_token": fused.get("us_per_token", lh.get("us_per_token")),
+           "tok_per_s": fused.get("tok_per_s", lh.get("tok_per_s")),
+           "nccl_all_gather_us_per_token": lh.get("us_per_token"), "shard_gemv_only_us": lh.get("gemv_only_us"),
+           "oracle_rel_l2": lh.get("oracle_rel_l2"), "matches_gathered_bitwise": fused.get("matches_gathered_bitwise")}
+    for k in ("greedy", "efficiency_note"):
+        if k in lh:
+            out[k] = lh[k]
+    return out
+
+
+def run_case(spec: str, launches: int):
+    """A few launches of one shape for a profiler: weights rotate over six replicas so that a captured
+    launch streams from DRAM; a few hundred MB on the device at most."""
+    import torch
+    from brotensor_b200 import ops
+    op, f, N, K, M = spec.split(":")
+    fmt, N, K, M = _FMT[f], int(N), int(K), int(M)
+    torch.cuda.set_device(0)
+    base = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=1)).cuda()
+    Ws = [base] + [torch.roll(base, 1028160 * (i + 1)).contiguous() for i in range(5)]
+    X = torch.from_numpy(synth.make_activations(M, K, seed=2)).cuda()
+    Y = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    for i in range(launches):
+        if op == "dequant":
+            ops.dequant(fmt, Ws[i % len(Ws)], N, K, torch.float16)
+        elif op == "gemm":
+            ops.gemm(fmt, Ws[i % len(Ws)], X, N, out=Y)
+        else:
+            ops.gemv(fmt, Ws[i % len(Ws)], X, N, out=Y)
+    torch.cuda.synchronize()
+    print("device status", ops.device_status())
+
+
+def run_phases():
+    """Where the time of a decode-GEMV launch goes, from %globaltimer stamps the trace build writes
+    (per CTA: entry, barriers ready, predecessor complete, activations staged, first tile started,
+    each pipeline's end, first and last weight copy issued). A CUDA graph chains 24 launches over
+    cold weight replicas, as the benchmark does; times are relative to the end of the launch before."""
+    import ctypes as C
+    import torch
+    from brotensor_b200 import _capi, ops
+    L = _capi.lib()
+    if not hasattr(L, "b200q_trace_set"):
+        raise SystemExit("--phases needs the trace build: python -m brotensor_b200.build --trace, then "
+                         "B200Q_LIB=brotensor_b200/lib/libb200q_trace.so python bench.py --phases")
+    L.b200q_trace_set.argtypes = [C.c_void_p, C.c_int]
+    L.b200q_trace_set.restype = None
+    torch.cuda.set_device(0)
+    ops.set_option("pdl", 1)
+    n_launch = 24
+    rows = []
+    for N in (1024, 4096, 14336):
+        fmt, K = synth.Q4_K, 4096
+        nbytes = synth.packed_bytes(fmt, N, K)
+        R = max(2, min(32, int(1.0e9 // nbytes)))
+        base = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=1)).cuda()
+        Ws = [base] + [torch.roll(base, 1028160 * (i + 1)).contiguous() for i in range(R - 1)]
+        X = torch.from_numpy(synth.make_activations(1, K, seed=2)).cuda()
+        Y = torch.empty((1, N), dtype=torch.float32, device="cuda")
+        buf = torch.zeros((n_launch, 160, 16), dtype=torch.int64, device="cuda")
+        L.b200q_trace_set(None, 0)
+        for i in range(3):
+            ops.gemv(fmt, Ws[i % R], X, N, out=Y)
+        torch.cuda.synchronize()
+        L.b200q_trace_set(buf.data_ptr(), n_launch)
+        g, st = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(n_launch):
+                ops.gemv(fmt, Ws[i % R], X, N, out=Y)
+        L.b200q_trace_set(None, 0)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); g.replay(); e1.record(); torch.cuda.synchronize()
+        t = buf.cpu().numpy().astype(np.int64)
+        acc = {}
+        for i in range(4, n_launch - 1):
+            c = t[i][t[i][:, 0] > 0]
+            pv = t[i - 1][t[i - 1][:, 0] > 0]
+            pend = max(pv[:, 5].max(), pv[:, 6].max())
+            end = np.maximum(c[:, 5], c[:, 6])
+            for k, v in (("ctas", len(c)), ("period", end.max() - pend), ("entry", np.median(c[:, 0] - pend)),
+                         ("barriers_ready", np.median(c[:, 1] - pend)), ("first_copy_issued", np.median(c[:, 7] - pend)),
+                         ("predecessor_complete", np.median(c[:, 2] - pend)), ("x_staged", np.median(c[:, 3] - pend)),
+                         ("first_tile_started", np.median(c[:, 4] - pend)), ("last_copy_issued", np.median(c[:, 8] - pend)),
+                         ("cta_end_median", np.median(end - pend)), ("cta_end_last", end.max() - pend)):
+                acc.setdefault(k, []).append(float(v))
+        row = {"shape": f"q4k {N}x{K} M=1", "us_per_launch_under_trace": round(e0.elapsed_time(e1) / n_launch * 1e3, 2)}
+        row.update({k: round(float(np.median(v))) for k, v in acc.items()})
+        rows.append(row)
+        print(json.dumps(row), flush=True)
+    print("device status", ops.device_status())
+
+
 # --------------------------------------------------------------------------- GPU arm
 
 def main():
@@ -196,7 +306,17 @@ def main():
     ap.add_argument("--replicas", type=int, default=8)
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, metavar="OP:FMT:N:K:M",
+                    help="profiling driver: a handful of launches of one shape (op gemv|gemm|dequant, fmt q4k|q6k|q8_0) and nothing else")
+    ap.add_argument("--launches", type=int, default=4, help="launches of --case")
+    ap.add_argument("--phases", action="store_true",
+                    help="phase breakdown of the decode GEMV from %%globaltimer stamps (needs the trace build: "
+                         "python -m brotensor_b200.build --trace; B200Q_LIB=brotensor_b200/lib/libb200q_trace.so)")
     args = ap.parse_args()
+    if args.case:
+        return run_case(args.case, args.launches)
+    if args.phases:
+        return run_phases()
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -282,9 +402,19 @@ def main():
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    # the timed region is repeated to give the clock sampler something to see; the
-    # reported time is the mean over identical K-step graphs
-    reps = 5
+    # The K-step graph is replayed until the timed region covers at least 0.3 s (a single replay is
+    # a few milliseconds: too short for the clock sampler and for a stable median); every replay is
+    # timed on its own with CUDA events, the reported time is the median, the minimum goes along.
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    one_ms = max(e0.elapsed_time(e1), 1e-3)
+    reps = int(min(400, max(5, 300.0 / one_ms + 1)))
+    t = torch.tensor([float(reps)], device="cuda")
+    if world > 1:  # the same number of replays on every rank
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    reps = int(t.item())
     times = []
     for _ in range(reps):
         e0.record()
@@ -297,6 +427,8 @@ def main():
     torch.cuda.synchronize()
     clocks = sampler.stop()
     ms_total = float(np.median(times))
+    ms_min = float(np.min(times))
+    config["timed_region"] = f"{reps} replays of the {K_steps}-step graph, {sum(times) / 1e3:.2f} s in all; median per replay reported"
     t = torch.tensor([ms_total], device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -326,7 +458,7 @@ def main():
     roofline = {"bound": "hbm", "kernel": "gemv_dp_kernel<Q4_K, M=1> on 14336x4096 (gate_proj / up_proj)", "achieved": achieved,
                 "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": DOMINANT_KERNEL_DRAM_TRAFFIC,
-                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch (profiles/)",
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch",
                 "algorithmic_bytes_per_launch": alg_bytes,
                 "us_per_launch": dom_ms * 1e3}
 
@@ -409,7 +541,7 @@ def main():
     extras = {}
     if not args.no_extras:
         try:
-            from brotensor_b200 import bench_extras
+            import bench_extras
             extras = bench_extras.run(rank, world, peaks, cap_stream)
         except Exception as ex:  # extras never take the headline down
             extras = {"error": repr(ex)}
@@ -424,6 +556,7 @@ def main():
             "steps": K_steps, "warmup": W_steps, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
             "frac_of_hbm_peak": value / world / peaks["hbm_gbs"], "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "ms_per_step_min": ms_min / K_steps, "lm_head": lm_head_summary(extras, world),
             "e2e": e2e, "gpu_launches": 7 * K_steps, "clocks": clocks, "extras": extras,
             "setup_s": round(time.time() - t_setup, 1)}))
     if world > 1:

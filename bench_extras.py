@@ -15,7 +15,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-from . import ops, shard, synth
+from brotensor_b200 import ops, shard, synth
 
 
 def _time_graph(fn, n_launch, stream, reps=10):
@@ -36,11 +36,13 @@ def _time_graph(fn, n_launch, stream, reps=10):
     return float(np.median(ts)), float(np.min(ts))  # ms per launch
 
 
-def _replicas(fmt, N, K, seed, budget_bytes=1.2e9, cap=32):
+def _replicas(fmt, N, K, seed, budget_bytes=1.2e9, cap=32, want_host=False):
     nbytes = synth.packed_bytes(fmt, N, K)
     R = int(max(2, min(cap, budget_bytes // nbytes)))
-    base = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=seed)).cuda()
-    return [base] + [torch.roll(base, 1028160 * (i + 1)).contiguous() for i in range(R - 1)], nbytes
+    host = synth.make_blocks(fmt, N, K, seed=seed)
+    base = torch.from_numpy(host).cuda()
+    reps = [base] + [torch.roll(base, 1028160 * (i + 1)).contiguous() for i in range(R - 1)]
+    return (reps, nbytes, host) if want_host else (reps, nbytes)
 
 
 def gemv_case(fmt, N, K, M, stream, peak_gbs, n_launch=48):
@@ -59,7 +61,7 @@ def gemm_case(fmt, N, K, M, x_dtype, stream, peaks, n_launch=8):
     W = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=3)).cuda()
     X = torch.from_numpy(synth.make_activations(M, K, seed=3)).cuda().to(x_dtype)
     Y = torch.empty((M, N), dtype=torch.float32, device="cuda")
-    from . import _capi
+    from brotensor_b200 import _capi
     need = _capi.lib().b200q_gemm_workspace_bytes(fmt, ops._DT[x_dtype], M, N, K)
     ws = torch.empty(max(need, 256), dtype=torch.uint8, device="cuda")
     for _ in range(3):
@@ -84,10 +86,23 @@ def lm_head_case(rank, world, stream, peak_gbs, n_launch=16):
     assert rows * world == N, "the LM-head benchmark wants equal shards"
     # each rank generates only its shard (seeded per shard, so the content is independent of world size
     # only in distribution; parity of the sharded path is covered by the tests)
-    Ws, nbytes = _replicas(fmt, rows, K, seed=4000 + rank, budget_bytes=1.0e9, cap=6)
-    x = torch.from_numpy(synth.make_activations(1, K, seed=4)).cuda()
+    Ws, nbytes, W_host = _replicas(fmt, rows, K, seed=4000 + rank, budget_bytes=1.0e9, cap=6, want_host=True)
+    x_host = synth.make_activations(1, K, seed=4)
+    x = torch.from_numpy(x_host).cuda()
     local = torch.empty((1, rows), dtype=torch.float32, device="cuda")
     full = torch.empty((world, rows), dtype=torch.float32, device="cuda")
+    # parity gate before anything is timed: this rank's shard against the CPU oracle on its own rows
+    import os
+    import oracle
+    ops.gemv(fmt, Ws[0], x, rows, out=local)
+    torch.cuda.synchronize()
+    err = oracle.rel_l2(local.cpu().numpy(), oracle.cpu().matmul(fmt, W_host, x_host, threads=max(1, (os.cpu_count() or 1) // max(world, 1))))
+    del W_host
+    e_t = torch.tensor([err], device="cuda")
+    if world > 1:
+        dist.all_reduce(e_t, op=dist.ReduceOp.MAX)
+    err = float(e_t.item())
+    assert err < 2e-3, f"LM-head shard parity failed: rel-L2 {err}"
 
     def step(i):
         ops.gemv(fmt, Ws[i % len(Ws)], x, rows, out=local)
@@ -97,7 +112,7 @@ def lm_head_case(rank, world, stream, peak_gbs, n_launch=16):
     for i in range(3):
         step(i)
     torch.cuda.synchronize()
-    out = {"fmt": "q6k", "N": N, "K": K, "ranks": world, "rows_per_rank": rows}
+    out = {"fmt": "q6k", "N": N, "K": K, "ranks": world, "rows_per_rank": rows, "oracle_rel_l2": err}
     # the gather cannot be captured on every NCCL configuration; fall back to stream launches
     try:
         med, mn = _time_graph(step, n_launch, stream)
@@ -133,7 +148,7 @@ def lm_head_case(rank, world, stream, peak_gbs, n_launch=16):
 def _fused_head(fmt, rows, K, row0, N, rank, world, Ws, x, stream, n_launch, ref_full):
     """The one-kernel form: the shard GEMV stores its rows into every rank's result vector over
     NVLink and signals arrival itself (brotensor_b200::ShardedHead); no collective call."""
-    from . import hostapi
+    from brotensor_b200 import hostapi
     try:
         hostapi.init()
         dev = torch.cuda.current_device()
@@ -176,7 +191,7 @@ def _fused_head(fmt, rows, K, row0, N, rank, world, Ws, x, stream, n_launch, ref
 
 def dequant_case(fmt, N, K, stream, peak_gbs, R=6, n_launch=12):
     """Decode to FP16 (the reference's dequant_*_to_fp16): bytes = packed read + FP16 written."""
-    from . import _capi
+    from brotensor_b200 import _capi
     W = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=2)).cuda()
     outs = [torch.empty((N, K), dtype=torch.float16, device="cuda") for _ in range(R)]  # R x 32 MiB > L2
 
@@ -266,7 +281,7 @@ def grouped_layer_set(stream, peak_gbs, R=8, n_steps=24):
 def repack_case(stream, peak_gbs, N=4096, K=14336, R=12):
     """Q6_K down_proj in the GGUF layout against the device-side regrouped one (b200q_repack):
     the repack pass itself, the decode GEMV and the decode to FP16 on both layouts."""
-    from . import _capi
+    from brotensor_b200 import _capi
     fmt, pf = synth.Q6_K, synth.Q6_K_R8
     base = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=9)).cuda()
     raw = [base] + [torch.roll(base, 1680 * 97 * (i + 1)).contiguous() for i in range(R - 1)]

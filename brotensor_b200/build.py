@@ -90,25 +90,9 @@ def build_host(force: bool = False) -> str | None:
     return lib
 
 
-def build_host_tests(force: bool = False) -> str | None:
-    """The C++ test executable of the host layer (links the CPU oracle as its checker)."""
-    src = os.path.join(ROOT, "tests", "cpp", "host_tests.cpp")
-    if not os.path.exists(src):
-        return None
-    subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle"), os.path.join(ROOT, "oracle", "liboracle.so")], check=True)
-    exe = os.path.join(LIBDIR, "host_tests")
-    deps = [src, os.path.join(LIBDIR, "libbrotensor_b200.so"), os.path.join(ROOT, "oracle", "liboracle.so")]
-    if force or _newer(deps, exe):
-        _run(["g++", "-std=c++20", "-O1", "-o", exe, src, "-I" + os.path.join(ROOT, "include"), "-I/usr/local/cuda/include",
-              "-L" + LIBDIR, "-lbrotensor_b200", "-lb200q", "-L" + os.path.join(ROOT, "oracle"), "-loracle",
-              "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../oracle", "-lpthread"])
-    return exe
-
-
 def build_all(force: bool = False, verbose: bool = False) -> None:
     build_kernels(force, verbose)
     build_host(force)
-    build_host_tests(force)
 
 
 if __name__ == "__main__":

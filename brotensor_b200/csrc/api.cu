@@ -31,6 +31,7 @@ void dp_set_groups(int v);
 void dp_set_tile_pairs(int v);
 void dp_set_split_full(int v);
 void dp_set_wait_limit_us(int v);
+void dp_set_lean(int v);
 int dp_get_wait_limit_us();
 int dp_get_tile_pairs();
 int dp_get_groups();
@@ -431,6 +432,7 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "gemv_split_full")) dp_set_split_full(value);
     else if (!strcmp(key, "gemm_pair")) gemm_set_pair(value);
     else if (!strcmp(key, "wait_limit_us")) dp_set_wait_limit_us(value);
+    else if (!strcmp(key, "gemv_lean")) dp_set_lean(value);
     else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
     return B200Q_OK;
 }

@@ -43,7 +43,6 @@ namespace b200q {
     do {                     \
     } while (0)
 #endif
-
 __device__ __forceinline__ int dp2a_lo_su(uint32_t x, uint32_t b, int c) {  // signed x pairs, unsigned bytes
     int d;
     asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(b), "r"(c));
@@ -152,13 +151,13 @@ __device__ __forceinline__ void x_store_seg(
 // Stages the activations as int16 with one power-of-two scale per 128-element group. A thread's
 // global loads go out four segments at a time before any of them is converted, so a long row
 // (K = 14336: 3.5 segments per thread) costs one load latency instead of one per segment.
-template <int FMT>
+template <int FMT, bool kLean = false>
 __device__ __forceinline__ void stage_x16(const StreamParams& p, uint32_t sbase, int tid, int nthreads) {
     const int total = (p.K >> 3) * p.M;  // K % 256 == 0, so a multiple of 32: whole warps are in or out
-    if (total <= nthreads) {  // at most one segment per thread (K = 4096, one activation row)
+    if (kLean || total <= nthreads) {  // at most one segment per thread (K = 4096, one activation row)
         if (tid < total) {
             float v[8];
-            x_load_seg(p.X, p.x_dtype, p.K, tid, v);
+            x_load_seg(p.X, kLean ? B200Q_DT_F32 : p.x_dtype, p.K, tid, v);
             x_store_seg<FMT>(p, sbase, tid, make_float4(v[0], v[1], v[2], v[3]), make_float4(v[4], v[5], v[6], v[7]));
         }
         return;
@@ -663,6 +662,10 @@ struct TileRef {
 };
 // Bits of the kernel's EXT template argument (see gemv_dp_kernel).
 constexpr int kExtSeg = 1, kExtShard = 2, kExtNorm = 4, kExtSwiglu = 8;
+// Not a form but a promise about the launch that lets the compiler drop code: FP32 activations and
+// results, no bias, one slice per tile with one barrier per consumer warp, at most one staging
+// segment per thread. The commonest decode call (hidden size 4096, one token) qualifies.
+constexpr int kExtLean = 32;
 
 template <int EXT>
 __device__ __forceinline__ TileRef tile_ref(const StreamParams& p, int vrow) {
@@ -687,7 +690,8 @@ template <int FMT, int MT, int NG, int RP, int EXT = 0>
 __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_kernel(const __grid_constant__ StreamParams p) {
     constexpr int TR = kTileRows * RP;
     // Q4_K and Q8_0 always run with one full barrier per consumer warp; only Q6_K chooses at run time.
-    constexpr bool kSplitAlways = FMT != kQ6_K && FMT != kQ6_KP;
+    constexpr bool kLean = (EXT & kExtLean) != 0;
+    constexpr bool kSplitAlways = (FMT != kQ6_K && FMT != kQ6_KP) || kLean;
     const bool split_full = kSplitAlways || p.split_full != 0;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;  // shared-space address
@@ -745,7 +749,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
             const TileRef tr = tile_ref<EXT>(p, row_begin + tile * TR);
             const int row0 = tr.row0;
             const int nrows = min(min(TR, row_end - (row_begin + tile * TR)), tr.N - row0);
-            for (int slice = 0; slice < p.n_slices; ++slice) {
+            for (int slice = 0; slice < (kLean ? 1 : p.n_slices); ++slice) {
                 if (!wait_or_abort(smem_u32(&bar_empty[g][slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty, wait_limit)) return;
                 const int c0 = slice * p.slice_chunks;
                 const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
@@ -785,7 +789,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     const unsigned int sh_epoch = ((EXT & kExtShard) && p.sh_world > 0) ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
     const unsigned int sh_buf = (sh_epoch + 1u) & 1u;
     if ((EXT & kExtNorm) && MT == 1 && p.norm_gamma) stage_x16_norm<FMT>(p, sbase, tid, kConsumers * 32, norm_red);
-    else stage_x16<FMT>(p, sbase, tid, kConsumers * 32);
+    else stage_x16<FMT, (EXT & kExtLean) != 0>(p, sbase, tid, kConsumers * 32);
     TRACE_STAMP(tid == 0, 3);
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumers * 32) : "memory");
 
@@ -812,7 +816,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         const TileRef tr = tile_ref<EXT>(p, row_begin + tile * TR);
         const int row0 = tr.row0;
         const int nrows = min(min(TR, row_end - (row_begin + tile * TR)), tr.N - row0);
-        for (int slice = 0; slice < p.n_slices; ++slice) {
+        for (int slice = 0; slice < (kLean ? 1 : p.n_slices); ++slice) {
             if (live) {
                 // keep the decision warp-uniform
                 const bool ok = wait_or_abort(smem_u32(&bar_full[g][slot][split_full ? wl : 0]), phase, &abort_flag, p.status, kDevTimeoutFull, wait_limit);
@@ -890,13 +894,13 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                     const int nr = min(min(TR, row_end - vr), t2.N - t2.row0), rr = 2 * wl + (o & 1);
                     if (rr < nr) {
                         const int n = t2.row0 + rr;
-                        if (t2.bias) {
+                        if (!kLean && t2.bias) {
                             if (p.x_dtype == B200Q_DT_F32) s += static_cast<const float*>(t2.bias)[n];
                             else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(t2.bias)[n]);
                             else s += __bfloat162float(static_cast<const __nv_bfloat16*>(t2.bias)[n]);
                         }
                         if ((EXT & kExtShard) && p.sh_world > 0) p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
-                        else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(t2.Y)[n] = s;
+                        else if (kLean || p.y_dtype == B200Q_DT_F32) static_cast<float*>(t2.Y)[n] = s;
                         else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(t2.Y)[n] = __float2half_rn(s);
                         else static_cast<__nv_bfloat16*>(t2.Y)[n] = __float2bfloat16_rn(s);
                     }
@@ -970,6 +974,9 @@ void dp_set_split_full(int v) { g_opt_split_full = v < 0 ? -1 : (v ? 1 : 0); }
 void dp_set_groups(int v) { g_opt_groups = v < 1 ? 1 : (v > 2 ? 2 : v); }
 int dp_get_groups() { return g_opt_groups; }
 // Bound of the kernels' mbarrier and peer-arrival waits in microseconds; 0: one second.
+// 1: launches that qualify take the lean instantiation (kExtLean)
+static int g_opt_lean = 1;
+void dp_set_lean(int v) { g_opt_lean = v ? 1 : 0; }
 static int g_opt_wait_limit_us = 0;
 void dp_set_wait_limit_us(int v) { g_opt_wait_limit_us = v < 0 ? 0 : v; }
 int dp_get_wait_limit_us() { return g_opt_wait_limit_us; }
@@ -1111,6 +1118,9 @@ static int launch_dp_g(const StreamParams& p, int ng, int rp, int grid, size_t s
         // grouped, sharded and fused forms: one activation row, 16-row tiles
         const int ext = (p.n_seg > 1 ? kExtSeg : 0) | (p.sh_world > 0 ? kExtShard : 0) | (p.norm_gamma ? (kExtNorm | kExtSeg) : 0) |
                         (p.W_up ? kExtSwiglu : 0);
+        if (ext == 0 && rp == 1 && g_opt_lean && p.x_dtype == B200Q_DT_F32 && p.y_dtype == B200Q_DT_F32 && !p.bias && p.n_slices == 1 &&
+            p.split_full && (p.K >> 3) <= kConsumerWarps * ng * 32)
+            return ng == 2 ? launch_dp_k<FMT, 1, 2, 1, kExtLean>(p, grid, smem, st) : launch_dp_k<FMT, 1, 1, 1, kExtLean>(p, grid, smem, st);
         switch (ext) {
             case 0: break;
             case kExtSeg:

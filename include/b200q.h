@@ -150,7 +150,13 @@ int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void*
  *   state         this rank's own two uint32 (CTA counter, call counter), zero-
  *                 initialised; its second word is the call count n.
  * All ranks must make the same sequence of calls. A rank that never arrives
- * makes the others report B200Q_ERR_TIMEOUT through b200q_device_status().
+ * makes the others report B200Q_ERR_TIMEOUT through b200q_device_status(): the
+ * kernel gives up after the wait limit (one second, or the "wait_limit_us"
+ * option), records status 105 and returns; nothing traps or hangs. After such
+ * a timeout this rank's call counter has advanced without its peers', so the
+ * exchange memory of ALL ranks (peer_out, peer_flags, state) must be zeroed or
+ * created anew before the head is used again; plain b200q_gemv calls on the
+ * device are unaffected.
  * brotensor has no sharded form; the closest is its P2P bring-up
  * (src/cuda/register.cu:90-103).
  */
@@ -230,6 +236,9 @@ int b200q_device_status(int* status_out);
  *                 one pipeline with 32-row tiles; "gemv_split_full" (Q6_K only) -1 = automatic, 0 = one full
  *                 barrier per stage, 1 = one per consumer warp and stage
  *   "gemm_pair"   0 = one-CTA tcgen05 kernel, otherwise the CTA-pair kernel (default)
+ *   "gemv_lean"   0 = never take the trimmed instantiation of the integer-dot kernel (FP32 in and out, no bias)
+ *   "wait_limit_us" bound of the decode kernels' device-side waits (stage barriers, peer arrival) in
+ *                 microseconds; 0 = one second. Tests shorten it to see a wait run out.
  * Returns B200Q_ERR_BAD_ARG for an unknown key.
  */
 int b200q_set_option(const char* key, int value);

@@ -46,6 +46,36 @@ def test_single_rank_head_matches_gemv_and_oracle(fmt, N, K, cpu_oracle):
 
 
 @pytest.mark.gpu
+def test_lm_head_full_size_against_the_oracle(cpu_oracle):
+    """The LM-head configuration at its full size: Q6_K 128256 x 4096, one activation row. The plain
+    GEMV and the single-rank sharded head against the CPU oracle's FP32 result, bound rel-L2 2e-3
+    (the reference checks its Q6_K GEMV the same way on small shapes, tests/test_q6k_parity.cpp:139-151)."""
+    import torch
+    from brotensor_b200 import hostapi, ops
+    import oracle
+    fmt, N, K = synth.Q6_K, 128256, 4096
+    Wh = synth.make_blocks(fmt, N, K, seed=4)
+    xh = synth.make_activations(1, K, seed=4)
+    want = cpu_oracle.matmul(fmt, Wh, xh, threads=os.cpu_count() or 1).reshape(-1)
+    Wd = torch.from_numpy(Wh).cuda()
+    x = torch.from_numpy(xh).cuda()
+    got = ops.gemv(fmt, Wd, x, N).cpu().numpy().reshape(-1)
+    assert got.shape == (N,)
+    err = oracle.rel_l2(got, want)
+    assert err < 2e-3, f"gemv: rel-L2 {err}"
+    hostapi.init()
+    w = hostapi.Weight.view(fmt, Wd.data_ptr(), N, K, 0)
+    head = hostapi.ShardedHead(w, 0, N, 0, 1)
+    torch.cuda.synchronize()
+    head.run(x.data_ptr(), K, 0)
+    logits = head.logits()
+    assert np.array_equal(logits, got)  # the same kernel arithmetic
+    assert oracle.rel_l2(logits, want) < 2e-3
+    assert ops.device_status() == 0
+    head.close()
+
+
+@pytest.mark.gpu
 def test_head_argument_checks():
     from brotensor_b200 import hostapi
     hostapi.init()

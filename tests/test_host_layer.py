@@ -18,26 +18,28 @@ LIB = os.path.join(ROOT, "brotensor_b200", "lib")
 
 @pytest.fixture(scope="module")
 def built():
-    from brotensor_b200 import build
-    build.build_all()
-    return LIB
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("build_host_tests", os.path.join(ROOT, "tests", "cpp", "build_host_tests.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.build()
 
 
-def run_host_tests(mode):
-    r = subprocess.run([os.path.join(LIB, "host_tests"), mode], capture_output=True, text=True, timeout=600)
+def run_host_tests(exe, mode):
+    r = subprocess.run([exe, mode], capture_output=True, text=True, timeout=600)
     print(r.stdout[-3000:], r.stderr[-2000:])
     assert r.returncode == 0, r.stdout[-2000:]
     return r.stdout
 
 
 def test_host_layer_cpu_cases(built):
-    out = run_host_tests("cpu")
+    out = run_host_tests(built, "cpu")
     assert "OK (0 failures)" in out
 
 
 @pytest.mark.gpu
 def test_host_layer_gpu_cases(built):
-    out = run_host_tests("gpu")
+    out = run_host_tests(built, "gpu")
     assert "OK (0 failures)" in out and "skipping" not in out
 
 
