@@ -15,6 +15,7 @@ LIB_PATH = os.environ.get("B200Q_LIB") or os.path.join(PKG, "lib", "libb200q.so"
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_TIMEOUT, ERR_WORKSPACE = 1, 2, 3, 4, 5
 Q8_0, Q4_K, Q6_K = 14, 22, 24
+Q4_0, Q5_K = 10, 23  # carried by brotensor's loader without ops; decode, GEMV (plain-load kernel) and gather here
 Q6_K_R8 = 124  # Q6_K regrouped by field in runs of eight blocks (b200q_repack)
 F32, F16, BF16 = 0, 1, 4
 
@@ -31,6 +32,7 @@ SYMBOLS = [
     ("b200q_repack", _i, [_i, _vp, _vp, _i64, _i, _vp]),
     ("b200q_unpack", _i, [_i, _vp, _vp, _i64, _i, _vp]),
     ("b200q_dequant", _i, [_i, _vp, _vp, _i, _i64, _i, _vp]),
+    ("b200q_embedding_gather", _i, [_i, _vp, _vp, _i, _i64, _i, _vp, _i, _vp]),
     ("b200q_gemv", _i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     ("b200q_gemv_multi_rmsnorm", _i, [_i, _i, C.POINTER(_vp), C.POINTER(_i), C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _vp, C.c_float, _i, _i, _vp]),
     ("b200q_gemv_swiglu", _i, [_i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),

@@ -12,6 +12,7 @@
 namespace b200q {
 
 int launch_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows, int K, cudaStream_t st);
+int launch_gather(int fmt, const void* W, const int32_t* idx, void* out, int out_dtype, int B, int64_t rows, int K, cudaStream_t st);
 int launch_repack(int fmt, const void* src, void* dst, int64_t rows, int K, bool to_runs, cudaStream_t st);
 int launch_gemv_simple(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype,
                        int M, int N, int K, cudaStream_t st);
@@ -104,6 +105,11 @@ static int g_opt_gemm_path = 0;
 static bool dt_ok(int dt) { return dt == B200Q_DT_F32 || dt == B200Q_DT_F16 || dt == B200Q_DT_BF16; }
 static int dt_size(int dt) { return dt == B200Q_DT_F32 ? 4 : 2; }
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+// Alignment a weight pointer needs for its block header loads.
+static size_t w_align(int fmt) { return fmt == kQ6_KP ? 16 : (fmt == kQ4_K || fmt == kQ5_K) ? 4 : 2; }
+// Formats the streaming decode kernels, the tensor-core GEMM and the fused / sharded forms take; the
+// others (Q4_0, Q5_K) run through the plain-load GEMV.
+static bool streaming_fmt(int fmt) { return fmt == kQ4_K || fmt == kQ6_K || fmt == kQ6_KP || fmt == kQ8_0; }
 
 static int check_linear_args(const char* op, int fmt, const void* W, const void* X, int x_dtype, const void* Y,
                              int y_dtype, int M, int N, int K) {
@@ -115,7 +121,7 @@ static int check_linear_args(const char* op, int fmt, const void* W, const void*
     if (fmt == kQ6_KP && K % kQ6RunElems) return fail(B200Q_ERR_BAD_ARG, "%s: K (%d) must be a multiple of %d for repacked Q6_K", op, K, kQ6RunElems);
     if (M == 0 || N == 0) return B200Q_OK;
     if (!W || !X || !Y) return fail(B200Q_ERR_BAD_ARG, "%s: null pointer", op);
-    if (!aligned(W, fmt == kQ6_KP ? 16 : fmt == kQ4_K ? 4 : 2)) return fail(B200Q_ERR_BAD_ARG, "%s: W is not aligned to its block header", op);
+    if (!aligned(W, w_align(fmt))) return fail(B200Q_ERR_BAD_ARG, "%s: W is not aligned to its block header", op);
     if (!aligned(X, 16)) return fail(B200Q_ERR_BAD_ARG, "%s: X must be 16-byte aligned", op);
     if (!aligned(Y, (size_t)dt_size(y_dtype))) return fail(B200Q_ERR_BAD_ARG, "%s: Y is not aligned to its element size", op);
     return B200Q_OK;
@@ -143,8 +149,12 @@ const char* b200q_status_str(int s) {
 
 const char* b200q_last_error(void) { return g_err; }
 
-int b200q_block_elems(int fmt) { return fmt == kQ8_0 ? 32 : (fmt == kQ4_K || fmt == kQ6_K || fmt == kQ6_KP) ? 256 : 0; }
-int b200q_block_bytes(int fmt) { return fmt == kQ8_0 ? 34 : fmt == kQ4_K ? 144 : (fmt == kQ6_K || fmt == kQ6_KP) ? 210 : 0; }
+int b200q_block_elems(int fmt) {
+    return (fmt == kQ8_0 || fmt == kQ4_0) ? 32 : (fmt == kQ4_K || fmt == kQ6_K || fmt == kQ6_KP || fmt == kQ5_K) ? 256 : 0;
+}
+int b200q_block_bytes(int fmt) {
+    return fmt == kQ8_0 ? 34 : fmt == kQ4_0 ? 18 : fmt == kQ4_K ? 144 : fmt == kQ5_K ? 176 : (fmt == kQ6_K || fmt == kQ6_KP) ? 210 : 0;
+}
 size_t b200q_packed_bytes(int fmt, int64_t rows, int K) {
     const int be = b200q_block_elems(fmt);
     if (!be || rows < 0 || K < 0 || K % be) return 0;
@@ -184,11 +194,28 @@ int b200q_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows
     if (fmt == kQ6_KP && K % kQ6RunElems) return fail(B200Q_ERR_BAD_ARG, "dequant: K (%d) must be a multiple of %d for repacked Q6_K", K, kQ6RunElems);
     if (rows == 0) return B200Q_OK;
     if (!W || !out) return fail(B200Q_ERR_BAD_ARG, "dequant: null pointer");
-    if (!aligned(W, fmt == kQ6_KP ? 16 : fmt == kQ4_K ? 4 : 2)) return fail(B200Q_ERR_BAD_ARG, "dequant: W is not aligned to its block header");
+    if (!aligned(W, w_align(fmt))) return fail(B200Q_ERR_BAD_ARG, "dequant: W is not aligned to its block header");
     if (!aligned(out, 16)) return fail(B200Q_ERR_BAD_ARG, "dequant: output must be 16-byte aligned");
     DevInfo* d;
     if (int rc = dev_info(&d)) return rc;
     return launch_dequant(fmt, W, out, out_dtype, rows, K, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_embedding_gather(int fmt, const void* table, const int32_t* idx, int B, int64_t rows, int K, void* out, int out_dtype,
+                           void* stream) {
+    const int be = b200q_block_elems(fmt);
+    if (!be) return fail(B200Q_ERR_BAD_ARG, "embedding_gather: unknown block format %d", fmt);
+    if (!dt_ok(out_dtype)) return fail(B200Q_ERR_BAD_ARG, "embedding_gather: unknown output dtype %d", out_dtype);
+    if (B < 0 || rows < 0 || K <= 0 || K % be || K % 8) return fail(B200Q_ERR_BAD_ARG, "embedding_gather: K (%d) must be a positive multiple of %d", K, be > 8 ? be : 8);
+    if (fmt == kQ6_KP && K % kQ6RunElems) return fail(B200Q_ERR_BAD_ARG, "embedding_gather: K (%d) must be a multiple of %d for repacked Q6_K", K, kQ6RunElems);
+    if (B == 0) return B200Q_OK;
+    if (!table || !idx || !out) return fail(B200Q_ERR_BAD_ARG, "embedding_gather: null pointer");
+    if (!aligned(table, w_align(fmt))) return fail(B200Q_ERR_BAD_ARG, "embedding_gather: table is not aligned to its block header");
+    if (!aligned(idx, 4)) return fail(B200Q_ERR_BAD_ARG, "embedding_gather: idx must be 4-byte aligned");
+    if (!aligned(out, 16)) return fail(B200Q_ERR_BAD_ARG, "embedding_gather: output must be 16-byte aligned");
+    DevInfo* d;
+    if (int rc = dev_info(&d)) return rc;
+    return launch_gather(fmt, table, idx, out, out_dtype, B, rows, K, static_cast<cudaStream_t>(stream));
 }
 
 // The streaming kernel for a decode GEMV of M <= 8 rows, by measurement on B200 (14336 x 4096 and
@@ -224,6 +251,7 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
     DevInfo* d;
     if (int rc = dev_info(&d)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!streaming_fmt(fmt)) return launch_gemv_simple(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
     // 0 = automatic, 1 = plain-load kernel, 2 = warp-MMA streaming kernel, 3 = integer-dot streaming kernel
     if (g_opt_gemv_path == 0) {
         bool taken = false;
@@ -263,6 +291,7 @@ int b200q_gemv(int fmt, const void* W, const void* X, int x_dtype, const void* b
 
 int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void* x, int x_dtype, void* y, int y_dtype,
                       int N, int K, void* stream) {
+    if (b200q_block_elems(fmt) && !streaming_fmt(fmt)) return fail(B200Q_ERR_UNSUPPORTED, "gemv_swiglu: block format %d has no fused form", fmt);
     if (int rc = check_linear_args("gemv_swiglu", fmt, W_gate, x, x_dtype, y, y_dtype, 1, N, K)) return rc;
     if (int rc = check_linear_args("gemv_swiglu", fmt, W_up, x, x_dtype, y, y_dtype, 1, N, K)) return rc;
     if (N == 0) return B200Q_OK;
@@ -288,7 +317,7 @@ int b200q_gemv_multi(int fmt, int n, const void* const* W, const int* N, void* c
     DevInfo* d;
     if (int rc = dev_info(&d)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (n > 1 && (g_opt_gemv_path == 0 || g_opt_gemv_path == 3)) {
+    if (n > 1 && streaming_fmt(fmt) && (g_opt_gemv_path == 0 || g_opt_gemv_path == 3)) {
         bool taken = false;
         if (int rc = launch_gemv_dp_multi(fmt, n, W, N, Y, bias, x, x_dtype, y_dtype, K, d->sms, d->smem_optin - 1024, d->status, st, &taken, nullptr, 0.f))
             return rc;
@@ -304,6 +333,7 @@ int b200q_gemv_multi_rmsnorm(int fmt, int n, const void* const* W, const int* N,
                              const void* x, int x_dtype, const void* gamma, float eps, int y_dtype, int K, void* stream) {
     if (n < 1 || n > kMaxSegments) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: %d matrices (1..%d)", n, kMaxSegments);
     if (!W || !N || !Y) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: null table");
+    if (b200q_block_elems(fmt) && !streaming_fmt(fmt)) return fail(B200Q_ERR_UNSUPPORTED, "gemv_multi_rmsnorm: block format %d has no fused form", fmt);
     if (!gamma || !aligned(gamma, 16)) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: gamma must be a 16-byte aligned vector of K elements");
     if (!(eps >= 0.f)) return fail(B200Q_ERR_BAD_ARG, "gemv_multi_rmsnorm: eps must not be negative");
     for (int s = 0; s < n; ++s) {
@@ -324,6 +354,7 @@ int b200q_gemv_multi_rmsnorm(int fmt, int n, const void* const* W, const int* N,
 int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
                      int row_offset, int total_rows, int rank, int world, void* const* peer_out,
                      void* const* peer_flags, void* state, void* stream) {
+    if (b200q_block_elems(fmt) && !streaming_fmt(fmt)) return fail(B200Q_ERR_UNSUPPORTED, "gemv_shard: block format %d has no sharded form", fmt);
     static float dummy_y;  // check_linear_args wants a non-null result pointer; the sharded form has none
     if (int rc = check_linear_args("gemv_shard", fmt, W_shard, x, x_dtype, &dummy_y, B200Q_DT_F32, 1, rows, K)) return rc;
     if (world < 1 || world > kMaxShardRanks || rank < 0 || rank >= world)

@@ -21,6 +21,8 @@ constexpr int kQ8_0 = B200Q_FMT_Q8_0;
 constexpr int kQ4_K = B200Q_FMT_Q4_K;
 constexpr int kQ6_K = B200Q_FMT_Q6_K;
 constexpr int kQ6_KP = B200Q_FMT_Q6_K_R8;  // Q6_K regrouped by field in runs of eight blocks
+constexpr int kQ4_0 = B200Q_FMT_Q4_0;
+constexpr int kQ5_K = B200Q_FMT_Q5_K;
 constexpr int kQ6RunBytes = 1680, kQ6RunElems = 2048;
 
 // Device status codes written by kernels whose bounded waits run out.
@@ -52,6 +54,16 @@ template <>
 struct Blk<kQ8_0> {
     static constexpr int elems = 32, bytes = 34, align = 2;
     static constexpr int chunk_blocks = 8;
+};
+template <>
+struct Blk<kQ4_0> {  // ggml block_q4_0
+    static constexpr int elems = 32, bytes = 18, align = 2;
+    static constexpr int chunk_blocks = 8;
+};
+template <>
+struct Blk<kQ5_K> {  // ggml block_q5_K
+    static constexpr int elems = 256, bytes = 176, align = 4;
+    static constexpr int chunk_blocks = 1;
 };
 
 // ---- host-side error plumbing ------------------------------------------------
@@ -191,6 +203,62 @@ __device__ __forceinline__ void decode8<kQ8_0>(const uint8_t* __restrict__ row, 
     for (int k = 0; k < 4; ++k) {
         w[k] = d * (float)(int)(signed char)((q0 >> (8 * k)) & 0xFFu);
         w[4 + k] = d * (float)(int)(signed char)((q1 >> (8 * k)) & 0xFFu);
+    }
+}
+
+// Q4_0 (ggml block_q4_0, dequantize_row_q4_0): element j of a block is the low nibble of qs[j] for
+// j < 16 and the high nibble of qs[j - 16] otherwise, minus 8, times d. d * (q - 8): 11 + 4 bits, exact.
+template <>
+__device__ __forceinline__ void decode8<kQ4_0>(const uint8_t* __restrict__ row, int u, float w[8]) {
+    const uint8_t* blk = row + (size_t)(u >> 2) * 18;
+    const float d = h2f(ld_nc_u16(blk));
+    const int part = u & 3;  // elements 8 * part .. 8 * part + 7
+    const uint8_t* q = blk + 2 + (part & 1) * 8;
+    uint32_t q0 = ld_nc_u32_a2(q), q1 = ld_nc_u32_a2(q + 4);
+    if (part >= 2) {
+        q0 >>= 4;
+        q1 >>= 4;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        w[k] = d * (float)((int)((q0 >> (8 * k)) & 0xFu) - 8);
+        w[4 + k] = d * (float)((int)((q1 >> (8 * k)) & 0xFu) - 8);
+    }
+}
+
+// Q5_K (ggml block_q5_K, dequantize_row_q5_K): d @0, dmin @2, scales[12] @4 packed as in Q4_K, qh[32] @16,
+// qs[128] @48. Sub-block is = 0..7 of 32 elements: byte qs[(is >> 1) * 32 + l], low nibble for even is,
+// high nibble for odd; the fifth bit is bit `is` of qh[l]. w = d * sc * q - dmin * m with q in 0..31:
+// 11 + 6 + 5 bits and 11 + 6 bits, both exact in FP32, one rounding in the subtraction.
+template <>
+__device__ __forceinline__ void decode8<kQ5_K>(const uint8_t* __restrict__ row, int u, float w[8]) {
+    const uint8_t* blk = row + (size_t)(u >> 5) * 176;
+    const int i = u & 31, is = i >> 2, l0 = (i & 3) * 8;
+    const uint32_t dd = ld_nc_u32(blk);
+    const uint32_t s0 = ld_nc_u32(blk + 4), s1 = ld_nc_u32(blk + 8), s2 = ld_nc_u32(blk + 12);
+    uint32_t sc, m;
+    if (is < 4) {
+        sc = (s0 >> (8 * is)) & 63u;
+        m = (s1 >> (8 * is)) & 63u;
+    } else {
+        const int j = is - 4;
+        sc = ((s2 >> (8 * j)) & 0xFu) | (((s0 >> (8 * j + 6)) & 3u) << 4);
+        m = ((s2 >> (8 * j + 4)) & 0xFu) | (((s1 >> (8 * j + 6)) & 3u) << 4);
+    }
+    const float ds = h2f(dd & 0xFFFFu) * (float)sc;
+    const float dm = h2f(dd >> 16) * (float)m;
+    const uint8_t* q = blk + 48 + (is >> 1) * 32 + l0;
+    const uint8_t* h = blk + 16 + l0;
+    uint32_t q0 = ld_nc_u32(q), q1 = ld_nc_u32(q + 4);
+    const uint32_t h0 = ld_nc_u32(h) >> is, h1 = ld_nc_u32(h + 4) >> is;
+    if (is & 1) {
+        q0 >>= 4;
+        q1 >>= 4;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        w[k] = ds * (float)(((q0 >> (8 * k)) & 0xFu) | (((h0 >> (8 * k)) & 1u) << 4)) - dm;
+        w[4 + k] = ds * (float)(((q1 >> (8 * k)) & 0xFu) | (((h1 >> (8 * k)) & 1u) << 4)) - dm;
     }
 }
 

@@ -195,8 +195,75 @@ int launch_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t row
         case kQ6_K: return launch_dequant_fmt<kQ6_K>(W, out, out_dtype, rows, K, st);
         case kQ6_KP: return launch_dequant_fmt<kQ6_KP>(W, out, out_dtype, rows, K, st);
         case kQ8_0: return launch_dequant_fmt<kQ8_0>(W, out, out_dtype, rows, K, st);
+        case kQ4_0: return launch_dequant_fmt<kQ4_0>(W, out, out_dtype, rows, K, st);
+        case kQ5_K: return launch_dequant_fmt<kQ5_K>(W, out, out_dtype, rows, K, st);
     }
     return fail(B200Q_ERR_BAD_ARG, "dequant: unknown block format %d", fmt);
+}
+
+// Row gather with decode (a quantized embedding table): the dequant kernel with the row taken from
+// an index vector. One thread decodes eight consecutive elements of one gathered row; an index
+// outside the table writes zeros and reads nothing.
+template <int FMT, typename OT>
+__global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__ W, const int32_t* __restrict__ idx, OT* __restrict__ out,
+                                                     long long total_units, int units_per_row, int row_bytes, long long rows) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long id = (long long)blockIdx.x * blockDim.x + threadIdx.x; id < total_units; id += stride) {
+        const long long b = id / units_per_row;
+        const int u = (int)(id - b * units_per_row);
+        const long long r = (long long)__ldg(idx + b);
+        float w[8];
+        if (r >= 0 && r < rows) {
+            decode8<FMT>(W + (size_t)r * row_bytes, u, w);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) w[k] = 0.f;
+        }
+        OT* o = out + (size_t)id * 8;
+        if constexpr (sizeof(OT) == 2) {
+            union {
+                OT h[8];
+                uint4 v;
+            } pk;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) pk.h[k] = from_f32<OT>(w[k]);
+            *reinterpret_cast<uint4*>(o) = pk.v;
+        } else {
+            reinterpret_cast<float4*>(o)[0] = make_float4(w[0], w[1], w[2], w[3]);
+            reinterpret_cast<float4*>(o)[1] = make_float4(w[4], w[5], w[6], w[7]);
+        }
+    }
+}
+
+template <int FMT>
+static int launch_gather_fmt(const void* W, const int32_t* idx, void* out, int out_dtype, int B, int64_t rows, int K, cudaStream_t st) {
+    const int upr = K / 8;
+    const long long total = (long long)B * upr;
+    const int row_bytes = (K / Blk<FMT>::elems) * Blk<FMT>::bytes;
+    long long blocks = (total + 255) / 256;
+    const long long cap = 148LL * 8 * 16;
+    if (blocks > cap) blocks = cap;
+    const uint8_t* w = static_cast<const uint8_t*>(W);
+    switch (out_dtype) {
+        case B200Q_DT_F16: gather_kernel<FMT, __half><<<(unsigned)blocks, 256, 0, st>>>(w, idx, (__half*)out, total, upr, row_bytes, rows); break;
+        case B200Q_DT_BF16: gather_kernel<FMT, __nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(w, idx, (__nv_bfloat16*)out, total, upr, row_bytes, rows); break;
+        case B200Q_DT_F32: gather_kernel<FMT, float><<<(unsigned)blocks, 256, 0, st>>>(w, idx, (float*)out, total, upr, row_bytes, rows); break;
+        default: return fail(B200Q_ERR_BAD_ARG, "embedding_gather: unknown output dtype %d", out_dtype);
+    }
+    B200Q_CUDA_TRY(cudaGetLastError());
+    return B200Q_OK;
+}
+
+int launch_gather(int fmt, const void* W, const int32_t* idx, void* out, int out_dtype, int B, int64_t rows, int K, cudaStream_t st) {
+    switch (fmt) {
+        case kQ4_K: return launch_gather_fmt<kQ4_K>(W, idx, out, out_dtype, B, rows, K, st);
+        case kQ6_K: return launch_gather_fmt<kQ6_K>(W, idx, out, out_dtype, B, rows, K, st);
+        case kQ6_KP: return launch_gather_fmt<kQ6_KP>(W, idx, out, out_dtype, B, rows, K, st);
+        case kQ8_0: return launch_gather_fmt<kQ8_0>(W, idx, out, out_dtype, B, rows, K, st);
+        case kQ4_0: return launch_gather_fmt<kQ4_0>(W, idx, out, out_dtype, B, rows, K, st);
+        case kQ5_K: return launch_gather_fmt<kQ5_K>(W, idx, out, out_dtype, B, rows, K, st);
+    }
+    return fail(B200Q_ERR_BAD_ARG, "embedding_gather: unknown block format %d", fmt);
 }
 
 }  // namespace b200q

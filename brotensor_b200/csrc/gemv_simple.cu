@@ -115,6 +115,8 @@ int launch_gemv_simple(int fmt, const void* W, const void* X, int x_dtype, const
         case kQ6_K: return launch_simple_f<kQ6_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
         case kQ6_KP: return launch_simple_f<kQ6_KP>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
         case kQ8_0: return launch_simple_f<kQ8_0>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
+        case kQ4_0: return launch_simple_f<kQ4_0>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
+        case kQ5_K: return launch_simple_f<kQ5_K>(W, X, x_dtype, bias, Y, y_dtype, M, N, K, st);
     }
     return fail(B200Q_ERR_BAD_ARG, "gemv: unknown block format %d", fmt);
 }

@@ -5,6 +5,7 @@
 // output, and calls the C-ABI of include/b200q.h on the thread's current stream.
 #include <cuda_runtime_api.h>
 
+#include <cstdint>
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -306,6 +307,29 @@ void batched_impl(int fmt, Dtype wdt, const char* dname, int block, const char* 
 B200_FMT_OPS(q4k, B200Q_FMT_Q4_K, Dtype::Q4_K, "Q4_K", 256)
 B200_FMT_OPS(q6k, B200Q_FMT_Q6_K, Dtype::Q6_K, "Q6_K", 256)
 B200_FMT_OPS(q8_0, B200Q_FMT_Q8_0, Dtype::Q8_0, "Q8_0", 32)
+B200_FMT_OPS(q4_0, B200Q_FMT_Q4_0, Dtype::Q4_0, "Q4_0", 32)
+B200_FMT_OPS(q5k, B200Q_FMT_Q5_K, Dtype::Q5_K, "Q5_K", 256)
+
+void embedding_impl(const Tensor& table, const std::int32_t* d_idx, int B, Tensor& out) {
+    const char* op = "embedding_lookup_forward";
+    int fmt = 0;
+    switch (table.dtype) {
+        case Dtype::Q4_K: fmt = B200Q_FMT_Q4_K; break;
+        case Dtype::Q6_K: fmt = B200Q_FMT_Q6_K; break;
+        case Dtype::Q8_0: fmt = B200Q_FMT_Q8_0; break;
+        case Dtype::Q4_0: fmt = B200Q_FMT_Q4_0; break;
+        case Dtype::Q5_K: fmt = B200Q_FMT_Q5_K; break;
+        default: op_fail(op, "table dtype must be Q4_K, Q6_K, Q8_0, Q4_0 or Q5_K (this op is the quantized-table form)");
+    }
+    if (table.rows <= 0 || table.cols <= 0) op_fail(op, "table has non-positive shape");
+    if (B < 0) op_fail(op, "negative batch");
+    if (B > 0 && !d_idx) op_fail(op, "null index pointer");
+    const bool keep = out.rows == B && out.cols == table.cols && act_dtype(out.dtype) && out.data;
+    if (!keep) out.resize(B, table.cols, Dtype::FP16);
+    if (B == 0) return;
+    check_status(b200q_embedding_gather(layout_fmt(fmt, table), table.data, d_idx, B, table.rows, table.cols, out.data,
+                                        static_cast<int>(out.dtype), cuda_current_stream(table.device.index)), op);
+}
 
 }  // namespace
 
@@ -321,6 +345,13 @@ void fill_cuda_tables(OpsVTable& ops, AllocVTable& alloc) {
     ops.dequant_q8_0_to_fp16 = dequant_q8_0;
     ops.linear_forward_q8_0_fp16 = gemv_q8_0;
     ops.linear_forward_batched_q8_0_fp16 = batched_q8_0;
+    ops.dequant_q4_0_to_fp16 = dequant_q4_0;
+    ops.linear_forward_q4_0_fp16 = gemv_q4_0;
+    ops.linear_forward_batched_q4_0_fp16 = batched_q4_0;
+    ops.dequant_q5k_to_fp16 = dequant_q5k;
+    ops.linear_forward_q5k_fp16 = gemv_q5k;
+    ops.linear_forward_batched_q5k_fp16 = batched_q5k;
+    ops.embedding_lookup_forward = embedding_impl;
     ops.dequant_q6k_to_fp16 = dequant_q6k;
     ops.linear_forward_q6k_fp16 = gemv_q6k;
     ops.linear_forward_batched_q6k_fp16 = batched_q6k;

@@ -40,6 +40,20 @@ B200_DEQUANT_OP(dequant_q6k_to_fp16)
 B200_LINEAR_OP(linear_forward_q6k_fp16)
 B200_LINEAR_OP(linear_forward_batched_q6k_fp16)
 
+B200_DEQUANT_OP(dequant_q4_0_to_fp16)
+B200_LINEAR_OP(linear_forward_q4_0_fp16)
+B200_LINEAR_OP(linear_forward_batched_q4_0_fp16)
+B200_DEQUANT_OP(dequant_q5k_to_fp16)
+B200_LINEAR_OP(linear_forward_q5k_fp16)
+B200_LINEAR_OP(linear_forward_batched_q5k_fp16)
+
+void embedding_lookup_forward(const Tensor& table, const std::int32_t* d_idx, int B, Tensor& out) {
+    const detail::OpsVTable& v = detail::dispatch_with_opts(table, {&out});
+    if (!v.embedding_lookup_forward) detail::throw_not_implemented("embedding_lookup_forward", table.device);
+    detail::adopt_output(out, table.device);
+    v.embedding_lookup_forward(table, d_idx, B, out);
+}
+
 void linear_forward_group_fp16(const Tensor* const* W, const Tensor* const* bias, int n, const Tensor& x, Tensor* const* y) {
     if (n <= 0 || !W || !y || !W[0] || !y[0]) throw std::runtime_error("brotensor: linear_forward_group_fp16: no matrices");
     const detail::OpsVTable& v = detail::dispatch_with_opts(*W[0], {&x, y[0]});

@@ -59,6 +59,18 @@ def dequant(fmt: int, W: torch.Tensor, N: int, K: int, out_dtype=torch.float16) 
     return out
 
 
+def embedding_gather(fmt: int, table: torch.Tensor, idx: torch.Tensor, rows: int, K: int, out_dtype=torch.float16) -> torch.Tensor:
+    """out[b] = decode(table row idx[b]); idx: int32 device tensor. Rows outside the table come back as zeros."""
+    _check_w(fmt, table, rows, K)
+    if idx.dtype != torch.int32 or not idx.is_cuda or not idx.is_contiguous():
+        raise ValueError("idx must be a contiguous CUDA int32 tensor")
+    B = idx.numel()
+    out = torch.empty((B, K), dtype=out_dtype, device=table.device)
+    with torch.cuda.device(table.device):
+        capi.check(capi.lib().b200q_embedding_gather(fmt, table.data_ptr(), idx.data_ptr(), B, rows, K, out.data_ptr(), _DT[out_dtype], _stream()))
+    return out
+
+
 def _linear(entry: str, fmt, W, X, N, bias, out, out_dtype, ws):
     if X.dim() == 1:
         X = X.unsqueeze(0)

@@ -11,10 +11,11 @@ from __future__ import annotations
 import numpy as np
 
 Q8_0, Q4_K, Q6_K = 14, 22, 24
+Q4_0, Q5_K = 10, 23  # ggml block_q4_0 / block_q5_K
 Q6_K_R8 = 124  # device-side regrouped form of Q6_K (same bytes per block; see include/b200q.h)
-BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q6_K: 256, Q6_K_R8: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210, Q6_K_R8: 210}
-FMT_NAME = {Q8_0: "q8_0", Q4_K: "q4k", Q6_K: "q6k", Q6_K_R8: "q6k_r8"}
+BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q6_K: 256, Q6_K_R8: 256, Q4_0: 32, Q5_K: 256}
+BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210, Q6_K_R8: 210, Q4_0: 18, Q5_K: 176}
+FMT_NAME = {Q8_0: "q8_0", Q4_K: "q4k", Q6_K: "q6k", Q6_K_R8: "q6k_r8", Q4_0: "q4_0", Q5_K: "q5k"}
 
 
 def packed_bytes(fmt: int, rows: int, K: int) -> int:
@@ -51,6 +52,13 @@ def make_blocks(fmt: int, rows: int, K: int, seed: int) -> np.ndarray:
     elif fmt == Q8_0:
         out[:, 0:2] = _f16_bytes(rng, nb, 0.005)
         out[:, 2:34] = rng.integers(-127, 128, size=(nb, 32), dtype=np.int8).view(np.uint8)
+    elif fmt == Q4_0:  # d = fp16(|N(0,1)|*0.005), 16 uniform bytes of 4-bit quants
+        out[:, 0:2] = _f16_bytes(rng, nb, 0.005)
+        out[:, 2:18] = rng.integers(0, 256, size=(nb, 16), dtype=np.uint8)
+    elif fmt == Q5_K:  # as Q4_K plus 32 uniform bytes of fifth bits
+        out[:, 0:2] = _f16_bytes(rng, nb, 0.002)
+        out[:, 2:4] = _f16_bytes(rng, nb, 0.002)
+        out[:, 4:176] = rng.integers(0, 256, size=(nb, 172), dtype=np.uint8)
     else:
         raise ValueError(f"unknown block format {fmt}")
     return out.reshape(-1)

@@ -41,6 +41,13 @@ extern "C" {
 #define B200Q_FMT_Q4_K 22 /* 256 elements / 144 B: fp16 d, fp16 dmin, u8 scales[12], u8 qs[128] */
 #define B200Q_FMT_Q6_K 24 /* 256 elements / 210 B: u8 ql[128], u8 qh[64], i8 scales[16], fp16 d */
 /*
+ * Two more GGUF formats that brotensor's loader carries as opaque storage with no op behind them
+ * (src/gguf.cpp:111-130); layouts as ggml defines them. Decode, dequant, decode GEMV, GEMM (as passes
+ * of the GEMV) and the row gather take them; the tensor-core prefill kernel and the sharded head do not.
+ */
+#define B200Q_FMT_Q4_0 10 /*  32 elements /  18 B: fp16 d, u8 qs[16]; w = d * (nibble - 8), element j < 16 the low nibble of qs[j], else the high nibble of qs[j - 16] */
+#define B200Q_FMT_Q5_K 23 /* 256 elements / 176 B: fp16 d, fp16 dmin, u8 scales[12] (packed as in Q4_K), u8 qh[32], u8 qs[128]; w = d * sc * (nibble + 16 * bit) - dmin * m */
+/*
  * Q6_K repacked on the device in runs of eight blocks (b200q_repack): the same 1680 bytes per run,
  * regrouped by field - ql[8][128] @0, qh[8][64] @1024, scales[8][16] @1536, fp16 d[8] @1664 - so that
  * every field starts on a 16-byte boundary (raw Q6_K blocks are only 2-byte aligned). Content is
@@ -86,6 +93,19 @@ int b200q_unpack(int fmt, const void* src, void* dst, int64_t rows, int K, void*
  * q6k.cu:232-259, q8_0.cu:195-222). Rows beyond 65535 are handled.
  */
 int b200q_dequant(int fmt, const void* W, void* out, int out_dtype, int64_t rows, int K, void* stream);
+
+/*
+ * Row gather with decode, for a quantized embedding table (a GGUF token_embd stored as Q4_K / Q6_K /
+ * Q8_0 / Q5_K / Q4_0, or a tied LM head): out[b][:] = decode(table row idx[b]) for b < B, the same
+ * exact FP32 decode and single rounding as b200q_dequant of those rows. table: rows x K quantized;
+ * idx: B int32 on the device; out: B x K of out_dtype, 16-byte aligned. An index outside [0, rows)
+ * gives a row of zeros (brotensor leaves that case undefined, include/brotensor/ops/embedding.h:37-39;
+ * nothing is read out of bounds here). brotensor's embedding_lookup_forward refuses quantized tables
+ * (src/cuda/embedding.cu:150-154: "quantized tables must be dequantized first"), which costs a full
+ * FP16 copy of the table; this op reads B rows of packed bytes.
+ */
+int b200q_embedding_gather(int fmt, const void* table, const int32_t* idx, int B, int64_t rows, int K, void* out, int out_dtype,
+                           void* stream);
 
 /*
  * Decode GEMV for 1..8 activation rows:

@@ -5,6 +5,8 @@
 // Only the nine quant slots exist here.
 #pragma once
 
+#include <cstdint>
+
 #include <cstddef>
 #include <initializer_list>
 
@@ -26,6 +28,16 @@ struct OpsVTable {
     DequantFn dequant_q6k_to_fp16 = nullptr;
     LinearFn linear_forward_q6k_fp16 = nullptr;
     LinearFn linear_forward_batched_q6k_fp16 = nullptr;
+    // Extension: the two commonest GGUF formats that brotensor's loader carries without ops (src/gguf.cpp:111-130).
+    DequantFn dequant_q4_0_to_fp16 = nullptr;
+    LinearFn linear_forward_q4_0_fp16 = nullptr;
+    LinearFn linear_forward_batched_q4_0_fp16 = nullptr;
+    DequantFn dequant_q5k_to_fp16 = nullptr;
+    LinearFn linear_forward_q5k_fp16 = nullptr;
+    LinearFn linear_forward_batched_q5k_fp16 = nullptr;
+    // brotensor's embedding_lookup_forward (include/brotensor/ops/embedding.h:14-16), here for QUANTIZED tables,
+    // which brotensor refuses (src/cuda/embedding.cu:150-154).
+    void (*embedding_lookup_forward)(const Tensor& table, const std::int32_t* d_idx, int B, Tensor& out) = nullptr;
     // Extension, not in brotensor's table: several matrices against one activation vector.
     GroupFn linear_forward_group_fp16 = nullptr;
     // Extension: gate and up projection with the SwiGLU gate applied in the kernel's epilogue.

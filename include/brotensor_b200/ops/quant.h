@@ -13,6 +13,8 @@
 // Errors are std::runtime_error("brotensor: <op>: <reason>") as in the reference.
 #pragma once
 
+#include <cstdint>
+
 #include "../tensor.h"
 
 namespace brotensor_b200 {
@@ -28,6 +30,27 @@ void linear_forward_batched_q8_0_fp16(const Tensor& W_q8, const Tensor* bias, co
 void dequant_q6k_to_fp16(const Tensor& W_q6k, Tensor& W_fp16);
 void linear_forward_q6k_fp16(const Tensor& W_q6k, const Tensor* bias, const Tensor& x, Tensor& y);
 void linear_forward_batched_q6k_fp16(const Tensor& W_q6k, const Tensor* bias, const Tensor& X_BD, Tensor& Y_BD);
+
+// Extension: Q4_0 and Q5_K, which brotensor's GGUF loader hands out as opaque storage with no op behind
+// them (src/gguf.cpp:111-130). Same three ops, shapes, dtypes and errors as for the formats above; the
+// decode follows ggml's block definitions. They run on the plain-load GEMV (weights read once for up to
+// eight activation rows), not on the streaming and tensor-core kernels.
+void dequant_q4_0_to_fp16(const Tensor& W_q4_0, Tensor& W_fp16);
+void linear_forward_q4_0_fp16(const Tensor& W_q4_0, const Tensor* bias, const Tensor& x, Tensor& y);
+void linear_forward_batched_q4_0_fp16(const Tensor& W_q4_0, const Tensor* bias, const Tensor& X_BD, Tensor& Y_BD);
+void dequant_q5k_to_fp16(const Tensor& W_q5k, Tensor& W_fp16);
+void linear_forward_q5k_fp16(const Tensor& W_q5k, const Tensor* bias, const Tensor& x, Tensor& y);
+void linear_forward_batched_q5k_fp16(const Tensor& W_q5k, const Tensor* bias, const Tensor& X_BD, Tensor& Y_BD);
+
+// brotensor's embedding_lookup_forward (include/brotensor/ops/embedding.h:14-16) for a QUANTIZED table
+// (Q4_K, Q6_K, Q8_0, Q4_0, Q5_K): out (B, D) = decode of the table rows d_idx[0..B), the same values as
+// dequant_*_to_fp16 of those rows. d_idx: B int32 on the table's device. out is resized to (B, D) FP16
+// unless it is pre-sized with that shape as FP32 / FP16 / BF16. brotensor throws for quantized tables
+// ("quantized tables must be dequantized first", src/cuda/embedding.cu:150-154); a GGUF token_embd
+// stored as Q4_K / Q6_K (and a tied LM head) needs no FP16 copy this way. An index outside [0, rows)
+// yields a row of zeros (undefined in brotensor). FP32 / FP16 / BF16 tables are not this op's business
+// and are refused.
+void embedding_lookup_forward(const Tensor& table, const std::int32_t* d_idx, int B, Tensor& out);
 
 // Extension (brotensor issues one launch per projection): n <= 4 weight matrices of ONE quant
 // dtype (Q4_K, Q6_K or Q8_0) and one `in` against the same activation vector x (in, 1) in a

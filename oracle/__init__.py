@@ -17,8 +17,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 Q8_0, Q4_K, Q6_K = 14, 22, 24
-BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q6_K: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210}
+Q4_0, Q5_K = 10, 23  # decoders restated from the ggml block definitions (the reference has none)
+BLOCK_ELEMS = {Q8_0: 32, Q4_K: 256, Q6_K: 256, Q4_0: 32, Q5_K: 256}
+BLOCK_BYTES = {Q8_0: 34, Q4_K: 144, Q6_K: 210, Q4_0: 18, Q5_K: 176}
 
 _u8p = C.POINTER(C.c_uint8)
 _f32p = C.POINTER(C.c_float)

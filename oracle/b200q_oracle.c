@@ -17,6 +17,13 @@
  *                        (sequential FP32 accumulation, k ascending)
  *   fp16/bf16 <-> fp32   src/tensor.cpp:162-260 (round to nearest even)
  *
+ * Two formats have no decoder anywhere in brotensor (its loader carries them as opaque storage,
+ * src/gguf.cpp:111-130): Q4_0 and Q5_K. Their decoders below restate ggml's published block
+ * definitions (block_q4_0 / dequantize_row_q4_0, block_q5_K / dequantize_row_q5_K of ggml-quants.c;
+ * ggml is not part of the reference tree). For these two, parity is pinned to that specification
+ * and to a second, independently written numpy restatement in tests/test_formats_extra.py - not to
+ * reference code.
+ *
  * Parity is pinned: tests/test_oracle.py checks every function here against
  * golden vectors produced by the reference's own functions (compiled from the
  * reference sources into oracle/_ref) and, when that library is present,
@@ -28,8 +35,10 @@
 #include <stdlib.h>
 #include <string.h>
 
+#define FMT_Q4_0 10
 #define FMT_Q8_0 14
 #define FMT_Q4_K 22
+#define FMT_Q5_K 23
 #define FMT_Q6_K 24
 
 /* ---- scalar conversions -------------------------------------------------- */
@@ -102,8 +111,12 @@ uint16_t oracle_fp32_to_bf16(float v) {
 
 /* ---- block geometry -------------------------------------------------------- */
 
-int oracle_block_elems(int fmt) { return fmt == FMT_Q8_0 ? 32 : (fmt == FMT_Q4_K || fmt == FMT_Q6_K) ? 256 : 0; }
-int oracle_block_bytes(int fmt) { return fmt == FMT_Q8_0 ? 34 : fmt == FMT_Q4_K ? 144 : fmt == FMT_Q6_K ? 210 : 0; }
+int oracle_block_elems(int fmt) {
+    return (fmt == FMT_Q8_0 || fmt == FMT_Q4_0) ? 32 : (fmt == FMT_Q4_K || fmt == FMT_Q6_K || fmt == FMT_Q5_K) ? 256 : 0;
+}
+int oracle_block_bytes(int fmt) {
+    return fmt == FMT_Q8_0 ? 34 : fmt == FMT_Q4_0 ? 18 : fmt == FMT_Q4_K ? 144 : fmt == FMT_Q5_K ? 176 : fmt == FMT_Q6_K ? 210 : 0;
+}
 
 /* ---- Q4_K ------------------------------------------------------------------ */
 
@@ -189,11 +202,54 @@ void oracle_q8_0_dequant_block(const uint8_t* blk, float* dst) {
     for (int i = 0; i < 32; ++i) dst[i] = d * (float)qs[i];
 }
 
+/* ---- Q4_0 (ggml block_q4_0) -------------------------------------------------- */
+
+/* 18-byte block: fp16 d @0, qs[16] @2. Element j < 16 is the low nibble of qs[j], element j + 16 its
+ * high nibble; value d * (nibble - 8). */
+void oracle_q4_0_dequant_block(const uint8_t* blk, float* dst) {
+    uint16_t dh;
+    memcpy(&dh, blk, 2);
+    const float d = oracle_fp16_to_fp32(dh);
+    const uint8_t* qs = blk + 2;
+    for (int j = 0; j < 16; ++j) {
+        dst[j] = d * (float)((int)(qs[j] & 0x0F) - 8);
+        dst[j + 16] = d * (float)((int)(qs[j] >> 4) - 8);
+    }
+}
+
+/* ---- Q5_K (ggml block_q5_K) -------------------------------------------------- */
+
+/* 176-byte block: fp16 d @0, fp16 dmin @2, scales[12] @4 (the Q4_K packing), qh[32] @16, qs[128] @48.
+ * For each 64-element group j = 0..3: the low nibbles of qs[32 j .. 32 j + 31] with bit 2 j of qh[l] as
+ * fifth bit are sub-block 2 j, the high nibbles with bit 2 j + 1 sub-block 2 j + 1;
+ * value d * sc * q - dmin * m. */
+void oracle_q5k_dequant_block(const uint8_t* blk, float* dst) {
+    uint16_t dh, mh;
+    memcpy(&dh, blk, 2);
+    memcpy(&mh, blk + 2, 2);
+    const float d = oracle_fp16_to_fp32(dh);
+    const float dmin = oracle_fp16_to_fp32(mh);
+    uint8_t sc[8], m[8];
+    oracle_q4k_unpack_sc_m(blk + 4, sc, m);
+    const uint8_t* qh = blk + 16;
+    const uint8_t* ql = blk + 48;
+    for (int j = 0; j < 4; ++j) {
+        for (int l = 0; l < 32; ++l) {
+            const int lo = (ql[32 * j + l] & 0x0F) + (((qh[l] >> (2 * j)) & 1) ? 16 : 0);
+            const int hi = (ql[32 * j + l] >> 4) + (((qh[l] >> (2 * j + 1)) & 1) ? 16 : 0);
+            dst[64 * j + l] = d * (float)sc[2 * j] * (float)lo - dmin * (float)m[2 * j];
+            dst[64 * j + 32 + l] = d * (float)sc[2 * j + 1] * (float)hi - dmin * (float)m[2 * j + 1];
+        }
+    }
+}
+
 /* ---- row / matrix level ---------------------------------------------------- */
 
 static void dequant_block(int fmt, const uint8_t* blk, float* dst) {
     if (fmt == FMT_Q4_K) oracle_q4k_dequant_block(blk, dst);
     else if (fmt == FMT_Q6_K) oracle_q6k_dequant_block(blk, dst);
+    else if (fmt == FMT_Q5_K) oracle_q5k_dequant_block(blk, dst);
+    else if (fmt == FMT_Q4_0) oracle_q4_0_dequant_block(blk, dst);
     else oracle_q8_0_dequant_block(blk, dst);
 }
 

@@ -554,6 +554,93 @@ static void test_gpu_group_rmsnorm_op() {
     CHECK(threw);
 }
 
+// Q4_0 and Q5_K (formats brotensor's loader carries without ops) through the public ops, and the
+// quantized embedding lookup that brotensor refuses (tests/test_embedding_extra_parity.cpp:141-154
+// pins that refusal; here the same call returns the rows' exact decode).
+static void test_gpu_extra_formats_and_embedding() {
+    std::printf("test_gpu_extra_formats_and_embedding\n");
+    const Device dev = Device::CUDA;
+    struct Extra {
+        FmtCase c;
+    } extras[] = {
+        {{"q4_0", B200Q_FMT_Q4_0, Dtype::Q4_0, 32, 18, bt::dequant_q4_0_to_fp16, bt::linear_forward_q4_0_fp16, bt::linear_forward_batched_q4_0_fp16, nullptr}},
+        {{"q5k", B200Q_FMT_Q5_K, Dtype::Q5_K, 256, 176, bt::dequant_q5k_to_fp16, bt::linear_forward_q5k_fp16, bt::linear_forward_batched_q5k_fp16, nullptr}},
+    };
+    for (const auto& e : extras) {
+        const FmtCase& c = e.c;
+        const int OUT = 96, IN = 512, B = 16;
+        std::vector<uint8_t> Wb = make_blocks(c, OUT, IN);
+        if (c.fmt == B200Q_FMT_Q4_0 || c.fmt == B200Q_FMT_Q5_K) {  // their fp16 fields sit at the block's start
+            for (size_t i = 0; i < Wb.size() / c.bytes; ++i) {
+                uint8_t* p = &Wb[i * c.bytes];
+                auto put = [&](int off, float f) { const uint16_t h = bt::fp32_to_fp16_bits(f); p[off] = h & 0xFF; p[off + 1] = h >> 8; };
+                put(0, 0.02f * frand(0.5f, 1.5f));
+                if (c.fmt == B200Q_FMT_Q5_K) put(2, 0.008f * frand(0.5f, 1.5f));
+            }
+        }
+        Tensor W = Tensor::empty_on(dev, OUT, IN, c.dt);
+        cudaMemcpy(W.data, Wb.data(), Wb.size(), cudaMemcpyHostToDevice);
+        Tensor Wh;
+        c.dequant(W, Wh);
+        CHECK(Wh.dtype == Dtype::FP16 && Wh.rows == OUT && Wh.cols == IN);
+        std::vector<uint16_t> got((size_t)OUT * IN), want((size_t)OUT * IN);
+        Wh.copy_to_host_fp16(got.data());
+        oracle_dequant_16(c.fmt, Wb.data(), OUT, IN, 1, want.data());
+        CHECK(got == want);
+        std::vector<float> xf(IN), Xf((size_t)B * IN), y_ref(OUT), Y_ref((size_t)B * OUT);
+        for (auto& v : xf) v = frand(-0.3f, 0.3f);
+        for (auto& v : Xf) v = frand(-0.3f, 0.3f);
+        oracle_matmul(c.fmt, Wb.data(), xf.data(), nullptr, y_ref.data(), nullptr, 1, OUT, IN, 1);
+        oracle_matmul(c.fmt, Wb.data(), Xf.data(), nullptr, Y_ref.data(), nullptr, B, OUT, IN, 2);
+        Tensor x = Tensor::from_host_on(dev, xf.data(), IN, 1), y;
+        c.gemv(W, nullptr, x, y);
+        CHECK(y.dtype == Dtype::FP32 && y.rows == OUT && y.cols == 1);
+        CHECK(rel_l2(y.to_host_vector(), y_ref) < 2e-3);
+        Tensor X = Tensor::from_host_on(dev, Xf.data(), B, IN), Y;
+        c.batched(W, nullptr, X, Y);
+        CHECK(Y.rows == B && Y.cols == OUT);
+        CHECK(rel_l2(Y.to_host_vector(), Y_ref) < 2e-3);
+        Tensor wrong = Tensor::zeros_on(dev, 4, IN, Dtype::FP16);
+        CHECK(throws_with([&] { c.gemv(wrong, nullptr, x, y); }, "W must be Dtype::"));
+    }
+    // quantized embedding lookup
+    {
+        const FmtCase q4{"q4k", B200Q_FMT_Q4_K, Dtype::Q4_K, 256, 144, nullptr, nullptr, nullptr, nullptr};
+        const int V = 300, D = 512, B = 6;
+        const std::vector<uint8_t> Tb = make_blocks(q4, V, D);
+        Tensor table = Tensor::empty_on(dev, V, D, Dtype::Q4_K);
+        cudaMemcpy(table.data, Tb.data(), Tb.size(), cudaMemcpyHostToDevice);
+        const int32_t idx_h[B] = {7, 0, 299, 7, -3, 300};
+        int32_t* d_idx = nullptr;
+        cudaMalloc(reinterpret_cast<void**>(&d_idx), sizeof(idx_h));
+        cudaMemcpy(d_idx, idx_h, sizeof(idx_h), cudaMemcpyHostToDevice);
+        Tensor out;
+        bt::embedding_lookup_forward(table, d_idx, B, out);
+        CHECK(out.rows == B && out.cols == D && out.dtype == Dtype::FP16 && out.device == dev);
+        std::vector<uint16_t> got((size_t)B * D), full((size_t)V * D);
+        out.copy_to_host_fp16(got.data());
+        oracle_dequant_16(B200Q_FMT_Q4_K, Tb.data(), V, D, 1, full.data());
+        bool ok = true, zeros = true;
+        for (int b = 0; b < B; ++b)
+            for (int j = 0; j < D; ++j) {
+                if (idx_h[b] >= 0 && idx_h[b] < V) ok = ok && got[(size_t)b * D + j] == full[(size_t)idx_h[b] * D + j];
+                else zeros = zeros && got[(size_t)b * D + j] == 0;
+            }
+        CHECK(ok);
+        CHECK(zeros);  // indices outside the table give rows of zeros
+        Tensor out32 = Tensor::empty_on(dev, B, D, Dtype::FP32);
+        bt::embedding_lookup_forward(table, d_idx, B, out32);
+        CHECK(out32.dtype == Dtype::FP32);
+        Tensor dense = Tensor::zeros_on(dev, V, D, Dtype::FP16);
+        CHECK(throws_with([&] { bt::embedding_lookup_forward(dense, d_idx, B, out); }, "table dtype must be"));
+        CHECK(throws_with([&] { bt::embedding_lookup_forward(table, nullptr, B, out); }, "null index"));
+        Tensor none;
+        bt::embedding_lookup_forward(table, d_idx, 0, none);
+        CHECK(none.rows == 0 && none.cols == D);
+        cudaFree(d_idx);
+    }
+}
+
 int main(int argc, char** argv) {
     const std::string mode = argc > 1 ? argv[1] : "cpu";
     bt::init();
@@ -579,6 +666,7 @@ int main(int argc, char** argv) {
         test_gpu_repack_weights();
         test_gpu_swiglu_op();
         test_gpu_group_rmsnorm_op();
+        test_gpu_extra_formats_and_embedding();
         int st = 0;
         CHECK(b200q_device_status(&st) == B200Q_OK && st == 0);
     }
