@@ -329,13 +329,26 @@ def main():
         if rank != 0:
             return
         cb, k, w, ms = run_cpu_arm("reference", args.steps, max(args.warmup, 0))
+        ref_cuda = None
+        if not args.no_extras:
+            # same-box comparator: the reference's own CUDA kernels recompiled for sm_100a (informational;
+            # the line's value stays the CPU number, as the reference's path for this metric is its CPU code)
+            try:
+                import torch
+                if torch.cuda.is_available():
+                    import bench_extras
+                    ref_cuda = bench_extras.reference_cuda(measured_peaks(), torch.cuda.current_stream(), ROOT)
+                else:
+                    ref_cuda = {"unavailable": "no CUDA device"}
+            except Exception as e:  # noqa: BLE001 - the CPU line must still print
+                ref_cuda = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         print(json.dumps({
             "impl": "reference", "metric": "q4k_q6k_decode_gemv_packed_weight_GBps", "value": cb["value"],
             "unit": "GB/s", "n_gpus": args.gpus, "steps": k, "warmup": w, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": config, "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}))
+            "gpu_launches": 0, "reference_cuda_sm100a": ref_cuda}))
         return
 
     import torch

@@ -313,6 +313,77 @@ def repack_case(stream, peak_gbs, N=4096, K=14336, R=12):
     return res
 
 
+def reference_cuda(peaks, stream, root):
+    """brotensor's OWN CUDA quant kernels (src/cuda/q4k.cu, q6k.cu, q8_0.cu and the WMMA prefill files)
+    compiled unmodified for sm_100a into oracle/_ref/libref_cuda.so and called through brotensor's public
+    ops (FP16 activations and outputs, the only dtype that API has) on the same box: the decode layer
+    set, config 2 and the prefill shape, timed like this repository's own arm (CUDA events around graph
+    replays that rotate over weight replicas larger than the L2). Reference arm only."""
+    import ctypes
+    import os
+    path = os.path.join(root, "oracle", "_ref", "libref_cuda.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libref_cuda.so not built (make -C oracle gpu)"}
+    lib = ctypes.CDLL(path)
+    lib.refcuda_last_error.restype = ctypes.c_char_p
+    lib.refcuda_linear.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 3 + [ctypes.c_int] * 3
+    lib.refcuda_set_stream.argtypes = [ctypes.c_void_p]
+    if not lib.refcuda_init():
+        return {"unavailable": "brotensor's CUDA backend did not register: " + lib.refcuda_last_error().decode()}
+    tag = {synth.Q4_K: 22, synth.Q6_K: 24, synth.Q8_0: 14}  # brotensor::Dtype (include/brotensor/tensor.h:17-33)
+
+    def linear(fmt, W, X, Y, B, N, K):
+        if lib.refcuda_linear(tag[fmt], W.data_ptr(), X.data_ptr(), Y.data_ptr(), B, N, K):
+            raise RuntimeError("brotensor: " + lib.refcuda_last_error().decode())
+
+    def timed(fn, n_launch):
+        lib.refcuda_set_stream(torch.cuda.current_stream().cuda_stream)
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            lib.refcuda_set_stream(s.cuda_stream)
+            try:
+                med, mn = _time_graph(fn, n_launch, s)
+                how = "graph"
+            finally:
+                lib.refcuda_set_stream(torch.cuda.current_stream().cuda_stream)
+        return med, mn, how
+
+    def case(fmt, N, K, M, n_launch=24):
+        Ws, nbytes = _replicas(fmt, N, K, seed=N + K)
+        X = torch.from_numpy(synth.make_activations(M, K, seed=M)).cuda().half()
+        Y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        med, mn, how = timed(lambda i: linear(fmt, Ws[i % len(Ws)], X, Y, M, N, K), n_launch)
+        r = {"fmt": synth.FMT_NAME[fmt], "N": N, "K": K, "M": M, "us": med * 1e3, "us_min": mn * 1e3, "timing": how}
+        if M <= 8:
+            r["GBps"] = nbytes / (med * 1e-3) / 1e9
+            r["frac_of_hbm_peak"] = r["GBps"] / peaks["hbm_gbs"]
+        else:
+            r["TFLOPs"] = 2.0 * M * N * K / (med * 1e-3) / 1e12
+            r["frac_of_bf16_burst_peak"] = r["TFLOPs"] / peaks["bf16_tflops"]
+        # the numbers of a wrong kernel are worth nothing: compare against this repository's checked path
+        ref = torch.empty((M, N), dtype=torch.float32, device="cuda")
+        (ops.gemv if M <= 8 else ops.gemm)(fmt, Ws[0], X.float(), N, out=ref)
+        linear(fmt, Ws[0], X, Y, M, N, K)
+        torch.cuda.synchronize()
+        r["rel_l2_vs_this_repo"] = float((Y.float() - ref).norm() / ref.norm())
+        return r
+
+    out = {"what": "brotensor src/cuda quant kernels, unmodified, nvcc -gencode arch=compute_100a,code=sm_100a, "
+                   "through brotensor's public ops (FP16 x and y)"}
+    per = [case(fmt, N, K, 1) | {"name": name} for name, fmt, N, K in synth.LLAMA3_8B_LAYER_SET]
+    out["layer_set_per_kernel"] = per
+    total_us = sum(c["us"] for c in per)
+    layer_bytes = sum(synth.packed_bytes(f, n, k) for _, f, n, k in synth.LLAMA3_8B_LAYER_SET)
+    out["layer_set"] = {"us": total_us, "GBps": layer_bytes / (total_us * 1e-6) / 1e9,
+                        "note": "sum of the seven per-kernel times (each kernel timed back to back with itself)"}
+    out["config2_q8_0_14336x4096"] = [case(synth.Q8_0, 14336, 4096, M) for M in (1, 2, 4, 8)]
+    out["config3_prefill_512"] = [case(f, 14336, 4096, 512, n_launch=6) for f in (synth.Q4_K, synth.Q6_K, synth.Q8_0)]
+    return out
+
+
 def run(rank, world, peaks, stream):
     out = {}
     if world == 1:

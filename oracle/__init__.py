@@ -39,6 +39,15 @@ def build(force: bool = False) -> None:
         subprocess.run(["make", "-s", "-C", HERE, "REF=" + REF_TREE], check=True)
 
 
+def build_gpu() -> None:
+    """GPU-side checker builds (cross-compiled; see the Makefile's `gpu` target): brotensor's core with its
+    own CUDA quant kernels (_ref/libref_cuda.so, the same-box comparator) and brotensor's own parity tests
+    linked against this repository's binding (_ref/b200_test_*). Needs the reference tree and a built
+    libb200q.so; a no-op where the tree is absent (the prebuilt files travel)."""
+    if os.path.isdir(os.path.join(REF_TREE, "tests")):
+        subprocess.run(["make", "-s", "-C", HERE, "gpu", "REF=" + REF_TREE, "-j8"], check=True)
+
+
 def _ptr(a: np.ndarray, t):
     return a.ctypes.data_as(t)
 
