@@ -128,8 +128,8 @@ void check_status(int rc, const char* op) {
 }
 
 // Workspace of the tensor-core GEMM (activations in operand layout): allocated per call from the
-// stream-ordered pool on the current stream and released behind the kernel, as brotensor's batched ops
-// do (src/cuda/q4k.cu:395-411). That is legal inside a stream capture (the graph owns the allocation),
+// stream-ordered pool on the current stream and released behind the kernel, as brotensor's ops take
+// their scratch (src/cuda/bias_act.cu:34-38). That is legal inside a stream capture (the graph owns the allocation),
 // safe for threads on different streams, and no pointer outlives the call that a later, larger call
 // could free under a captured graph.
 struct StreamScratch {

@@ -79,8 +79,8 @@ void batched(int fmt, Dtype wdt, const char* dname, int block, const char* op, c
     if (B == 0 || out == 0) return;
     const void* b = (bias && bias->size() > 0) ? bias->data : nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(brotensor::cuda_current_stream());
-    // workspace of the tensor-core GEMM: stream-ordered per call, as the stock batched ops allocate
-    // theirs (src/cuda/q4k.cu:395-411)
+    // workspace of the tensor-core GEMM: stream-ordered per call, as the stock ops take their scratch
+    // (src/cuda/bias_act.cu:34-38)
     const size_t need = B > 8 ? b200q_gemm_workspace_bytes(fmt, B200Q_DT_F16, B, out, K) : 0;
     void* ws = nullptr;
     if (need && cudaMallocAsync(&ws, need, st) != cudaSuccess) op_fail(op, "workspace allocation failed");
