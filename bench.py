@@ -233,7 +233,7 @@ def run_case(spec: str, launches: int):
     print("device status", ops.device_status())
 
 
-def run_phases():
+def run_phases(pdl=1):
     """Where the time of a decode-GEMV launch goes, from %globaltimer stamps the trace build writes
     (per CTA: entry, barriers ready, predecessor complete, activations staged, first tile started,
     each pipeline's end, first and last weight copy issued). A CUDA graph chains 24 launches over
@@ -248,7 +248,7 @@ def run_phases():
     L.b200q_trace_set.argtypes = [C.c_void_p, C.c_int]
     L.b200q_trace_set.restype = None
     torch.cuda.set_device(0)
-    ops.set_option("pdl", 1)
+    ops.set_option("pdl", pdl)
     n_launch = 24
     rows = []
     for N in (1024, 4096, 14336):
@@ -288,6 +288,9 @@ def run_phases():
                          ("first_tile_started", np.median(c[:, 4] - pend)), ("last_copy_issued", np.median(c[:, 8] - pend)),
                          ("cta_end_median", np.median(end - pend)), ("cta_end_last", end.max() - pend)):
                 acc.setdefault(k, []).append(float(v))
+            for j in range(9, 16):  # activation-resident kernel: end of warp 0's items
+                if (c[:, j] > 0).any():
+                    acc.setdefault(f"warp0_item{j - 9}_done", []).append(float(np.median(c[:, j][c[:, j] > 0] - pend)))
         row = {"shape": f"q4k {N}x{K} M=1", "us_per_launch_under_trace": round(e0.elapsed_time(e1) / n_launch * 1e3, 2)}
         row.update({k: round(float(np.median(v))) for k, v in acc.items()})
         rows.append(row)
@@ -309,6 +312,7 @@ def main():
     ap.add_argument("--case", default=None, metavar="OP:FMT:N:K:M",
                     help="profiling driver: a handful of launches of one shape (op gemv|gemm|dequant, fmt q4k|q6k|q8_0) and nothing else")
     ap.add_argument("--launches", type=int, default=4, help="launches of --case")
+    ap.add_argument("--no-pdl", action="store_true", help="--phases without programmatic dependent launch")
     ap.add_argument("--phases", action="store_true",
                     help="phase breakdown of the decode GEMV from %%globaltimer stamps (needs the trace build: "
                          "python -m brotensor_b200.build --trace; B200Q_LIB=brotensor_b200/lib/libb200q_trace.so)")
@@ -316,7 +320,7 @@ def main():
     if args.case:
         return run_case(args.case, args.launches)
     if args.phases:
-        return run_phases()
+        return run_phases(pdl=0 if args.no_pdl else 1)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -468,7 +472,7 @@ def main():
         dts.append(e0.elapsed_time(e1) / n_dom)
     dom_ms = float(np.median(dts))
     achieved = alg_bytes / (dom_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "gemv_dp_kernel<Q4_K, M=1> on 14336x4096 (gate_proj / up_proj)", "achieved": achieved,
+    roofline = {"bound": "hbm", "kernel": "gemv_xr_q4k_kernel (activation-resident Q4_K decode GEMV) on 14336x4096 (gate_proj / up_proj)", "achieved": achieved,
                 "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": DOMINANT_KERNEL_DRAM_TRAFFIC,
                 "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch",

@@ -33,6 +33,10 @@ void dp_set_tile_pairs(int v);
 void dp_set_split_full(int v);
 void dp_set_wait_limit_us(int v);
 void dp_set_lean(int v);
+int launch_gemv_xr(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N, int K,
+                   int sms, int* status, cudaStream_t st, bool* taken);
+void xr_set_enabled(int v);
+int xr_get_enabled();
 int dp_get_wait_limit_us();
 int dp_get_tile_pairs();
 int dp_get_groups();
@@ -231,6 +235,10 @@ static int gemv_streaming(DevInfo* d, int fmt, const void* W, const void* X, int
     const bool mma_first = M >= (fmt == kQ8_0 ? 3 : 4);
     if (mma_first) {
         if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, smem, d->status, st, taken)) return rc;
+        if (*taken) return B200Q_OK;
+    }
+    if (M == 1) {
+        if (int rc = launch_gemv_xr(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->status, st, taken)) return rc;
         if (*taken) return B200Q_OK;
     }
     if (M <= 4) {
@@ -464,6 +472,7 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "gemm_pair")) gemm_set_pair(value);
     else if (!strcmp(key, "wait_limit_us")) dp_set_wait_limit_us(value);
     else if (!strcmp(key, "gemv_lean")) dp_set_lean(value);
+    else if (!strcmp(key, "gemv_xr")) xr_set_enabled(value);
     else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
     return B200Q_OK;
 }
@@ -476,6 +485,7 @@ int b200q_get_option(const char* key, int* out) {
     else if (!strcmp(key, "gemv_stage_kb")) *out = stream_get_option(2);
     else if (!strcmp(key, "gemv_grid")) *out = stream_get_option(3);
     else if (!strcmp(key, "gemv_groups")) *out = dp_get_groups();
+    else if (!strcmp(key, "gemv_xr")) *out = xr_get_enabled();
     else if (!strcmp(key, "gemv_tile_pairs")) *out = dp_get_tile_pairs();
     else if (!strcmp(key, "gemm_pair")) *out = gemm_get_pair();
     else if (!strcmp(key, "wait_limit_us")) *out = dp_get_wait_limit_us();

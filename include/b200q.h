@@ -256,6 +256,8 @@ int b200q_device_status(int* status_out);
  *                 one pipeline with 32-row tiles; "gemv_split_full" (Q6_K only) -1 = automatic, 0 = one full
  *                 barrier per stage, 1 = one per consumer warp and stage
  *   "gemm_pair"   0 = one-CTA tcgen05 kernel, otherwise the CTA-pair kernel (default)
+ *   "gemv_xr"     Q4_K, one activation row, K <= 4096: 1 = the activation-resident kernel where it is the
+ *                 faster one (default), 2 = for every such call, 0 = never
  *   "gemv_lean"   0 = never take the trimmed instantiation of the integer-dot kernel (FP32 in and out, no bias)
  *   "wait_limit_us" bound of the decode kernels' device-side waits (stage barriers, peer arrival) in
  *                 microseconds; 0 = one second. Tests shorten it to see a wait run out.
