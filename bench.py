@@ -204,9 +204,12 @@ def lm_head_summary(extras, world):
            "tok_per_s": fused.get("tok_per_s", lh.get("tok_per_s")),
            "nccl_all_gather_us_per_token": lh.get("us_per_token"), "shard_gemv_only_us": lh.get("gemv_only_us"),
            "oracle_rel_l2": lh.get("oracle_rel_l2"), "matches_gathered_bitwise": fused.get("matches_gathered_bitwise")}
-    for k in ("greedy", "efficiency_note"):
-        if k in lh:
-            out[k] = lh[k]
+    g = fused.get("greedy") or {}
+    if g:
+        out["greedy_us_per_token"] = g.get("us_per_token")
+        out["greedy_matches_argmax_of_gathered"] = g.get("matches_argmax_of_gathered")
+    # efficiency against one GPU needs the N = 1 line of the same box; the ideal is N x the one-GPU rate
+    out["ideal_us_per_token_at_hbm_peak"] = synth.packed_bytes(synth.Q6_K, 128256, 4096) / max(world, 1) / (measured_peaks()["hbm_gbs"] * 1e3)
     return out
 
 
@@ -233,7 +236,7 @@ def run_case(spec: str, launches: int):
     print("device status", ops.device_status())
 
 
-def run_phases(pdl=1):
+def run_phases(pdl=1, shapes="q4k:1024:4096,q4k:4096:4096,q4k:14336:4096,q6k:4096:14336"):
     """Where the time of a decode-GEMV launch goes, from %globaltimer stamps the trace build writes
     (per CTA: entry, barriers ready, predecessor complete, activations staged, first tile started,
     each pipeline's end, first and last weight copy issued). A CUDA graph chains 24 launches over
@@ -251,8 +254,9 @@ def run_phases(pdl=1):
     ops.set_option("pdl", pdl)
     n_launch = 24
     rows = []
-    for N in (1024, 4096, 14336):
-        fmt, K = synth.Q4_K, 4096
+    for spec in shapes.split(","):
+        fname, N, K = spec.split(":")
+        fmt, N, K = {"q4k": synth.Q4_K, "q6k": synth.Q6_K, "q8_0": synth.Q8_0}[fname], int(N), int(K)
         nbytes = synth.packed_bytes(fmt, N, K)
         R = max(2, min(32, int(1.0e9 // nbytes)))
         base = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=1)).cuda()
@@ -291,7 +295,7 @@ def run_phases(pdl=1):
             for j in range(9, 16):  # activation-resident kernel: end of warp 0's items
                 if (c[:, j] > 0).any():
                     acc.setdefault(f"warp0_item{j - 9}_done", []).append(float(np.median(c[:, j][c[:, j] > 0] - pend)))
-        row = {"shape": f"q4k {N}x{K} M=1", "us_per_launch_under_trace": round(e0.elapsed_time(e1) / n_launch * 1e3, 2)}
+        row = {"shape": f"{fname} {N}x{K} M=1", "us_per_launch_under_trace": round(e0.elapsed_time(e1) / n_launch * 1e3, 2)}
         row.update({k: round(float(np.median(v))) for k, v in acc.items()})
         rows.append(row)
         print(json.dumps(row), flush=True)
@@ -313,14 +317,14 @@ def main():
                     help="profiling driver: a handful of launches of one shape (op gemv|gemm|dequant, fmt q4k|q6k|q8_0) and nothing else")
     ap.add_argument("--launches", type=int, default=4, help="launches of --case")
     ap.add_argument("--no-pdl", action="store_true", help="--phases without programmatic dependent launch")
-    ap.add_argument("--phases", action="store_true",
+    ap.add_argument("--phases", nargs="?", const="", default=None, metavar="FMT:N:K,...",
                     help="phase breakdown of the decode GEMV from %%globaltimer stamps (needs the trace build: "
                          "python -m brotensor_b200.build --trace; B200Q_LIB=brotensor_b200/lib/libb200q_trace.so)")
     args = ap.parse_args()
     if args.case:
         return run_case(args.case, args.launches)
-    if args.phases:
-        return run_phases(pdl=0 if args.no_pdl else 1)
+    if args.phases is not None:
+        return run_phases(0 if args.no_pdl else 1, *([args.phases] if args.phases else []))
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -181,10 +181,34 @@ def _fused_head(fmt, rows, K, row0, N, rank, world, Ws, x, stream, n_launch, ref
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
+        # the greedy-sampling form: one (value, row) candidate per rank crosses the links instead of the logits
+        head.run_topk(x.data_ptr(), K, 1, 0, weights[0])
+        tv, tr = head.top(1)
+        ref = ref_full.reshape(-1).cpu().numpy()
+        best = int(np.lexsort((np.arange(ref.size), -ref))[0])
+        greedy_ok = bool(int(tr[0]) == best and tv[0] == ref[best])
+        if world > 1:
+            dist.barrier()
+
+        def step_top(i):
+            head.run_topk(x.data_ptr(), K, 1, 0, weights[i % len(weights)])
+
+        hostapi.set_stream(stream.cuda_stream, dev)
+        gmed, _ = _time_graph(step_top, n_launch, stream)
+        hostapi.set_stream(torch.cuda.current_stream().cuda_stream, dev)
+        t = torch.tensor([gmed], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gmed = float(t.item())
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         status = ops.device_status()
         head.close()
         return {"us_per_token": med * 1e3, "tok_per_s": 1.0 / (med * 1e-3), "matches_gathered_bitwise": same,
-                "device_status": status, "exchange": "peer stores + arrival words inside the GEMV kernel (CUDA IPC memory)"}
+                "greedy": {"us_per_token": gmed * 1e3, "tok_per_s": 1.0 / (gmed * 1e-3), "matches_argmax_of_gathered": greedy_ok,
+                           "exchange": "one (value, row) candidate per rank; argmax of the whole vocabulary on every rank"},
+                "device_status": status, "exchange": "peer stores + one release-add per CTA and peer inside the GEMV kernel (CUDA IPC memory)"}
     except Exception as ex:  # noqa: BLE001
         return {"error": repr(ex)}
 

@@ -33,6 +33,7 @@ void dp_set_tile_pairs(int v);
 void dp_set_split_full(int v);
 void dp_set_wait_limit_us(int v);
 void dp_set_lean(int v);
+void dp_set_step_fill(int v);
 int launch_gemv_xr(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N, int K,
                    int sms, int* status, cudaStream_t st, bool* taken);
 void xr_set_enabled(int v);
@@ -359,20 +360,27 @@ int b200q_gemv_multi_rmsnorm(int fmt, int n, const void* const* W, const int* N,
     return B200Q_OK;
 }
 
-int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
-                     int row_offset, int total_rows, int rank, int world, void* const* peer_out,
-                     void* const* peer_flags, void* state, void* stream) {
-    if (b200q_block_elems(fmt) && !streaming_fmt(fmt)) return fail(B200Q_ERR_UNSUPPORTED, "gemv_shard: block format %d has no sharded form", fmt);
+static int gemv_shard_impl(const char* name, int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows,
+                           int K, int row_offset, int total_rows, int rank, int world, void* const* peer_out,
+                           void* const* peer_flags, void* const* peer_cand, void* state, int k, void* top_val, void* top_idx,
+                           void* stream) {
+    if (b200q_block_elems(fmt) && !streaming_fmt(fmt)) return fail(B200Q_ERR_UNSUPPORTED, "%s: block format %d has no sharded form", name, fmt);
     static float dummy_y;  // check_linear_args wants a non-null result pointer; the sharded form has none
-    if (int rc = check_linear_args("gemv_shard", fmt, W_shard, x, x_dtype, &dummy_y, B200Q_DT_F32, 1, rows, K)) return rc;
+    if (int rc = check_linear_args(name, fmt, W_shard, x, x_dtype, &dummy_y, B200Q_DT_F32, 1, rows, K)) return rc;
     if (world < 1 || world > kMaxShardRanks || rank < 0 || rank >= world)
-        return fail(B200Q_ERR_BAD_ARG, "gemv_shard: rank %d of %d (at most %d ranks)", rank, world, kMaxShardRanks);
+        return fail(B200Q_ERR_BAD_ARG, "%s: rank %d of %d (at most %d ranks)", name, rank, world, kMaxShardRanks);
     if (row_offset < 0 || total_rows <= 0 || (long long)row_offset + rows > total_rows)
-        return fail(B200Q_ERR_BAD_ARG, "gemv_shard: rows [%d, %d) do not lie in [0, %d)", row_offset, row_offset + rows, total_rows);
-    if (!peer_out || !peer_flags || !state) return fail(B200Q_ERR_BAD_ARG, "gemv_shard: null peer table or state");
+        return fail(B200Q_ERR_BAD_ARG, "%s: rows [%d, %d) do not lie in [0, %d)", name, row_offset, row_offset + rows, total_rows);
+    if (!peer_out || !peer_flags || !state) return fail(B200Q_ERR_BAD_ARG, "%s: null peer table or state", name);
     for (int q = 0; q < world; ++q)
-        if (!peer_out[q] || !peer_flags[q]) return fail(B200Q_ERR_BAD_ARG, "gemv_shard: null pointer for rank %d", q);
-    if (rows == 0) return fail(B200Q_ERR_UNSUPPORTED, "gemv_shard: an empty shard cannot signal its arrival");
+        if (!peer_out[q] || !peer_flags[q]) return fail(B200Q_ERR_BAD_ARG, "%s: null pointer for rank %d", name, q);
+    if (rows == 0) return fail(B200Q_ERR_UNSUPPORTED, "%s: an empty shard cannot signal its arrival", name);
+    if (k) {
+        if (k < 1 || k > kMaxTopK) return fail(B200Q_ERR_BAD_ARG, "%s: k = %d candidates (1 .. %d)", name, k, kMaxTopK);
+        if (!peer_cand || !top_val || !top_idx) return fail(B200Q_ERR_BAD_ARG, "%s: null candidate table or result", name);
+        for (int q = 0; q < world; ++q)
+            if (!peer_cand[q]) return fail(B200Q_ERR_BAD_ARG, "%s: null candidate table for rank %d", name, q);
+    }
     DevInfo* d;
     if (int rc = dev_info(&d)) return rc;
     ShardOut sh;
@@ -383,13 +391,33 @@ int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, c
     sh.out = reinterpret_cast<float* const*>(peer_out);
     sh.flags = reinterpret_cast<unsigned int* const*>(peer_flags);
     sh.state = static_cast<unsigned int*>(state);
+    sh.topk = k;
+    sh.cand = reinterpret_cast<uint32_t* const*>(peer_cand);
+    sh.top_val = static_cast<float*>(top_val);
+    sh.top_idx = static_cast<int*>(top_idx);
     bool taken = false;
     if (int rc = launch_gemv_dp(fmt, W_shard, x, x_dtype, bias_shard, nullptr, B200Q_DT_F32, 1, rows, K, d->sms,
                                 d->smem_optin - 1024, d->status, static_cast<cudaStream_t>(stream), &taken, &sh))
         return rc;
     if (!taken)
-        return fail(B200Q_ERR_UNSUPPORTED, "gemv_shard: shape (rows %d, K %d, fmt %d) or weight alignment is outside the streaming kernel", rows, K, fmt);
+        return fail(B200Q_ERR_UNSUPPORTED, "%s: shape (rows %d, K %d, fmt %d) or weight alignment is outside the streaming kernel", name, rows, K, fmt);
     return B200Q_OK;
+}
+
+int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
+                     int row_offset, int total_rows, int rank, int world, void* const* peer_out,
+                     void* const* peer_flags, void* state, void* stream) {
+    return gemv_shard_impl("gemv_shard", fmt, W_shard, x, x_dtype, bias_shard, rows, K, row_offset, total_rows, rank, world, peer_out,
+                           peer_flags, nullptr, state, 0, nullptr, nullptr, stream);
+}
+
+int b200q_gemv_shard_topk(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
+                          int row_offset, int total_rows, int rank, int world, void* const* peer_out,
+                          void* const* peer_flags, void* const* peer_cand, void* state, int k, void* top_val, void* top_idx,
+                          void* stream) {
+    if (k < 1) return fail(B200Q_ERR_BAD_ARG, "gemv_shard_topk: k = %d candidates (1 .. %d)", k, kMaxTopK);
+    return gemv_shard_impl("gemv_shard_topk", fmt, W_shard, x, x_dtype, bias_shard, rows, K, row_offset, total_rows, rank, world,
+                           peer_out, peer_flags, peer_cand, state, k, top_val, top_idx, stream);
 }
 
 size_t b200q_gemm_workspace_bytes(int fmt, int x_dtype, int M, int N, int K) {
@@ -473,6 +501,7 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "wait_limit_us")) dp_set_wait_limit_us(value);
     else if (!strcmp(key, "gemv_lean")) dp_set_lean(value);
     else if (!strcmp(key, "gemv_xr")) xr_set_enabled(value);
+    else if (!strcmp(key, "gemv_step_fill")) dp_set_step_fill(value);
     else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
     return B200Q_OK;
 }

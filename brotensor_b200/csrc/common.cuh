@@ -71,6 +71,7 @@ void set_error(const char* fmt, ...);
 int fail(int code, const char* fmt, ...);
 
 constexpr int kMaxShardRanks = 8;
+constexpr int kMaxTopK = 8;  // candidates per rank in the candidate form of the sharded head
 constexpr int kMaxSegments = 4;  // weight matrices one grouped GEMV launch can take
 // Host-side description of a row-sharded GEMV output (StreamParams::sh_* on the device side).
 struct ShardOut {
@@ -78,6 +79,11 @@ struct ShardOut {
     float* const* out;
     unsigned int* const* flags;
     unsigned int* state;
+    // candidate form: k in 1..kMaxTopK, every rank's candidate table, this rank's results (else 0 / null)
+    int topk = 0;
+    uint32_t* const* cand = nullptr;
+    float* top_val = nullptr;
+    int* top_idx = nullptr;
 };
 int* device_status_word(int dev);  // device pointer to this device's status word, or nullptr
 

@@ -495,19 +495,79 @@ __device__ __forceinline__ void item_q6kp_half(uint32_t rowA, uint32_t rowB, int
     }
 }
 
+// Order of the LM head's candidates: larger value first, among equal values the lower index
+// (brotensor's greedy rule, include/brotensor/ops/sampling.h:27-28: "ties keep the lowest index").
+__device__ __forceinline__ bool cand_before(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+
+// The k best of the candidates the CTA's threads hold (C each; unused ones are (-inf, INT_MAX)), in
+// the candidates' order, left in scr[64 .. 64 + k) (values) and scr[64 + kMaxTopK ..) (rows): k
+// passes, each taking the best candidate that comes after the previous pick. Called by all `nthreads`
+// threads (named barrier 1); scr[32 .. 64 + 2 * kMaxTopK) is scratch.
+template <int C>
+__device__ __forceinline__ void block_topk(const float (&v)[C], const int (&ix)[C], int k, uint32_t* scr, int tid, int nthreads) {
+    const int nwarps = nthreads >> 5;
+    float pv = __int_as_float(0x7f800000);  // +inf
+    int pi = -1;
+    for (int r = 0; r < k; ++r) {
+        float bv = __int_as_float(0xff800000);  // -inf
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int u = 0; u < C; ++u)
+            if (cand_before(pv, pi, v[u], ix[u]) && cand_before(v[u], ix[u], bv, bi)) { bv = v[u]; bi = ix[u]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (cand_before(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if ((tid & 31) == 0) {
+            scr[32 + 2 * (tid >> 5)] = __float_as_uint(bv);
+            scr[33 + 2 * (tid >> 5)] = (uint32_t)bi;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        bv = __uint_as_float(scr[32]);
+        bi = (int)scr[33];
+        for (int w = 1; w < nwarps; ++w) {  // the same order in every thread
+            const float ov = __uint_as_float(scr[32 + 2 * w]);
+            const int oi = (int)scr[33 + 2 * w];
+            if (cand_before(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        pv = bv;
+        pi = bi;
+        if (tid == 0) {  // fewer than k candidates leave (-inf, INT_MAX)
+            scr[64 + r] = __float_as_uint(bv);
+            scr[64 + kMaxTopK + r] = (uint32_t)bi;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    }
+}
+
 // Sharded epilogue, run by all `nthreads` consumer threads of a CTA (thread ids 0 .. nthreads-1) after
-// they have stored the CTA's rows [row_begin, row_end) into this rank's result vector.
+// they have stored the CTA's rows [row_begin, row_end) into this rank's result vector. `scr` is at
+// least 1 KB of shared memory that nothing else uses any more.
+//
+// Full-logits form (sh_topk == 0): the CTA forwards its rows to every peer's result vector and then
+// publishes ITSELF at every peer: one red.release.sys.add of 1 on the peer's counter word for this
+// rank (the release orders the CTA's forwarded rows, seen through the CTA barrier, before it). Nothing
+// waits for this rank's slowest CTA before the fast ones are announced. The CTA that finishes last on
+// this rank (a gpu-scope counter) waits - bounded - until every peer's counter at this rank has
+// reached calls x that peer's grid size (which the peer's CTA 0 leaves in a second word), so that on
+// return from the kernel the whole result vector of this launch is complete in this rank's memory.
+//
+// Candidate form (sh_topk = k in 1..8): nothing but k (value, index) pairs per rank crosses the links.
+// The last CTA of the rank selects the shard's k best logits, writes them into every peer's
+// candidate table, announces the whole grid at once, waits for the peers likewise, merges the
+// world x k candidates and leaves the k best (value, global row) in sh_top_val / sh_top_idx.
 __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_begin, int row_end, unsigned int sh_epoch,
-                                              unsigned int sh_buf, int tid, int nthreads) {
-    // Every consumer warp gets here (aborted ones too). When the whole grid has stored its
-    // rows, the last CTA publishes this rank's arrival to all ranks and waits - bounded -
-    // until every rank has arrived at this one, so that on return from the kernel the
-    // full result vector of this launch is complete in this rank's memory.
+                                              unsigned int sh_buf, int tid, int nthreads, uint32_t* scr) {
+    // Every consumer warp gets here (aborted ones too).
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-    // This CTA's rows are one contiguous piece of the result vector: forward it to every peer
-    // with coalesced stores (a warp writes 128 consecutive bytes per peer) instead of one
-    // 4-byte NVLink write per row and peer.
-    if (p.sh_world > 1) {
+    const int k = p.sh_topk;
+    const unsigned int epoch = sh_epoch + 1u;
+    if (k == 0 && p.sh_world > 1) {
+        // This CTA's rows are one contiguous piece of the result vector: forward it to every peer
+        // with coalesced stores (a warp writes 128 consecutive bytes per peer) instead of one
+        // 4-byte NVLink write per row and peer.
         const size_t base = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + row_begin);
         const float* own = p.sh_out[p.sh_rank] + base;
         for (int i = tid; i < row_end - row_begin; i += nthreads) {
@@ -516,41 +576,130 @@ __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_beg
                 if (q != p.sh_rank) p.sh_out[q][base + i] = v;
         }
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-    }
-    if (tid == 0) {
-        // Release chain with one system-scope fence on the critical path: each CTA's arrival
-        // is a gpu-scope release (its rows, seen through the barrier above, come before it);
-        // the last CTA acquires those, then one system-scope fence orders the whole grid's
-        // peer stores before the arrival words (release cumulativity).
-        unsigned int done;
-        asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
-        if (done == gridDim.x - 1) {
-            asm volatile("fence.acq_rel.gpu;" ::: "memory");
-            p.sh_state[0] = 0;
-            const unsigned int epoch = sh_epoch + 1u;
-            asm volatile("fence.acq_rel.sys;" ::: "memory");
-            for (int q = 0; q < p.sh_world; ++q)
-                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[q] + p.sh_rank), "r"(epoch) : "memory");
-            const uint64_t t0 = global_timer_ns();
-            bool ok = true;
-            for (int q = 0; q < p.sh_world && ok; ++q) {
-                for (;;) {
-                    unsigned int v;
-                    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
-                    if ((int)(v - epoch) >= 0) break;
-                    if (global_timer_ns() - t0 > (p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs)) {  // a peer never arrived
-                        if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
-                        ok = false;
-                        break;
-                    }
-                }
-            }
-            // acquire side for the peers' rows (they sit in this GPU's L2 already: a peer's rows
-            // are performed before its arrival word); needed only when there are peers
-            if (p.sh_world > 1) asm volatile("fence.acq_rel.sys;" ::: "memory");
-            *(volatile unsigned int*)&p.sh_state[1] = epoch;
+        if (tid < p.sh_world && tid != p.sh_rank) {  // one thread per peer
+            if (blockIdx.x == 0) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[tid] + kMaxShardRanks + p.sh_rank), "r"(gridDim.x) : "memory");
+            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.sh_flags[tid] + p.sh_rank) : "memory");
         }
     }
+    uint32_t* const cta_cand = k > 0 ? p.sh_cand[p.sh_rank] + 2 * kMaxShardRanks * 2 * kMaxTopK : nullptr;  // [CTA][8 values, 8 rows]
+    if (k > 0) {
+        // ---- this CTA's k best rows, from its own piece of the result vector (at most four per thread in registers)
+        const float* own = p.sh_out[p.sh_rank] + (size_t)sh_buf * p.sh_total + p.sh_row_offset + row_begin;
+        float v[4];
+        int ix[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = tid + u * nthreads;
+            v[u] = i < row_end - row_begin ? __ldcg(own + i) : __int_as_float(0xff800000);
+            ix[u] = i < row_end - row_begin ? p.sh_row_offset + row_begin + i : 0x7fffffff;
+        }
+        block_topk<4>(v, ix, k, scr, tid, nthreads);
+        if (tid < 2 * kMaxTopK) cta_cand[(size_t)blockIdx.x * 2 * kMaxTopK + tid] = scr[64 + tid];
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    }
+    if (tid == 0) {
+        // the rank's last CTA: acquires the other CTAs' candidates (candidate form) through the gpu-scope counter
+        unsigned int done;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
+        scr[0] = (done == gridDim.x - 1) ? 1u : 0u;
+    }
+    if (k == 0 && tid != 0) return;
+    if (k > 0) {
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        if (!scr[0]) return;
+        // ---- this rank's k best: the best of the CTAs' candidates (at most eight per thread in registers)
+        float v[8];
+        int ix[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int c = tid + u * nthreads, cta = c / kMaxTopK, j = c % kMaxTopK;
+            const bool in = cta < (int)gridDim.x && j < k;
+            v[u] = in ? __uint_as_float(__ldcg(cta_cand + (size_t)cta * 2 * kMaxTopK + j)) : __int_as_float(0xff800000);
+            ix[u] = in ? (int)__ldcg(cta_cand + (size_t)cta * 2 * kMaxTopK + kMaxTopK + j) : 0x7fffffff;
+        }
+        block_topk<8>(v, ix, k, scr, tid, nthreads);
+        // into every rank's table (this rank's own copy included: the merge below reads one table)
+        for (int j = tid; j < p.sh_world * 2 * kMaxTopK; j += nthreads) {
+            const int q = j / (2 * kMaxTopK), w = j - q * 2 * kMaxTopK;
+            if ((w & (kMaxTopK - 1)) < k)
+                p.sh_cand[q][((size_t)sh_buf * kMaxShardRanks + p.sh_rank) * 2 * kMaxTopK + w] = scr[64 + w];
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        if (tid < p.sh_world && tid != p.sh_rank) {
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[tid] + kMaxShardRanks + p.sh_rank), "r"(gridDim.x) : "memory");
+            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.sh_flags[tid] + p.sh_rank), "r"(gridDim.x) : "memory");
+        }
+        if (tid != 0) {
+            if (tid >= 32) return;
+        }
+    } else if (!scr[0]) {
+        return;
+    }
+    // ---- the rank's last CTA: thread 0 waits for the peers (warp 0 stays for the candidate merge)
+    bool ok = true;
+    if (tid == 0) {
+        p.sh_state[0] = 0;
+        const uint64_t t0 = global_timer_ns();
+        const uint64_t limit = p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs;
+        for (int q = 0; q < p.sh_world && ok; ++q) {
+            if (q == p.sh_rank) continue;
+            for (;;) {
+                unsigned int g, v;
+                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(g) : "l"(p.sh_flags[p.sh_rank] + kMaxShardRanks + q) : "memory");
+                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
+                if (g != 0 && (int)(v - epoch * g) >= 0) break;
+                if (global_timer_ns() - t0 > limit) {  // a peer never arrived
+                    if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
+                    ok = false;
+                    break;
+                }
+            }
+        }
+        // acquire side for the peers' rows or candidates (a peer's stores are performed before its
+        // announcement); needed only when there are peers
+        if (p.sh_world > 1) asm volatile("fence.acq_rel.sys;" ::: "memory");
+        scr[1] = ok ? 1u : 0u;
+    }
+    if (k > 0) {
+        __syncwarp();
+        ok = scr[1] != 0;
+        // merge: lane l holds candidate l % 8 of rank l / 8 (two per lane with more than four ranks)
+        const uint32_t* tab = p.sh_cand[p.sh_rank] + (size_t)sh_buf * kMaxShardRanks * 2 * kMaxTopK;
+        float cv[2];
+        int ci[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int c = tid + 32 * h, q = c / kMaxTopK, j = c % kMaxTopK;
+            cv[h] = __int_as_float(0xff800000);
+            ci[h] = 0x7fffffff;
+            if (ok && q < p.sh_world && j < k) {
+                cv[h] = __uint_as_float(__ldcg(tab + (size_t)q * 2 * kMaxTopK + j));
+                ci[h] = (int)__ldcg(tab + (size_t)q * 2 * kMaxTopK + kMaxTopK + j);
+            }
+        }
+        float pv = __int_as_float(0x7f800000);
+        int pi = -1;
+        for (int r = 0; r < k; ++r) {
+            float bv = __int_as_float(0xff800000);
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+                if (cand_before(pv, pi, cv[h], ci[h]) && cand_before(cv[h], ci[h], bv, bi)) { bv = cv[h]; bi = ci[h]; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (cand_before(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+            pv = bv;
+            pi = bi;
+            if (tid == 0 && ok) {
+                p.sh_top_val[r] = bv;
+                p.sh_top_idx[r] = bi;
+            }
+        }
+    }
+    if (tid == 0) *(volatile unsigned int*)&p.sh_state[1] = epoch;
 }
 
 // NG independent pipelines inside one CTA: pipeline g has eight consumer warps, its own
@@ -651,12 +800,16 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         const uint32_t ring = sbase + (uint32_t)(p.off_stage + g * p.n_stages * stage_bytes);
         int slot = 0;
         uint32_t phase = 0;
+        bool met = !p.step_fill;  // whether this warp has been to named barrier 3 (see below)
         for (int tile = g; tile < n_tiles; tile += NG) {
             const TileRef tr = tile_ref<EXT>(p, row_begin + tile * TR);
             const int row0 = tr.row0;
             const int nrows = min(min(TR, row_end - (row_begin + tile * TR)), tr.N - row0);
             for (int slice = 0; slice < (kLean ? 1 : p.n_slices); ++slice) {
-                if (!wait_or_abort(smem_u32(&bar_empty[g][slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty, wait_limit)) return;
+                if (!wait_or_abort(smem_u32(&bar_empty[g][slot]), phase ^ 1, &abort_flag, p.status, kDevTimeoutEmpty, wait_limit)) {
+                    if (!met) asm volatile("bar.sync 3, %0;" ::"n"((kConsumers + NG) * 32) : "memory");
+                    return;
+                }
                 const int c0 = slice * p.slice_chunks;
                 const int nch = min(p.slice_chunks, p.chunks_per_row - c0);
                 const uint32_t bytes = (uint32_t)nch * Chunk<FMT>::bytes;
@@ -678,12 +831,22 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                              split_full ? full + 8u * ((lane >> 1) & (kConsumerWarps - 1)) : full);
                 }
                 TRACE_STAMP(g == 0 && lane == 0 && tile == 0 && slice == 0, 7);
+                // Copies in flight share the SM's ingest rate with the activation loads: with the whole
+                // ring requested at once the activations (which every item needs) arrive last. So only
+                // the first stage goes out ahead of them; the rest follows once the consumers are about
+                // to issue their loads (named barrier 3: they arrive, the producers wait).
+                if (!met) {
+                    met = true;
+                    asm volatile("bar.sync 3, %0;" ::"n"((kConsumers + NG) * 32) : "memory");
+                }
                 if (++slot == p.n_stages) {
                     slot = 0;
                     phase ^= 1;
                 }
             }
         }
+        // every producer warp meets barrier 3 exactly once, with or without tiles of its own
+        if (!met) asm volatile("bar.sync 3, %0;" ::"n"((kConsumers + NG) * 32) : "memory");
         TRACE_STAMP(g == 0 && lane == 0, 8);
         return;
     }
@@ -691,6 +854,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     // ---- consumers
     grid_dep_wait();  // activations (and Y) belong to the stream-ordered predecessor
     TRACE_STAMP(tid == 0, 2);
+    if (p.step_fill) asm volatile("bar.arrive 3, %0;" ::"n"((kConsumers + NG) * 32) : "memory");
     // launch counter of the sharded form: stable while this launch runs (only its last CTA bumps it)
     const unsigned int sh_epoch = ((EXT & kExtShard) && p.sh_world > 0) ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
     const unsigned int sh_buf = (sh_epoch + 1u) & 1u;
@@ -861,7 +1025,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         }
     }
     TRACE_STAMP((tid & 31) == 0, 5 + (warp >= kConsumerWarps ? 1 : 0));  // last writer of each pipeline wins: about its end
-    if ((EXT & kExtShard) && p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32);
+    if ((EXT & kExtShard) && p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32, reinterpret_cast<uint32_t*>(smem_raw + (sbase - smem_u32(smem_raw))));
 }
 
 // ---- host side ------------------------------------------------------------------------
@@ -881,6 +1045,8 @@ void dp_set_groups(int v) { g_opt_groups = v < 1 ? 1 : (v > 2 ? 2 : v); }
 int dp_get_groups() { return g_opt_groups; }
 // Bound of the kernels' mbarrier and peer-arrival waits in microseconds; 0: one second.
 // 1: launches that qualify take the lean instantiation (kExtLean)
+static int g_opt_step_fill = 1;
+void dp_set_step_fill(int v) { g_opt_step_fill = v ? 1 : 0; }
 static int g_opt_lean = 1;
 void dp_set_lean(int v) { g_opt_lean = v ? 1 : 0; }
 
@@ -999,6 +1165,7 @@ static int launch_dp_k(const StreamParams& p_in, int grid, size_t smem, cudaStre
         p.split_r = units % grid;
     }
     p.wait_limit_us = (unsigned int)g_opt_wait_limit_us;
+    p.step_fill = g_opt_step_fill;
 #ifdef B200Q_TRACE
     p.trace = dp_trace_next(grid);
 #endif
@@ -1093,8 +1260,17 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
         for (int q = 0; q < sh->world; ++q) {
             p.sh_out[q] = sh->out[q];
             p.sh_flags[q] = sh->flags[q];
+            p.sh_cand[q] = sh->cand ? sh->cand[q] : nullptr;
         }
         p.sh_state = sh->state;
+        p.sh_topk = sh->topk;
+        // the candidate form keeps a CTA's rows (four per consumer thread) and the CTAs' candidates
+        // (eight per thread, 256 CTAs in the scratch table) in registers
+        const int threads = kConsumerWarps * ng * 32;
+        if (sh->topk > 0 && ((N + grid - 1) / grid + kTileRows > 4 * threads || grid * kMaxTopK > 8 * threads || grid > 256))
+            return fail(B200Q_ERR_UNSUPPORTED, "gemv_shard_topk: %d rows over %d CTAs exceed the candidate form's capacity", N, grid);
+        p.sh_top_val = sh->top_val;
+        p.sh_top_idx = sh->top_idx;
     }
     switch (M) {
         case 1: return launch_dp_g<FMT, 1>(p, ng, rp, grid, smem, st);

@@ -34,6 +34,7 @@ struct StreamParams {
     // split_q + (b < split_r) of them, starting at b * split_q + min(b, split_r) (no division on the device).
     int split_q, split_r;
     unsigned int wait_limit_us;  // bound of the device-side waits in microseconds (0: one second)
+    int step_fill;               // 1: only the first stage of a pipeline is requested ahead of the activation loads
 #ifdef B200Q_TRACE
     unsigned long long* trace;  // trace builds: sixteen %globaltimer stamps per CTA of this launch
 #endif
@@ -61,8 +62,14 @@ struct StreamParams {
     int sh_world, sh_rank;       // sh_world == 0: plain GEMV
     int sh_row_offset, sh_total; // first global row of this shard; rows of the whole matrix
     float* sh_out[kMaxShardRanks];         // rank q's result buffers: two vectors of sh_total floats, used alternately
-    unsigned int* sh_flags[kMaxShardRanks]; // rank q's arrival words, one per writing rank
+    unsigned int* sh_flags[kMaxShardRanks]; // rank q's arrival words: [r] CTAs of rank r announced so far (all calls), [kMaxShardRanks + r] rank r's grid size
     unsigned int* sh_state;      // this rank: [0] CTAs finished in this launch, [1] completed launches (epoch)
+    // Candidate form of the sharded head (sh_topk = k > 0): rank q's candidate table
+    // [2 parities][kMaxShardRanks writers][kMaxTopK values, kMaxTopK indices] and this rank's k results.
+    int sh_topk;
+    uint32_t* sh_cand[kMaxShardRanks];
+    float* sh_top_val;
+    int* sh_top_idx;
 };
 
 template <int FMT>

@@ -296,6 +296,25 @@ int b200h_head_run(void* hh, void* W_or_null, void* x_dev, int in, int x_dtype) 
         else h.forward(x);
     });
 }
+// The candidate form: k (value, row) pairs instead of the logits cross the links.
+int b200h_head_run_topk(void* hh, void* W_or_null, void* x_dev, int in, int x_dtype, int k) {
+    return guarded([&] {
+        ShardedHead& h = *static_cast<ShardedHead*>(hh);
+        const Tensor x = Tensor::view(h.device(), x_dev, in, 1, static_cast<Dtype>(x_dtype));
+        if (W_or_null) h.forward_topk_with(*static_cast<Tensor*>(W_or_null), x, k);
+        else h.forward_topk(x, k);
+    });
+}
+// Waits for the head's device, then copies the k candidates of the latest run_topk (values, rows).
+int b200h_head_top_to_host(void* hh, float* vals, int* rows, int k) {
+    return guarded([&] {
+        ShardedHead& h = *static_cast<ShardedHead*>(hh);
+        sync(h.device());
+        Tensor::view(h.device(), const_cast<float*>(h.top_values()), k, 1, Dtype::FP32).copy_to_host(vals);
+        Tensor::view(h.device(), const_cast<std::int32_t*>(h.top_rows()), k, 1, Dtype::INT32).copy_raw_to_host(rows);
+    });
+}
+const void* b200h_head_top_rows(void* hh) { return static_cast<ShardedHead*>(hh)->top_rows(); }
 // Waits for the head's device, then copies the latest full result vector to `dst` (total_rows floats).
 int b200h_head_logits_to_host(void* hh, float* dst) {
     return guarded([&] {

@@ -39,8 +39,10 @@ ShardedHead::ShardedHead(const Tensor& W_shard, int row_offset, int total_rows, 
     if (row_offset < 0 || W_shard.rows <= 0 || row_offset + W_shard.rows > total_rows)
         throw std::runtime_error("brotensor: sharded_head: shard rows do not lie inside the matrix");
     cuda_check(cudaSetDevice(W_shard.device.index), "cudaSetDevice");
-    // exchange memory: [2][total_rows] floats, then `world` arrival words (padded to 256 bytes)
-    const std::size_t bytes = out_bytes() + 256;
+    // exchange memory: [2][total_rows] floats, 256 bytes of arrival words, then the candidate table
+    // [2 parities][8 writing ranks][8 values + 8 rows] and this rank's per-CTA scratch [256][16]
+    // (b200q_gemv_shard_topk)
+    const std::size_t bytes = out_bytes() + 256 + (2 * 8 * 16 + 256 * 16) * sizeof(std::uint32_t);
     cuda_check(cudaMalloc(&local_, bytes), "cudaMalloc(exchange memory)");
     cuda_check(cudaMemset(local_, 0, bytes), "cudaMemset");
     cuda_check(cudaMalloc(&state_, 256), "cudaMalloc(state)");
@@ -67,9 +69,11 @@ void ShardedHead::connect(const std::vector<IpcHandle>& handles) {
     }
     peer_out_.resize(world_);
     peer_flags_.resize(world_);
+    peer_cand_.resize(world_);
     for (int q = 0; q < world_; ++q) {
         peer_out_[q] = peer_base_[q];
         peer_flags_[q] = static_cast<char*>(peer_base_[q]) + out_bytes();
+        peer_cand_[q] = static_cast<char*>(peer_base_[q]) + out_bytes() + 256;
     }
     connected_ = true;
 }
@@ -84,9 +88,15 @@ ShardedHead::~ShardedHead() {
     cudaGetLastError();
 }
 
-void ShardedHead::forward(const Tensor& x, const Tensor* bias_shard) { forward_with(*W_, x, bias_shard); }
+void ShardedHead::forward(const Tensor& x, const Tensor* bias_shard) { run(*W_, x, bias_shard, 0); }
+void ShardedHead::forward_with(const Tensor& W, const Tensor& x, const Tensor* bias_shard) { run(W, x, bias_shard, 0); }
+void ShardedHead::forward_topk(const Tensor& x, int k, const Tensor* bias_shard) { forward_topk_with(*W_, x, k, bias_shard); }
+void ShardedHead::forward_topk_with(const Tensor& W, const Tensor& x, int k, const Tensor* bias_shard) {
+    if (k < 1 || k > 8) throw std::runtime_error("brotensor: sharded_head: k must be 1..8");
+    run(W, x, bias_shard, k);
+}
 
-void ShardedHead::forward_with(const Tensor& W, const Tensor& x, const Tensor* bias_shard) {
+void ShardedHead::run(const Tensor& W, const Tensor& x, const Tensor* bias_shard, int k) {
     if (W.dtype != W_->dtype || W.rows != W_->rows || W.cols != W_->cols || W.device != W_->device)
         throw std::runtime_error("brotensor: sharded_head: weight does not match the shard this head was made for");
     if (!connected_) throw std::runtime_error("brotensor: sharded_head: forward before connect");
@@ -96,12 +106,20 @@ void ShardedHead::forward_with(const Tensor& W, const Tensor& x, const Tensor* b
         throw std::runtime_error("brotensor: sharded_head: bias must hold this shard's rows in x's dtype");
     cuda_check(cudaSetDevice(W_->device.index), "cudaSetDevice");
     const int wfmt = (W.dtype == Dtype::Q6_K && is_repacked(W)) ? B200Q_FMT_Q6_K_R8 : static_cast<int>(W.dtype);
-    const int rc = b200q_gemv_shard(wfmt, W.data, x.data, dt_code(x.dtype),
-                                    bias_shard ? bias_shard->data : nullptr, W_->rows, W_->cols, row_offset_, total_rows_,
-                                    rank_, world_, peer_out_.data(), peer_flags_.data(), state_, cuda_current_stream());
+    const void* b = bias_shard ? bias_shard->data : nullptr;
+    // this rank's results of the candidate form live behind the two state words
+    char* st = static_cast<char*>(state_);
+    const int rc = k == 0 ? b200q_gemv_shard(wfmt, W.data, x.data, dt_code(x.dtype), b, W_->rows, W_->cols, row_offset_, total_rows_, rank_,
+                                             world_, peer_out_.data(), peer_flags_.data(), state_, cuda_current_stream())
+                          : b200q_gemv_shard_topk(wfmt, W.data, x.data, dt_code(x.dtype), b, W_->rows, W_->cols, row_offset_, total_rows_,
+                                                  rank_, world_, peer_out_.data(), peer_flags_.data(), peer_cand_.data(), state_, k,
+                                                  st + 64, st + 128, cuda_current_stream());
     if (rc != B200Q_OK) throw std::runtime_error(std::string("brotensor: sharded_head: ") + b200q_last_error());
     ++calls_;
 }
+
+const float* ShardedHead::top_values() const { return reinterpret_cast<const float*>(static_cast<const char*>(state_) + 64); }
+const std::int32_t* ShardedHead::top_rows() const { return reinterpret_cast<const std::int32_t*>(static_cast<const char*>(state_) + 128); }
 
 const float* ShardedHead::logits() const {
     return static_cast<const float*>(local_) + (calls_ & 1u) * static_cast<std::size_t>(total_rows_);

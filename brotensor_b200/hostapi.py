@@ -55,6 +55,10 @@ def lib() -> C.CDLL:
         L.b200h_head_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.b200h_head_connect.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.b200h_head_run.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]
+        L.b200h_head_run_topk.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        L.b200h_head_top_to_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+        L.b200h_head_top_rows.restype = C.c_void_p
+        L.b200h_head_top_rows.argtypes = [C.c_void_p]
         L.b200h_head_logits.restype = C.c_void_p
         L.b200h_head_logits.argtypes = [C.c_void_p]
         L.b200h_head_calls.restype = C.c_ulonglong
@@ -237,6 +241,19 @@ class ShardedHead:
     def run(self, x_dev_ptr: int, in_features: int, x_dtype: int = 0, weight: "Weight | None" = None) -> None:
         """Enqueues one forward; `weight` substitutes another tensor of the shard's shape."""
         _check(lib().b200h_head_run(self.h, weight.h if weight is not None else None, x_dev_ptr, in_features, x_dtype) == 0)
+
+    def run_topk(self, x_dev_ptr: int, in_features: int, k: int, x_dtype: int = 0, weight: "Weight | None" = None) -> None:
+        """Enqueues one forward of the candidate form: k (value, row) pairs per rank cross the links."""
+        _check(lib().b200h_head_run_topk(self.h, weight.h if weight is not None else None, x_dev_ptr, in_features, x_dtype, k) == 0)
+
+    def top(self, k: int):
+        """Synchronises the device and returns (values, rows) of the latest run_topk, best first."""
+        v, r = np.empty(k, np.float32), np.empty(k, np.int32)
+        _check(lib().b200h_head_top_to_host(self.h, v.ctypes.data, r.ctypes.data, k) == 0)
+        return v, r
+
+    def top_rows_ptr(self) -> int:
+        return int(lib().b200h_head_top_rows(self.h))
 
     def logits_ptr(self) -> int:
         return int(lib().b200h_head_logits(self.h))

@@ -156,17 +156,20 @@ int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void*
 /*
  * Row-sharded decode GEMV for one rank of a multi-GPU LM head (M = 1):
  * this rank owns rows [row_offset, row_offset + rows) of a matrix of total_rows
- * rows; W_shard is the byte range of those rows, x is replicated. The kernel
- * writes every finished row straight into ALL ranks' result vectors through
- * peer pointers (NVLink stores), then sets its arrival word at every rank and
- * waits - at most one second - for all ranks' arrival words at its own, so when
- * the kernel has completed, this rank holds the whole result vector. There is
- * no separate collective.
+ * rows; W_shard is the byte range of those rows, x is replicated. Every CTA of
+ * the kernel writes its finished rows straight into ALL ranks' result vectors
+ * through peer pointers (NVLink stores) and then announces itself at every peer
+ * (one release-add on a counter word); the CTA that finishes last on this rank
+ * waits - at most one second - until every peer's CTAs have been announced
+ * here, so when the kernel has completed, this rank holds the whole result
+ * vector. There is no separate collective.
  *   peer_out[q]   rank q's result memory: TWO vectors of total_rows FP32, used
  *                 alternately; after the n-th call on this state the result is
  *                 vector (n & 1). Must be zero-initialised device memory
  *                 mapped into this process (e.g. CUDA IPC).
- *   peer_flags[q] rank q's arrival words, `world` x uint32, zero-initialised.
+ *   peer_flags[q] rank q's arrival words, 16 x uint32, zero-initialised: word r
+ *                 counts the CTAs rank r has announced over all calls, word 8 + r
+ *                 holds rank r's grid size.
  *   state         this rank's own two uint32 (CTA counter, call counter), zero-
  *                 initialised; its second word is the call count n.
  * All ranks must make the same sequence of calls. A rank that never arrives
@@ -179,10 +182,29 @@ int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void*
  * device are unaffected.
  * brotensor has no sharded form; the closest is its P2P bring-up
  * (src/cuda/register.cu:90-103).
+ *
+ * b200q_gemv_shard_topk is the candidate form for greedy / top-k sampling
+ * (k = 1 .. 8): nothing but k (value, row) pairs per rank crosses the links.
+ * Each rank keeps its shard's logits in its OWN result vector only, selects its
+ * k best, writes them into every rank's candidate table, and after the same
+ * announce-and-wait leaves the k best of all ranks in top_val (k FP32, largest
+ * first) and top_idx (k int32 global rows) on this device. Equal values keep
+ * the lower row, as brotensor's greedy sampling does
+ * (include/brotensor/ops/sampling.h:27-28); top_idx[0] is what sample_logits
+ * returns at temperature 0 on the full logit vector.
+ *   peer_cand[q]  rank q's candidate memory, 17408 bytes, zero-initialised, mapped
+ *                 like peer_out: 2 x 8 x 16 uint32 (parity, writing rank, 8 values +
+ *                 8 rows) that the peers write, then 256 x 16 uint32 of scratch for
+ *                 the rank's own CTAs.
+ * The two forms may be mixed on one set of exchange memory.
  */
 int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
                      int row_offset, int total_rows, int rank, int world, void* const* peer_out,
                      void* const* peer_flags, void* state, void* stream);
+int b200q_gemv_shard_topk(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
+                          int row_offset, int total_rows, int rank, int world, void* const* peer_out,
+                          void* const* peer_flags, void* const* peer_cand, void* state, int k, void* top_val, void* top_idx,
+                          void* stream);
 
 /*
  * Prefill GEMM on the tensor cores, any M >= 1:

@@ -1,12 +1,15 @@
 // Row-sharded LM head over the GPUs of one node, one process per GPU.
 //
 // Each rank owns a contiguous row range of a quantized (out, in) matrix and a block of
-// "exchange memory": two result vectors of `out` floats plus one arrival word per rank.
+// "exchange memory": two result vectors of `out` floats, the arrival words and a small table of
+// sampling candidates.
 // The ranks exchange CUDA IPC handles of these blocks once (the caller moves the 64-byte
 // handles between processes with whatever it has: torch.distributed, MPI, a file), map each
 // other's blocks, and from then on a forward is ONE kernel per rank: the decode GEMV of the
 // shard whose epilogue stores every row into all ranks' result vectors over NVLink and
 // then signals / awaits arrival (b200q_gemv_shard). No collective library on the data path.
+// forward_topk is the form for greedy / top-k sampling: k (value, row) candidates per rank cross
+// the links instead of the logits (b200q_gemv_shard_topk).
 //
 // brotensor has no sharded form of this op; it only brings up peer access
 // (src/cuda/register.cu:90-103).
@@ -42,6 +45,13 @@ public:
     // The same with another weight tensor of the shard's shape, dtype and device (e.g. the
     // benchmark's rotation over weight replicas that keeps the L2 cold).
     void forward_with(const Tensor& W_shard, const Tensor& x, const Tensor* bias_shard = nullptr);
+    // Candidate form, k in 1..8: after the kernel, top_values() / top_rows() hold the k largest logits of
+    // the WHOLE matrix (largest first, equal values: lower row first) and their rows, on every rank;
+    // logits() is then complete for this rank's own rows only. May be mixed with forward().
+    void forward_topk(const Tensor& x, int k, const Tensor* bias_shard = nullptr);
+    void forward_topk_with(const Tensor& W_shard, const Tensor& x, int k, const Tensor* bias_shard = nullptr);
+    const float* top_values() const;  // device pointers, 8 entries each, the first k valid
+    const std::int32_t* top_rows() const;
     // Device pointer to the full result vector of the most recent forward (total_rows floats),
     // valid once that forward's kernel has completed on the stream.
     const float* logits() const;
@@ -54,12 +64,13 @@ private:
     int row_offset_, total_rows_, rank_, world_;
     void* local_ = nullptr;                  // exchange memory of this rank
     std::vector<void*> peer_base_;           // mapped exchange memory of every rank (own = local_)
-    std::vector<void*> peer_out_, peer_flags_;
+    std::vector<void*> peer_out_, peer_flags_, peer_cand_;
     void* state_ = nullptr;
     IpcHandle handle_{};
     std::uint64_t calls_ = 0;
     bool connected_ = false;
     std::size_t out_bytes() const { return 2u * sizeof(float) * static_cast<std::size_t>(total_rows_); }
+    void run(const Tensor& W, const Tensor& x, const Tensor* bias_shard, int k);
 };
 
 }  // namespace brotensor_b200

@@ -2,7 +2,8 @@
 
 Compares, bitwise, the full result vector every rank holds after ShardedHead.run with the
 NCCL all-gather of the plain per-shard GEMV results, over several calls including calls
-issued back to back without a host synchronisation in between."""
+issued back to back without a host synchronisation in between; and the candidate (top-k) form
+against the sorted gathered logits."""
 import os
 import sys
 
@@ -53,6 +54,19 @@ def main():
         ref = shard.all_gather_rows(local_y, N, world, rank, align=16).cpu().numpy()
         if not np.array_equal(got, ref):
             bad += 1
+        # candidate form, mixed with the full form on the same exchange memory: every rank must end up
+        # with the k best rows of the WHOLE matrix (largest first, equal values: lower row first)
+        for k in (1, 5, 8):
+            head.run_topk(xs[k % 6].data_ptr(), K, k, 0)
+            vals, rows = head.top(k)
+            local_y = ops.gemv(fmt, Wd, xs[k % 6], e - b).reshape(-1)
+            full = shard.all_gather_rows(local_y, N, world, rank, align=16).cpu().numpy()
+            order = np.lexsort((np.arange(N), -full))[:k]
+            if not (np.array_equal(rows, order.astype(np.int32)) and np.array_equal(vals, full[order])):
+                bad += 1
+            head.run(xs[0].data_ptr(), K, 0)  # and a full forward after it still delivers every row
+            if not np.array_equal(head.logits(), shard.all_gather_rows(ops.gemv(fmt, Wd, xs[0], e - b).reshape(-1), N, world, rank, align=16).cpu().numpy()):
+                bad += 1
         if ops.device_status() != 0:
             bad += 1
         torch.cuda.synchronize()

