@@ -378,6 +378,7 @@ static int gemv_shard_impl(const char* name, int fmt, const void* W_shard, const
     if (k) {
         if (k < 1 || k > kMaxTopK) return fail(B200Q_ERR_BAD_ARG, "%s: k = %d candidates (1 .. %d)", name, k, kMaxTopK);
         if (!peer_cand || !top_val || !top_idx) return fail(B200Q_ERR_BAD_ARG, "%s: null candidate table or result", name);
+        if (total_rows >= 0xFFFFF) return fail(B200Q_ERR_UNSUPPORTED, "%s: a candidate's row has 20 bits (%d rows)", name, total_rows);
         for (int q = 0; q < world; ++q)
             if (!peer_cand[q]) return fail(B200Q_ERR_BAD_ARG, "%s: null candidate table for rank %d", name, q);
     }

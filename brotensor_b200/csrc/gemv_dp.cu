@@ -554,12 +554,13 @@ __device__ __forceinline__ void block_topk(const float (&v)[C], const int (&ix)[
 // reached calls x that peer's grid size (which the peer's CTA 0 leaves in a second word), so that on
 // return from the kernel the whole result vector of this launch is complete in this rank's memory.
 //
-// Candidate form (sh_topk = k in 1..8): nothing but k (value, index) pairs per rank crosses the links.
-// The last CTA of the rank selects the shard's k best logits, writes them into every peer's
-// candidate table, announces the whole grid at once, waits for the peers likewise, merges the
+// Candidate form (sh_topk = k in 1..8): nothing but eight 8-byte candidates per rank crosses the links.
+// Every CTA selects the k best of its rows; the rank's last CTA selects the k best of those, stores
+// them - value, row and a tag of the call count in one indivisible word each - into every rank's
+// candidate table, polls its own table until every peer's words carry this call's tag, merges the
 // world x k candidates and leaves the k best (value, global row) in sh_top_val / sh_top_idx.
 __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_begin, int row_end, unsigned int sh_epoch,
-                                              unsigned int sh_buf, int tid, int nthreads, uint32_t* scr) {
+                                              unsigned int sh_buf, int tid, int nthreads, uint32_t* scr, float top_v, int top_i, unsigned int cc) {
     // Every consumer warp gets here (aborted ones too).
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     const int k = p.sh_topk;
@@ -582,7 +583,55 @@ __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_beg
         }
     }
     uint32_t* const cta_cand = k > 0 ? p.sh_cand[p.sh_rank] + 2 * kMaxShardRanks * 2 * kMaxTopK : nullptr;  // [CTA][8 values, 8 rows]
-    if (k > 0) {
+    if (k == 1) {
+        // ---- greedy: the threads kept the best of the rows they stored; one 64-bit atomic maximum per CTA
+        // on a key that orders like the candidates (value first, then the LOWER row) makes the rank's
+        // best, and the CTA that finishes last reads it. The key of call c lives in word c & 1 of the
+        // scratch table's last entry; the last CTA clears the other word for the next call.
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, top_v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, top_i, o);
+            if (cand_before(ov, oi, top_v, top_i)) { top_v = ov; top_i = oi; }
+        }
+        if ((tid & 31) == 0) {
+            scr[32 + 2 * (tid >> 5)] = __float_as_uint(top_v);
+            scr[33 + 2 * (tid >> 5)] = (uint32_t)top_i;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        if (tid >= 32) return;
+        const int nwarps = nthreads >> 5;
+        top_v = tid < nwarps ? __uint_as_float(scr[32 + 2 * tid]) : __int_as_float(0xff800000);
+        top_i = tid < nwarps ? (int)scr[33 + 2 * tid] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, top_v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, top_i, o);
+            if (cand_before(ov, oi, top_v, top_i)) { top_v = ov; top_i = oi; }
+        }
+        const unsigned int cc1 = cc;
+        unsigned long long* keys = reinterpret_cast<unsigned long long*>(cta_cand + (size_t)255 * 2 * kMaxTopK);
+        unsigned int last = 0;
+        if (tid == 0) {
+            const uint32_t b = __float_as_uint(top_v), ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+            const unsigned long long key = ((unsigned long long)ord << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)top_i);
+            asm volatile("red.relaxed.gpu.global.max.u64 [%0], %1;" ::"l"(keys + (cc1 & 1u)), "l"(key) : "memory");
+            unsigned int done;
+            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
+            last = done == gridDim.x - 1 ? 1u : 0u;
+            if (last) {
+                unsigned long long best;
+                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(best) : "l"(keys + (cc1 & 1u)) : "memory");
+                keys[(cc1 & 1u) ^ 1u] = 0ull;
+                const uint32_t o2 = (uint32_t)(best >> 32), b2 = (o2 & 0x80000000u) ? (o2 & 0x7FFFFFFFu) : ~o2;
+                scr[64] = b2;
+                scr[64 + kMaxTopK] = 0xFFFFFFFFu - (uint32_t)best;
+            }
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) return;
+        __syncwarp();
+    } else if (k > 0) {
         // ---- this CTA's k best rows, from its own piece of the result vector (at most four per thread in registers)
         const float* own = p.sh_out[p.sh_rank] + (size_t)sh_buf * p.sh_total + p.sh_row_offset + row_begin;
         float v[4];
@@ -597,14 +646,14 @@ __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_beg
         if (tid < 2 * kMaxTopK) cta_cand[(size_t)blockIdx.x * 2 * kMaxTopK + tid] = scr[64 + tid];
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     }
-    if (tid == 0) {
+    if (tid == 0 && k != 1) {
         // the rank's last CTA: acquires the other CTAs' candidates (candidate form) through the gpu-scope counter
         unsigned int done;
         asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
         scr[0] = (done == gridDim.x - 1) ? 1u : 0u;
     }
     if (k == 0 && tid != 0) return;
-    if (k > 0) {
+    if (k > 1) {
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
         if (!scr[0]) return;
         // ---- this rank's k best: the best of the CTAs' candidates (at most eight per thread in registers)
@@ -618,65 +667,62 @@ __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_beg
             ix[u] = in ? (int)__ldcg(cta_cand + (size_t)cta * 2 * kMaxTopK + kMaxTopK + j) : 0x7fffffff;
         }
         block_topk<8>(v, ix, k, scr, tid, nthreads);
-        // into every rank's table (this rank's own copy included: the merge below reads one table)
-        for (int j = tid; j < p.sh_world * 2 * kMaxTopK; j += nthreads) {
-            const int q = j / (2 * kMaxTopK), w = j - q * 2 * kMaxTopK;
-            if ((w & (kMaxTopK - 1)) < k)
-                p.sh_cand[q][((size_t)sh_buf * kMaxShardRanks + p.sh_rank) * 2 * kMaxTopK + w] = scr[64 + w];
-        }
-        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-        if (tid < p.sh_world && tid != p.sh_rank) {
-            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[tid] + kMaxShardRanks + p.sh_rank), "r"(gridDim.x) : "memory");
-            asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.sh_flags[tid] + p.sh_rank), "r"(gridDim.x) : "memory");
-        }
-        if (tid != 0) {
-            if (tid >= 32) return;
-        }
-    } else if (!scr[0]) {
-        return;
+        if (tid >= 32) return;
     }
-    // ---- the rank's last CTA: thread 0 waits for the peers (warp 0 stays for the candidate merge)
-    bool ok = true;
-    if (tid == 0) {
-        p.sh_state[0] = 0;
+    if (k > 0) {
+        // ---- exchange (warp 0 of the rank's last CTA). A candidate is ONE 8-byte word: value bits below, row (20 bits) and a 12-bit tag of
+        // the candidate-form call count above. An aligned 8-byte store is indivisible, so the word
+        // validates itself: the receiver polls the slot until its tag is this call's, and no fence, flag
+        // or counter is on the path - one NVLink store latency. Every call writes all eight slots of its
+        // parity (the unused ones as (-inf, no row)), and a rank can run at most one call ahead of a
+        // peer (it needs the peer's candidates of the call before), so a slot is rewritten with another
+        // tag before its tag could come round again.
+        const unsigned int tag = cc & 0xFFFu, par = cc & 1u;
+        __syncwarp();
+        if (tid < kMaxTopK) {
+            const uint32_t vb = tid < k ? scr[64 + tid] : 0xff800000u;
+            const uint32_t row = tid < k ? (scr[64 + kMaxTopK + tid] & 0xFFFFFu) : 0xFFFFFu;
+            const unsigned long long w = (unsigned long long)vb | ((unsigned long long)(row | (tag << 20)) << 32);
+            for (int q = 0; q < p.sh_world; ++q) {
+                if (q == p.sh_rank) continue;  // its own candidates stay in shared memory
+                unsigned long long* slot = reinterpret_cast<unsigned long long*>(p.sh_cand[q]) + ((size_t)par * kMaxShardRanks + p.sh_rank) * kMaxTopK + tid;
+                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
+            }
+        }
+        // lane l waits for slot l % 8 of rank l / 8 (and of rank l / 8 + 4 with more than four ranks)
+        const unsigned long long* tab = reinterpret_cast<const unsigned long long*>(p.sh_cand[p.sh_rank]) + (size_t)par * kMaxShardRanks * kMaxTopK;
         const uint64_t t0 = global_timer_ns();
         const uint64_t limit = p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs;
-        for (int q = 0; q < p.sh_world && ok; ++q) {
-            if (q == p.sh_rank) continue;
-            for (;;) {
-                unsigned int g, v;
-                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(g) : "l"(p.sh_flags[p.sh_rank] + kMaxShardRanks + q) : "memory");
-                asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
-                if (g != 0 && (int)(v - epoch * g) >= 0) break;
-                if (global_timer_ns() - t0 > limit) {  // a peer never arrived
-                    if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
-                    ok = false;
-                    break;
+        float cv[2];
+        int ci[2];
+        bool ok = true;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int q = (tid >> 3) + 4 * h, j = tid & 7;
+            cv[h] = __int_as_float(0xff800000);
+            ci[h] = 0x7fffffff;
+            if (q == p.sh_rank && j < k) {
+                cv[h] = __uint_as_float(scr[64 + j]);
+                ci[h] = (int)scr[64 + kMaxTopK + j];
+            } else if (q < p.sh_world && j < k) {
+                for (;;) {
+                    unsigned long long w;
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(tab + (size_t)q * kMaxTopK + j) : "memory");
+                    if ((((unsigned int)(w >> 52)) & 0xFFFu) == tag) {
+                        cv[h] = __uint_as_float((uint32_t)w);
+                        const unsigned int row = (unsigned int)(w >> 32) & 0xFFFFFu;
+                        ci[h] = row == 0xFFFFFu ? 0x7fffffff : (int)row;
+                        break;
+                    }
+                    if (global_timer_ns() - t0 > limit) {  // a peer never arrived
+                        if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
+                        ok = false;
+                        break;
+                    }
                 }
             }
         }
-        // acquire side for the peers' rows or candidates (a peer's stores are performed before its
-        // announcement); needed only when there are peers
-        if (p.sh_world > 1) asm volatile("fence.acq_rel.sys;" ::: "memory");
-        scr[1] = ok ? 1u : 0u;
-    }
-    if (k > 0) {
-        __syncwarp();
-        ok = scr[1] != 0;
-        // merge: lane l holds candidate l % 8 of rank l / 8 (two per lane with more than four ranks)
-        const uint32_t* tab = p.sh_cand[p.sh_rank] + (size_t)sh_buf * kMaxShardRanks * 2 * kMaxTopK;
-        float cv[2];
-        int ci[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int c = tid + 32 * h, q = c / kMaxTopK, j = c % kMaxTopK;
-            cv[h] = __int_as_float(0xff800000);
-            ci[h] = 0x7fffffff;
-            if (ok && q < p.sh_world && j < k) {
-                cv[h] = __uint_as_float(__ldcg(tab + (size_t)q * 2 * kMaxTopK + j));
-                ci[h] = (int)__ldcg(tab + (size_t)q * 2 * kMaxTopK + kMaxTopK + j);
-            }
-        }
+        ok = __all_sync(0xffffffffu, ok);
         float pv = __int_as_float(0x7f800000);
         int pi = -1;
         for (int r = 0; r < k; ++r) {
@@ -698,8 +744,41 @@ __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_beg
                 p.sh_top_idx[r] = bi;
             }
         }
+        if (tid == 0) {
+            p.sh_state[0] = 0;
+            *(volatile unsigned int*)&p.sh_state[2] = cc;
+            *(volatile unsigned int*)&p.sh_state[1] = epoch;
+        }
+        return;
+    } else if (!scr[0]) {
+        return;
     }
-    if (tid == 0) *(volatile unsigned int*)&p.sh_state[1] = epoch;
+    // ---- full-logits form, the rank's last CTA (thread 0): wait for the peers' CTAs. The counters count
+    // full-form calls only (the candidate form does not touch them).
+    const unsigned int fc = *(volatile unsigned int*)&p.sh_state[3] + 1u;
+    p.sh_state[0] = 0;
+    const uint64_t t0 = global_timer_ns();
+    const uint64_t limit = p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs;
+    bool ok = true;
+    for (int q = 0; q < p.sh_world && ok; ++q) {
+        if (q == p.sh_rank) continue;
+        for (;;) {
+            unsigned int g, v;
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(g) : "l"(p.sh_flags[p.sh_rank] + kMaxShardRanks + q) : "memory");
+            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
+            if (g != 0 && (int)(v - fc * g) >= 0) break;
+            if (global_timer_ns() - t0 > limit) {  // a peer never arrived
+                if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
+                ok = false;
+                break;
+            }
+        }
+    }
+    // acquire side for the peers' rows (a peer's stores are performed before its announcement);
+    // needed only when there are peers
+    if (p.sh_world > 1) asm volatile("fence.acq_rel.sys;" ::: "memory");
+    *(volatile unsigned int*)&p.sh_state[3] = fc;
+    *(volatile unsigned int*)&p.sh_state[1] = epoch;
 }
 
 // NG independent pipelines inside one CTA: pipeline g has eight consumer warps, its own
@@ -858,6 +937,8 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     // launch counter of the sharded form: stable while this launch runs (only its last CTA bumps it)
     const unsigned int sh_epoch = ((EXT & kExtShard) && p.sh_world > 0) ? *(volatile unsigned int*)&p.sh_state[1] : 0u;
     const unsigned int sh_buf = (sh_epoch + 1u) & 1u;
+    // calls of the candidate form so far, this one included (likewise stable while the launch runs)
+    const unsigned int sh_cc = ((EXT & kExtShard) && p.sh_world > 0 && p.sh_topk > 0) ? *(volatile unsigned int*)&p.sh_state[2] + 1u : 0u;
     if ((EXT & kExtNorm) && MT == 1 && p.norm_gamma) stage_x16_norm<FMT>(p, sbase, tid, kConsumers * 32, norm_red);
     else stage_x16<FMT, (EXT & kExtLean) != 0>(p, sbase, tid, kConsumers * 32);
     TRACE_STAMP(tid == 0, 3);
@@ -873,6 +954,9 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
     // Deferred reduction (see the end of the tile loop): sums of the up to three tiles before the current one.
     constexpr bool kDefer = MT == 1 && RP == 1 && !(EXT & kExtSwiglu);
     float hold[3][2] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+    // greedy form of the sharded head: the best (value, global row) among the rows this thread has stored
+    float top_v = __int_as_float(0xff800000);
+    int top_i = 0x7fffffff;
     int held = 0;
     float acc[RP][2][MT];
 #pragma unroll
@@ -969,7 +1053,10 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                             else if (p.x_dtype == B200Q_DT_F16) s += __half2float(static_cast<const __half*>(t2.bias)[n]);
                             else s += __bfloat162float(static_cast<const __nv_bfloat16*>(t2.bias)[n]);
                         }
-                        if ((EXT & kExtShard) && p.sh_world > 0) p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
+                        if ((EXT & kExtShard) && p.sh_world > 0) {
+                            p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
+                            if (cand_before(s, p.sh_row_offset + n, top_v, top_i)) { top_v = s; top_i = p.sh_row_offset + n; }
+                        }
                         else if (kLean || p.y_dtype == B200Q_DT_F32) static_cast<float*>(t2.Y)[n] = s;
                         else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(t2.Y)[n] = __float2half_rn(s);
                         else static_cast<__nv_bfloat16*>(t2.Y)[n] = __float2bfloat16_rn(s);
@@ -1017,6 +1104,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
                         // sharded output: into this rank's own result vector first (which of the two
                         // vectors is this launch's parity); the CTA forwards its rows to the peers below
                         p.sh_out[p.sh_rank][(size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + n)] = s;
+                        if (m == 0 && cand_before(s, p.sh_row_offset + n, top_v, top_i)) { top_v = s; top_i = p.sh_row_offset + n; }
                     } else if (p.y_dtype == B200Q_DT_F32) static_cast<float*>(tr.Y)[o] = s;
                     else if (p.y_dtype == B200Q_DT_F16) static_cast<__half*>(tr.Y)[o] = __float2half_rn(s);
                     else static_cast<__nv_bfloat16*>(tr.Y)[o] = __float2bfloat16_rn(s);
@@ -1025,7 +1113,7 @@ __global__ void __launch_bounds__((kConsumerWarps + 1) * NG * 32, 1) gemv_dp_ker
         }
     }
     TRACE_STAMP((tid & 31) == 0, 5 + (warp >= kConsumerWarps ? 1 : 0));  // last writer of each pipeline wins: about its end
-    if ((EXT & kExtShard) && p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32, reinterpret_cast<uint32_t*>(smem_raw + (sbase - smem_u32(smem_raw))));
+    if ((EXT & kExtShard) && p.sh_world > 0) shard_publish(p, row_begin, row_end, sh_epoch, sh_buf, tid, kConsumers * 32, reinterpret_cast<uint32_t*>(smem_raw + (sbase - smem_u32(smem_raw))), top_v, top_i, sh_cc);
 }
 
 // ---- host side ------------------------------------------------------------------------

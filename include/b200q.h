@@ -170,8 +170,9 @@ int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void*
  *   peer_flags[q] rank q's arrival words, 16 x uint32, zero-initialised: word r
  *                 counts the CTAs rank r has announced over all calls, word 8 + r
  *                 holds rank r's grid size.
- *   state         this rank's own two uint32 (CTA counter, call counter), zero-
- *                 initialised; its second word is the call count n.
+ *   state         this rank's own four uint32 (CTA counter, calls of both forms,
+ *                 calls of the candidate form, calls of this form), zero-initialised;
+ *                 its second word is the call count n.
  * All ranks must make the same sequence of calls. A rank that never arrives
  * makes the others report B200Q_ERR_TIMEOUT through b200q_device_status(): the
  * kernel gives up after the wait limit (one second, or the "wait_limit_us"
@@ -184,18 +185,21 @@ int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void*
  * (src/cuda/register.cu:90-103).
  *
  * b200q_gemv_shard_topk is the candidate form for greedy / top-k sampling
- * (k = 1 .. 8): nothing but k (value, row) pairs per rank crosses the links.
- * Each rank keeps its shard's logits in its OWN result vector only, selects its
- * k best, writes them into every rank's candidate table, and after the same
- * announce-and-wait leaves the k best of all ranks in top_val (k FP32, largest
+ * (k = 1 .. 8, fewer than 1048575 rows): nothing but eight 8-byte candidates per
+ * rank crosses the links. Each rank keeps its shard's logits in its OWN result
+ * vector only, selects its k best and stores them - value, row and a tag of the
+ * call count in one indivisible word each - into every rank's candidate table;
+ * it then polls its own table until every peer's words carry this call's tag
+ * (no fence, flag or counter on the path; the same wait limit and timeout
+ * status) and leaves the k best of all ranks in top_val (k FP32, largest
  * first) and top_idx (k int32 global rows) on this device. Equal values keep
  * the lower row, as brotensor's greedy sampling does
  * (include/brotensor/ops/sampling.h:27-28); top_idx[0] is what sample_logits
  * returns at temperature 0 on the full logit vector.
  *   peer_cand[q]  rank q's candidate memory, 17408 bytes, zero-initialised, mapped
- *                 like peer_out: 2 x 8 x 16 uint32 (parity, writing rank, 8 values +
- *                 8 rows) that the peers write, then 256 x 16 uint32 of scratch for
- *                 the rank's own CTAs.
+ *                 like peer_out: 2 x 8 x 8 uint64 (parity of the call, writing rank,
+ *                 candidate) that the peers write, then 256 x 16 uint32 of scratch
+ *                 for the rank's own CTAs.
  * The two forms may be mixed on one set of exchange memory.
  */
 int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,

@@ -25,7 +25,7 @@ def test_peer_wait_runs_out_and_the_device_stays_usable(cpu_oracle):
     # that nobody ever signals, so rank 0's wait for rank 1 cannot complete
     outs = [torch.zeros(2 * total, dtype=torch.float32, device="cuda") for _ in range(world)]
     flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(world)]  # 8 counters + 8 grid sizes
-    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    state = torch.zeros(4, dtype=torch.int32, device="cuda")
     po = (C.c_void_p * world)(*[t.data_ptr() for t in outs])
     pf = (C.c_void_p * world)(*[t.data_ptr() for t in flags])
     assert ops.device_status() == 0
