@@ -37,9 +37,8 @@ SYMBOLS = [
     ("b200q_gemv_multi_rmsnorm", _i, [_i, _i, C.POINTER(_vp), C.POINTER(_i), C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _vp, C.c_float, _i, _i, _vp]),
     ("b200q_gemv_swiglu", _i, [_i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp]),
     ("b200q_gemv_multi", _i, [_i, _i, C.POINTER(_vp), C.POINTER(_i), C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _i, _i, _vp]),
-    ("b200q_gemv_shard", _i, [_i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), _vp, _vp]),
-    ("b200q_gemv_shard_topk", _i, [_i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _vp,
-                               _vp, _vp]),
+    ("b200q_gemv_shard", _i, [_i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), _vp, _vp]),
+    ("b200q_gemv_shard_topk", _i, [_i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(_vp), C.POINTER(_vp), _vp, _i, _vp, _vp, _vp]),
     ("b200q_gemm_workspace_bytes", _sz, [_i, _i, _i, _i, _i]),
     ("b200q_gemm", _i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp, _sz, _vp]),
     ("b200q_gemm_static_max_bytes", _sz, []),

@@ -362,8 +362,7 @@ int b200q_gemv_multi_rmsnorm(int fmt, int n, const void* const* W, const int* N,
 
 static int gemv_shard_impl(const char* name, int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows,
                            int K, int row_offset, int total_rows, int rank, int world, void* const* peer_out,
-                           void* const* peer_flags, void* const* peer_cand, void* state, int k, void* top_val, void* top_idx,
-                           void* stream) {
+                           void* const* peer_cand, void* state, int k, void* top_val, void* top_idx, void* stream) {
     if (b200q_block_elems(fmt) && !streaming_fmt(fmt)) return fail(B200Q_ERR_UNSUPPORTED, "%s: block format %d has no sharded form", name, fmt);
     static float dummy_y;  // check_linear_args wants a non-null result pointer; the sharded form has none
     if (int rc = check_linear_args(name, fmt, W_shard, x, x_dtype, &dummy_y, B200Q_DT_F32, 1, rows, K)) return rc;
@@ -371,9 +370,9 @@ static int gemv_shard_impl(const char* name, int fmt, const void* W_shard, const
         return fail(B200Q_ERR_BAD_ARG, "%s: rank %d of %d (at most %d ranks)", name, rank, world, kMaxShardRanks);
     if (row_offset < 0 || total_rows <= 0 || (long long)row_offset + rows > total_rows)
         return fail(B200Q_ERR_BAD_ARG, "%s: rows [%d, %d) do not lie in [0, %d)", name, row_offset, row_offset + rows, total_rows);
-    if (!peer_out || !peer_flags || !state) return fail(B200Q_ERR_BAD_ARG, "%s: null peer table or state", name);
+    if (!peer_out || !state) return fail(B200Q_ERR_BAD_ARG, "%s: null peer table or state", name);
     for (int q = 0; q < world; ++q)
-        if (!peer_out[q] || !peer_flags[q]) return fail(B200Q_ERR_BAD_ARG, "%s: null pointer for rank %d", name, q);
+        if (!peer_out[q]) return fail(B200Q_ERR_BAD_ARG, "%s: null pointer for rank %d", name, q);
     if (rows == 0) return fail(B200Q_ERR_UNSUPPORTED, "%s: an empty shard cannot signal its arrival", name);
     if (k) {
         if (k < 1 || k > kMaxTopK) return fail(B200Q_ERR_BAD_ARG, "%s: k = %d candidates (1 .. %d)", name, k, kMaxTopK);
@@ -390,7 +389,6 @@ static int gemv_shard_impl(const char* name, int fmt, const void* W_shard, const
     sh.row_offset = row_offset;
     sh.total_rows = total_rows;
     sh.out = reinterpret_cast<float* const*>(peer_out);
-    sh.flags = reinterpret_cast<unsigned int* const*>(peer_flags);
     sh.state = static_cast<unsigned int*>(state);
     sh.topk = k;
     sh.cand = reinterpret_cast<uint32_t* const*>(peer_cand);
@@ -406,19 +404,17 @@ static int gemv_shard_impl(const char* name, int fmt, const void* W_shard, const
 }
 
 int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
-                     int row_offset, int total_rows, int rank, int world, void* const* peer_out,
-                     void* const* peer_flags, void* state, void* stream) {
+                     int row_offset, int total_rows, int rank, int world, void* const* peer_out, void* state, void* stream) {
     return gemv_shard_impl("gemv_shard", fmt, W_shard, x, x_dtype, bias_shard, rows, K, row_offset, total_rows, rank, world, peer_out,
-                           peer_flags, nullptr, state, 0, nullptr, nullptr, stream);
+                           nullptr, state, 0, nullptr, nullptr, stream);
 }
 
 int b200q_gemv_shard_topk(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
                           int row_offset, int total_rows, int rank, int world, void* const* peer_out,
-                          void* const* peer_flags, void* const* peer_cand, void* state, int k, void* top_val, void* top_idx,
-                          void* stream) {
+                          void* const* peer_cand, void* state, int k, void* top_val, void* top_idx, void* stream) {
     if (k < 1) return fail(B200Q_ERR_BAD_ARG, "gemv_shard_topk: k = %d candidates (1 .. %d)", k, kMaxTopK);
     return gemv_shard_impl("gemv_shard_topk", fmt, W_shard, x, x_dtype, bias_shard, rows, K, row_offset, total_rows, rank, world,
-                           peer_out, peer_flags, peer_cand, state, k, top_val, top_idx, stream);
+                           peer_out, peer_cand, state, k, top_val, top_idx, stream);
 }
 
 size_t b200q_gemm_workspace_bytes(int fmt, int x_dtype, int M, int N, int K) {

@@ -71,13 +71,13 @@ void set_error(const char* fmt, ...);
 int fail(int code, const char* fmt, ...);
 
 constexpr int kMaxShardRanks = 8;
-constexpr int kMaxTopK = 8;  // candidates per rank in the candidate form of the sharded head
+constexpr int kMaxTopK = 8;      // candidates per CTA in the candidate form of the sharded head
+constexpr int kShardSlots = 256;  // CTA slots per rank in a candidate table (an upper bound of the grid)
 constexpr int kMaxSegments = 4;  // weight matrices one grouped GEMV launch can take
 // Host-side description of a row-sharded GEMV output (StreamParams::sh_* on the device side).
 struct ShardOut {
     int world, rank, row_offset, total_rows;
     float* const* out;
-    unsigned int* const* flags;
     unsigned int* state;
     // candidate form: k in 1..kMaxTopK, every rank's candidate table, this rank's results (else 0 / null)
     int topk = 0;

@@ -543,51 +543,89 @@ __device__ __forceinline__ void block_topk(const float (&v)[C], const int (&ix)[
 }
 
 // Sharded epilogue, run by all `nthreads` consumer threads of a CTA (thread ids 0 .. nthreads-1) after
-// they have stored the CTA's rows [row_begin, row_end) into this rank's result vector. `scr` is at
-// least 1 KB of shared memory that nothing else uses any more.
+// they have stored the CTA's rows [row_begin, row_end) into this rank's result vector. `scr` is
+// shared memory that nothing else uses any more (1 KB; 8 * 2048 * k bytes more in the candidate form
+// with k > 1).
 //
-// Full-logits form (sh_topk == 0): the CTA forwards its rows to every peer's result vector and then
-// publishes ITSELF at every peer: one red.release.sys.add of 1 on the peer's counter word for this
-// rank (the release orders the CTA's forwarded rows, seen through the CTA barrier, before it). Nothing
-// waits for this rank's slowest CTA before the fast ones are announced. The CTA that finishes last on
-// this rank (a gpu-scope counter) waits - bounded - until every peer's counter at this rank has
-// reached calls x that peer's grid size (which the peer's CTA 0 leaves in a second word), so that on
-// return from the kernel the whole result vector of this launch is complete in this rank's memory.
+// Nothing on the exchange path is a fence, a flag or a counter: every word that crosses the links
+// validates itself. An aligned 8-byte store is indivisible, so a word that carries its payload in
+// one half and the call's number in the other is either the old word or the new one, and the
+// receiver simply polls it until the number is this call's (bounded; a word that never comes sets
+// the timeout status). A rank can run at most one call ahead of a peer - it needs the peer's words
+// of the call before - so two buffers, used alternately, are enough.
 //
-// Candidate form (sh_topk = k in 1..8): nothing but eight 8-byte candidates per rank crosses the links.
-// Every CTA selects the k best of its rows; the rank's last CTA selects the k best of those, stores
-// them - value, row and a tag of the call count in one indivisible word each - into every rank's
-// candidate table, polls its own table until every peer's words carry this call's tag, merges the
-// world x k candidates and leaves the k best (value, global row) in sh_top_val / sh_top_idx.
+// Full-logits form (sh_topk == 0): the CTA sends its rows to every peer as (value, call number) words
+// - coalesced, 256 bytes per warp and peer - and then receives ITS SLICE of the whole vector: it
+// polls the words the peers have sent for rows [cta, cta + 1) * ceil(total / grid) and writes the
+// values into this rank's result vector. When every CTA has done so the kernel - and with it the
+// vector - is complete; the CTA that finishes last (a gpu-scope counter, off the data path) only
+// advances the call numbers.
+//
+// Candidate form (sh_topk = k in 1..8): every CTA of every rank reduces its rows to k candidates and
+// stores them - value, row (20 bits) and a 12-bit tag of the candidate-form call count per word - into
+// EVERY rank's table, which has 256 slots per rank: a CTA also fills the slots of the CTA numbers its
+// grid does not have ((-inf, no row)), so a receiver needs to know nobody's grid. CTA 0 of each
+// rank polls the 8 x 256 x k words, takes the k best in the candidates' order and leaves them in
+// sh_top_val / sh_top_idx; no CTA waits for another one of its own rank, and there is no atomic.
 __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_begin, int row_end, unsigned int sh_epoch,
                                               unsigned int sh_buf, int tid, int nthreads, uint32_t* scr, float top_v, int top_i, unsigned int cc) {
     // Every consumer warp gets here (aborted ones too).
     asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     const int k = p.sh_topk;
     const unsigned int epoch = sh_epoch + 1u;
-    if (k == 0 && p.sh_world > 1) {
-        // This CTA's rows are one contiguous piece of the result vector: forward it to every peer
-        // with coalesced stores (a warp writes 128 consecutive bytes per peer) instead of one
-        // 4-byte NVLink write per row and peer.
-        const size_t base = (size_t)sh_buf * p.sh_total + (size_t)(p.sh_row_offset + row_begin);
-        const float* own = p.sh_out[p.sh_rank] + base;
-        for (int i = tid; i < row_end - row_begin; i += nthreads) {
-            const float v = __ldcg(own + i);
-            for (int q = 0; q < p.sh_world; ++q)
-                if (q != p.sh_rank) p.sh_out[q][base + i] = v;
+    const uint64_t limit = p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs;
+    if (k == 0) {
+        if (p.sh_world > 1) {
+            // transfer words of rank q: behind its two result vectors, [2][sh_total] x 8 bytes
+            const size_t at = (size_t)sh_buf * p.sh_total;
+            const float* own = p.sh_out[p.sh_rank] + at + (size_t)(p.sh_row_offset + row_begin);
+            for (int i = tid; i < row_end - row_begin; i += nthreads) {
+                const unsigned long long w = (unsigned long long)__float_as_uint(__ldcg(own + i)) | ((unsigned long long)epoch << 32);
+                for (int q = 0; q < p.sh_world; ++q)
+                    if (q != p.sh_rank) {
+                        unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.sh_out[q] + 2 * (size_t)p.sh_total) + at + (size_t)(p.sh_row_offset + row_begin + i);
+                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+                    }
+            }
+            // receive this CTA's slice (rows of this rank's own shard are in place already)
+            const int slice = (p.sh_total + (int)gridDim.x - 1) / (int)gridDim.x;
+            const int r1 = min(p.sh_total, ((int)blockIdx.x + 1) * slice);
+            const unsigned long long* src = reinterpret_cast<const unsigned long long*>(p.sh_out[p.sh_rank] + 2 * (size_t)p.sh_total) + at;
+            float* dst = p.sh_out[p.sh_rank] + at;
+            const uint64_t t0 = global_timer_ns();
+            for (int r = (int)blockIdx.x * slice + tid; r < r1; r += nthreads) {
+                if (r >= p.sh_row_offset && r < p.sh_row_offset + p.N) continue;
+                for (;;) {
+                    unsigned long long w;
+                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src + r) : "memory");
+                    if ((unsigned int)(w >> 32) == epoch) {
+                        dst[r] = __uint_as_float((uint32_t)w);
+                        break;
+                    }
+                    if (global_timer_ns() - t0 > limit) {  // a peer's rows never came
+                        if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
+                        break;
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
         }
-        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-        if (tid < p.sh_world && tid != p.sh_rank) {  // one thread per peer
-            if (blockIdx.x == 0) asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sh_flags[tid] + kMaxShardRanks + p.sh_rank), "r"(gridDim.x) : "memory");
-            asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(p.sh_flags[tid] + p.sh_rank) : "memory");
+        if (tid == 0) {
+            unsigned int done;
+            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
+            if (done == gridDim.x - 1) {
+                p.sh_state[0] = 0;
+                *(volatile unsigned int*)&p.sh_state[1] = epoch;
+            }
         }
+        return;
     }
-    uint32_t* const cta_cand = k > 0 ? p.sh_cand[p.sh_rank] + 2 * kMaxShardRanks * 2 * kMaxTopK : nullptr;  // [CTA][8 values, 8 rows]
+
+    // ---- candidate form
+    TRACE_STAMP(tid == 0, 9);
+    const unsigned int tag = cc & 0xFFFu, par = cc & 1u;
     if (k == 1) {
-        // ---- greedy: the threads kept the best of the rows they stored; one 64-bit atomic maximum per CTA
-        // on a key that orders like the candidates (value first, then the LOWER row) makes the rank's
-        // best, and the CTA that finishes last reads it. The key of call c lives in word c & 1 of the
-        // scratch table's last entry; the last CTA clears the other word for the next call.
+        // the threads kept the best of the rows they stored: reduce over the CTA
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, top_v, o);
@@ -599,40 +637,24 @@ __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_beg
             scr[33 + 2 * (tid >> 5)] = (uint32_t)top_i;
         }
         asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-        if (tid >= 32) return;
-        const int nwarps = nthreads >> 5;
-        top_v = tid < nwarps ? __uint_as_float(scr[32 + 2 * tid]) : __int_as_float(0xff800000);
-        top_i = tid < nwarps ? (int)scr[33 + 2 * tid] : 0x7fffffff;
+        if (tid < 32) {
+            const int nwarps = nthreads >> 5;
+            top_v = tid < nwarps ? __uint_as_float(scr[32 + 2 * tid]) : __int_as_float(0xff800000);
+            top_i = tid < nwarps ? (int)scr[33 + 2 * tid] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, top_v, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, top_i, o);
-            if (cand_before(ov, oi, top_v, top_i)) { top_v = ov; top_i = oi; }
-        }
-        const unsigned int cc1 = cc;
-        unsigned long long* keys = reinterpret_cast<unsigned long long*>(cta_cand + (size_t)255 * 2 * kMaxTopK);
-        unsigned int last = 0;
-        if (tid == 0) {
-            const uint32_t b = __float_as_uint(top_v), ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-            const unsigned long long key = ((unsigned long long)ord << 32) | (unsigned long long)(0xFFFFFFFFu - (uint32_t)top_i);
-            asm volatile("red.relaxed.gpu.global.max.u64 [%0], %1;" ::"l"(keys + (cc1 & 1u)), "l"(key) : "memory");
-            unsigned int done;
-            asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
-            last = done == gridDim.x - 1 ? 1u : 0u;
-            if (last) {
-                unsigned long long best;
-                asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(best) : "l"(keys + (cc1 & 1u)) : "memory");
-                keys[(cc1 & 1u) ^ 1u] = 0ull;
-                const uint32_t o2 = (uint32_t)(best >> 32), b2 = (o2 & 0x80000000u) ? (o2 & 0x7FFFFFFFu) : ~o2;
-                scr[64] = b2;
-                scr[64 + kMaxTopK] = 0xFFFFFFFFu - (uint32_t)best;
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, top_v, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, top_i, o);
+                if (cand_before(ov, oi, top_v, top_i)) { top_v = ov; top_i = oi; }
+            }
+            if (tid == 0) {
+                scr[64] = __float_as_uint(top_v);
+                scr[64 + kMaxTopK] = (uint32_t)top_i;
             }
         }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (!last) return;
-        __syncwarp();
-    } else if (k > 0) {
-        // ---- this CTA's k best rows, from its own piece of the result vector (at most four per thread in registers)
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    } else {
+        // the k best of this CTA's rows, from its piece of the result vector (at most four per thread in registers)
         const float* own = p.sh_out[p.sh_rank] + (size_t)sh_buf * p.sh_total + p.sh_row_offset + row_begin;
         float v[4];
         int ix[4];
@@ -643,142 +665,108 @@ __device__ __forceinline__ void shard_publish(const StreamParams& p, int row_beg
             ix[u] = i < row_end - row_begin ? p.sh_row_offset + row_begin + i : 0x7fffffff;
         }
         block_topk<4>(v, ix, k, scr, tid, nthreads);
-        if (tid < 2 * kMaxTopK) cta_cand[(size_t)blockIdx.x * 2 * kMaxTopK + tid] = scr[64 + tid];
-        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
     }
-    if (tid == 0 && k != 1) {
-        // the rank's last CTA: acquires the other CTAs' candidates (candidate form) through the gpu-scope counter
-        unsigned int done;
-        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(done) : "l"(p.sh_state) : "memory");
-        scr[0] = (done == gridDim.x - 1) ? 1u : 0u;
+    // ---- send: candidate j of CTA slot c for rank q at [par][rank][c][j]; this CTA's own slot and the
+    // slots of the CTA numbers its grid does not have
+    for (int t = tid; t < p.sh_world * kMaxTopK; t += nthreads) {
+        const int q = t / kMaxTopK, j = t % kMaxTopK;  // every slot is rewritten in every call, used or not
+        unsigned long long* tab = reinterpret_cast<unsigned long long*>(p.sh_cand[q]) + ((size_t)par * kMaxShardRanks + p.sh_rank) * kShardSlots * kMaxTopK;
+        const unsigned long long none = 0xff800000ull | ((unsigned long long)(0xFFFFFu | (tag << 20)) << 32);
+        const uint32_t row = j < k ? scr[64 + kMaxTopK + j] : 0xFFFFFu;
+        const unsigned long long w = j < k ? (unsigned long long)scr[64 + j] | ((unsigned long long)((row >= 0xFFFFFu ? 0xFFFFFu : row) | (tag << 20)) << 32) : none;
+        for (int c = (int)blockIdx.x; c < kShardSlots; c += (int)gridDim.x) {
+            unsigned long long* dst = tab + (size_t)c * kMaxTopK + j;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(c == (int)blockIdx.x ? w : none) : "memory");
+        }
     }
-    if (k == 0 && tid != 0) return;
-    if (k > 1) {
-        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
-        if (!scr[0]) return;
-        // ---- this rank's k best: the best of the CTAs' candidates (at most eight per thread in registers)
-        float v[8];
-        int ix[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            const int c = tid + u * nthreads, cta = c / kMaxTopK, j = c % kMaxTopK;
-            const bool in = cta < (int)gridDim.x && j < k;
-            v[u] = in ? __uint_as_float(__ldcg(cta_cand + (size_t)cta * 2 * kMaxTopK + j)) : __int_as_float(0xff800000);
-            ix[u] = in ? (int)__ldcg(cta_cand + (size_t)cta * 2 * kMaxTopK + kMaxTopK + j) : 0x7fffffff;
-        }
-        block_topk<8>(v, ix, k, scr, tid, nthreads);
-        if (tid >= 32) return;
-    }
-    if (k > 0) {
-        // ---- exchange (warp 0 of the rank's last CTA). A candidate is ONE 8-byte word: value bits below, row (20 bits) and a 12-bit tag of
-        // the candidate-form call count above. An aligned 8-byte store is indivisible, so the word
-        // validates itself: the receiver polls the slot until its tag is this call's, and no fence, flag
-        // or counter is on the path - one NVLink store latency. Every call writes all eight slots of its
-        // parity (the unused ones as (-inf, no row)), and a rank can run at most one call ahead of a
-        // peer (it needs the peer's candidates of the call before), so a slot is rewritten with another
-        // tag before its tag could come round again.
-        const unsigned int tag = cc & 0xFFFu, par = cc & 1u;
-        __syncwarp();
-        if (tid < kMaxTopK) {
-            const uint32_t vb = tid < k ? scr[64 + tid] : 0xff800000u;
-            const uint32_t row = tid < k ? (scr[64 + kMaxTopK + tid] & 0xFFFFFu) : 0xFFFFFu;
-            const unsigned long long w = (unsigned long long)vb | ((unsigned long long)(row | (tag << 20)) << 32);
-            for (int q = 0; q < p.sh_world; ++q) {
-                if (q == p.sh_rank) continue;  // its own candidates stay in shared memory
-                unsigned long long* slot = reinterpret_cast<unsigned long long*>(p.sh_cand[q]) + ((size_t)par * kMaxShardRanks + p.sh_rank) * kMaxTopK + tid;
-                asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(slot), "l"(w) : "memory");
-            }
-        }
-        // lane l waits for slot l % 8 of rank l / 8 (and of rank l / 8 + 4 with more than four ranks)
-        const unsigned long long* tab = reinterpret_cast<const unsigned long long*>(p.sh_cand[p.sh_rank]) + (size_t)par * kMaxShardRanks * kMaxTopK;
-        const uint64_t t0 = global_timer_ns();
-        const uint64_t limit = p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs;
-        float cv[2];
-        int ci[2];
-        bool ok = true;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int q = (tid >> 3) + 4 * h, j = tid & 7;
-            cv[h] = __int_as_float(0xff800000);
-            ci[h] = 0x7fffffff;
-            if (q == p.sh_rank && j < k) {
-                cv[h] = __uint_as_float(scr[64 + j]);
-                ci[h] = (int)scr[64 + kMaxTopK + j];
-            } else if (q < p.sh_world && j < k) {
-                for (;;) {
-                    unsigned long long w;
-                    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(tab + (size_t)q * kMaxTopK + j) : "memory");
-                    if ((((unsigned int)(w >> 52)) & 0xFFFu) == tag) {
-                        cv[h] = __uint_as_float((uint32_t)w);
-                        const unsigned int row = (unsigned int)(w >> 32) & 0xFFFFFu;
-                        ci[h] = row == 0xFFFFFu ? 0x7fffffff : (int)row;
-                        break;
-                    }
-                    if (global_timer_ns() - t0 > limit) {  // a peer never arrived
-                        if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
-                        ok = false;
-                        break;
-                    }
-                }
-            }
-        }
-        ok = __all_sync(0xffffffffu, ok);
-        float pv = __int_as_float(0x7f800000);
-        int pi = -1;
-        for (int r = 0; r < k; ++r) {
-            float bv = __int_as_float(0xff800000);
-            int bi = 0x7fffffff;
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-                if (cand_before(pv, pi, cv[h], ci[h]) && cand_before(cv[h], ci[h], bv, bi)) { bv = cv[h]; bi = ci[h]; }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (cand_before(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-            }
-            pv = bv;
-            pi = bi;
-            if (tid == 0 && ok) {
-                p.sh_top_val[r] = bv;
-                p.sh_top_idx[r] = bi;
-            }
-        }
-        if (tid == 0) {
-            p.sh_state[0] = 0;
-            *(volatile unsigned int*)&p.sh_state[2] = cc;
-            *(volatile unsigned int*)&p.sh_state[1] = epoch;
-        }
-        return;
-    } else if (!scr[0]) {
-        return;
-    }
-    // ---- full-logits form, the rank's last CTA (thread 0): wait for the peers' CTAs. The counters count
-    // full-form calls only (the candidate form does not touch them).
-    const unsigned int fc = *(volatile unsigned int*)&p.sh_state[3] + 1u;
-    p.sh_state[0] = 0;
+    TRACE_STAMP(tid == 0, 10);
+    if (blockIdx.x != 0) return;
+    // ---- CTA 0 receives: all ranks' slots, candidates j < k
+    const unsigned long long* tab = reinterpret_cast<const unsigned long long*>(p.sh_cand[p.sh_rank]) + (size_t)par * kMaxShardRanks * kShardSlots * kMaxTopK;
+    const int n_words = p.sh_world * kShardSlots * k;
     const uint64_t t0 = global_timer_ns();
-    const uint64_t limit = p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : kWaitLimitNs;
     bool ok = true;
-    for (int q = 0; q < p.sh_world && ok; ++q) {
-        if (q == p.sh_rank) continue;
+    float bv = __int_as_float(0xff800000);
+    int bi = 0x7fffffff;
+    uint2* const pool = reinterpret_cast<uint2*>(scr + 256);  // k > 1: every received candidate, for the k passes below
+    for (int t = tid; t < n_words; t += nthreads) {
+        const int q = t / (kShardSlots * k), rem = t - q * kShardSlots * k, c = rem / k, j = rem - c * k;
+        const unsigned long long* src = tab + ((size_t)q * kShardSlots + c) * kMaxTopK + j;
+        float v = __int_as_float(0xff800000);
+        int row = 0x7fffffff;
         for (;;) {
-            unsigned int g, v;
-            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(g) : "l"(p.sh_flags[p.sh_rank] + kMaxShardRanks + q) : "memory");
-            asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.sh_flags[p.sh_rank] + q) : "memory");
-            if (g != 0 && (int)(v - fc * g) >= 0) break;
-            if (global_timer_ns() - t0 > limit) {  // a peer never arrived
+            unsigned long long w;
+            asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+            if ((((unsigned int)(w >> 52)) & 0xFFFu) == tag) {
+                v = __uint_as_float((uint32_t)w);
+                const unsigned int rw = (unsigned int)(w >> 32) & 0xFFFFFu;
+                row = rw == 0xFFFFFu ? 0x7fffffff : (int)rw;
+                break;
+            }
+            if (global_timer_ns() - t0 > limit) {  // a peer's candidates never came
                 if (p.status) atomicCAS(p.status, 0, kDevTimeoutPeer);
                 ok = false;
                 break;
             }
         }
+        if (k == 1) {
+            if (cand_before(v, row, bv, bi)) { bv = v; bi = row; }
+        } else {
+            pool[t] = make_uint2(__float_as_uint(v), (uint32_t)row);
+        }
     }
-    // acquire side for the peers' rows (a peer's stores are performed before its announcement);
-    // needed only when there are peers
-    if (p.sh_world > 1) asm volatile("fence.acq_rel.sys;" ::: "memory");
-    *(volatile unsigned int*)&p.sh_state[3] = fc;
-    *(volatile unsigned int*)&p.sh_state[1] = epoch;
+    TRACE_STAMP(tid == 0, 11);
+    scr[1] = 1u;
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    TRACE_STAMP(tid == 0, 12);
+    if (!ok) scr[1] = 0u;
+    asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    ok = scr[1] != 0u;
+    const int nwarps = nthreads >> 5;
+    float pv = __int_as_float(0x7f800000);
+    int pi = -1;
+    for (int r = 0; r < k; ++r) {
+        if (k > 1) {  // the best pooled candidate after the previous pick
+            bv = __int_as_float(0xff800000);
+            bi = 0x7fffffff;
+            for (int t = tid; t < n_words; t += nthreads) {
+                const uint2 e = pool[t];
+                const float v = __uint_as_float(e.x);
+                const int row = (int)e.y;
+                if (cand_before(pv, pi, v, row) && cand_before(v, row, bv, bi)) { bv = v; bi = row; }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (cand_before(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        if ((tid & 31) == 0) {
+            scr[32 + 2 * (tid >> 5)] = __float_as_uint(bv);
+            scr[33 + 2 * (tid >> 5)] = (uint32_t)bi;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+        bv = __uint_as_float(scr[32]);
+        bi = (int)scr[33];
+        for (int w = 1; w < nwarps; ++w) {  // the same order in every thread
+            const float ov = __uint_as_float(scr[32 + 2 * w]);
+            const int oi = (int)scr[33 + 2 * w];
+            if (cand_before(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        }
+        pv = bv;
+        pi = bi;
+        if (tid == 0 && ok) {
+            p.sh_top_val[r] = bv;
+            p.sh_top_idx[r] = bi;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+    }
+    if (tid == 0) {
+        *(volatile unsigned int*)&p.sh_state[2] = cc;
+        *(volatile unsigned int*)&p.sh_state[1] = epoch;
+    }
+    TRACE_STAMP(tid == 0, 13);
 }
 
 // NG independent pipelines inside one CTA: pipeline g has eight consumer warps, its own
@@ -1347,15 +1335,16 @@ static int launch_dp_f(const void* W, const void* X, int x_dtype, const void* bi
         p.sh_total = sh->total_rows;
         for (int q = 0; q < sh->world; ++q) {
             p.sh_out[q] = sh->out[q];
-            p.sh_flags[q] = sh->flags[q];
             p.sh_cand[q] = sh->cand ? sh->cand[q] : nullptr;
         }
         p.sh_state = sh->state;
         p.sh_topk = sh->topk;
-        // the candidate form keeps a CTA's rows (four per consumer thread) and the CTAs' candidates
-        // (eight per thread, 256 CTAs in the scratch table) in registers
+        // the candidate form keeps a CTA's rows in registers (four per consumer thread) when k > 1, has
+        // kShardSlots CTA slots per rank in the tables, and with k > 1 pools every received candidate in
+        // shared memory (the launch asks for that much if its ring is smaller)
         const int threads = kConsumerWarps * ng * 32;
-        if (sh->topk > 0 && ((N + grid - 1) / grid + kTileRows > 4 * threads || grid * kMaxTopK > 8 * threads || grid > 256))
+        if (sh->topk > 1 && smem < 2048 + (size_t)sh->world * kShardSlots * sh->topk * 8) smem = 2048 + (size_t)sh->world * kShardSlots * sh->topk * 8;
+        if (sh->topk > 0 && ((sh->topk > 1 && (N + grid - 1) / grid + kTileRows > 4 * threads) || grid > kShardSlots))
             return fail(B200Q_ERR_UNSUPPORTED, "gemv_shard_topk: %d rows over %d CTAs exceed the candidate form's capacity", N, grid);
         p.sh_top_val = sh->top_val;
         p.sh_top_idx = sh->top_idx;

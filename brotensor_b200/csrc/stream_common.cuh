@@ -61,11 +61,10 @@ struct StreamParams {
     // result vectors through peer pointers, followed by an arrival flag per rank.
     int sh_world, sh_rank;       // sh_world == 0: plain GEMV
     int sh_row_offset, sh_total; // first global row of this shard; rows of the whole matrix
-    float* sh_out[kMaxShardRanks];         // rank q's result buffers: two vectors of sh_total floats, used alternately
-    unsigned int* sh_flags[kMaxShardRanks]; // rank q's arrival words: [r] CTAs of rank r announced so far (all calls), [kMaxShardRanks + r] rank r's grid size
+    float* sh_out[kMaxShardRanks];         // rank q's result buffers: two vectors of sh_total floats, used alternately, then [2][sh_total] 8-byte transfer words
     unsigned int* sh_state;      // this rank: [0] CTAs finished in this launch, [1] completed launches (epoch)
     // Candidate form of the sharded head (sh_topk = k > 0): rank q's candidate table
-    // [2 parities][kMaxShardRanks writers][kMaxTopK values, kMaxTopK indices] and this rank's k results.
+    // [2 parities][kMaxShardRanks writers][kShardSlots CTAs][kMaxTopK] 8-byte words and this rank's k results.
     int sh_topk;
     uint32_t* sh_cand[kMaxShardRanks];
     float* sh_top_val;

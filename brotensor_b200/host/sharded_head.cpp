@@ -39,10 +39,10 @@ ShardedHead::ShardedHead(const Tensor& W_shard, int row_offset, int total_rows, 
     if (row_offset < 0 || W_shard.rows <= 0 || row_offset + W_shard.rows > total_rows)
         throw std::runtime_error("brotensor: sharded_head: shard rows do not lie inside the matrix");
     cuda_check(cudaSetDevice(W_shard.device.index), "cudaSetDevice");
-    // exchange memory: [2][total_rows] floats, 256 bytes of arrival words, then the candidate table
-    // [2 parities][8 writing ranks][8 values + 8 rows] and this rank's per-CTA scratch [256][16]
+    // exchange memory: [2][total_rows] floats (the result vectors), [2][total_rows] 8-byte transfer words
+    // (b200q_gemv_shard), then the candidate table [2 parities][8 ranks][256 CTA slots][8] x 8 bytes
     // (b200q_gemv_shard_topk)
-    const std::size_t bytes = out_bytes() + 256 + (2 * 8 * 16 + 256 * 16) * sizeof(std::uint32_t);
+    const std::size_t bytes = out_bytes() + kCandBytes;
     cuda_check(cudaMalloc(&local_, bytes), "cudaMalloc(exchange memory)");
     cuda_check(cudaMemset(local_, 0, bytes), "cudaMemset");
     cuda_check(cudaMalloc(&state_, 256), "cudaMalloc(state)");
@@ -68,12 +68,10 @@ void ShardedHead::connect(const std::vector<IpcHandle>& handles) {
         cuda_check(cudaIpcOpenMemHandle(&peer_base_[q], h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
     }
     peer_out_.resize(world_);
-    peer_flags_.resize(world_);
     peer_cand_.resize(world_);
     for (int q = 0; q < world_; ++q) {
         peer_out_[q] = peer_base_[q];
-        peer_flags_[q] = static_cast<char*>(peer_base_[q]) + out_bytes();
-        peer_cand_[q] = static_cast<char*>(peer_base_[q]) + out_bytes() + 256;
+        peer_cand_[q] = static_cast<char*>(peer_base_[q]) + out_bytes();
     }
     connected_ = true;
 }
@@ -110,9 +108,9 @@ void ShardedHead::run(const Tensor& W, const Tensor& x, const Tensor* bias_shard
     // this rank's results of the candidate form live behind the two state words
     char* st = static_cast<char*>(state_);
     const int rc = k == 0 ? b200q_gemv_shard(wfmt, W.data, x.data, dt_code(x.dtype), b, W_->rows, W_->cols, row_offset_, total_rows_, rank_,
-                                             world_, peer_out_.data(), peer_flags_.data(), state_, cuda_current_stream())
+                                             world_, peer_out_.data(), state_, cuda_current_stream())
                           : b200q_gemv_shard_topk(wfmt, W.data, x.data, dt_code(x.dtype), b, W_->rows, W_->cols, row_offset_, total_rows_,
-                                                  rank_, world_, peer_out_.data(), peer_flags_.data(), peer_cand_.data(), state_, k,
+                                                  rank_, world_, peer_out_.data(), peer_cand_.data(), state_, k,
                                                   st + 64, st + 128, cuda_current_stream());
     if (rc != B200Q_OK) throw std::runtime_error(std::string("brotensor: sharded_head: ") + b200q_last_error());
     ++calls_;

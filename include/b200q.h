@@ -156,59 +156,55 @@ int b200q_gemv_swiglu(int fmt, const void* W_gate, const void* W_up, const void*
 /*
  * Row-sharded decode GEMV for one rank of a multi-GPU LM head (M = 1):
  * this rank owns rows [row_offset, row_offset + rows) of a matrix of total_rows
- * rows; W_shard is the byte range of those rows, x is replicated. Every CTA of
- * the kernel writes its finished rows straight into ALL ranks' result vectors
- * through peer pointers (NVLink stores) and then announces itself at every peer
- * (one release-add on a counter word); the CTA that finishes last on this rank
- * waits - at most one second - until every peer's CTAs have been announced
- * here, so when the kernel has completed, this rank holds the whole result
- * vector. There is no separate collective.
- *   peer_out[q]   rank q's result memory: TWO vectors of total_rows FP32, used
- *                 alternately; after the n-th call on this state the result is
- *                 vector (n & 1). Must be zero-initialised device memory
- *                 mapped into this process (e.g. CUDA IPC).
- *   peer_flags[q] rank q's arrival words, 16 x uint32, zero-initialised: word r
- *                 counts the CTAs rank r has announced over all calls, word 8 + r
- *                 holds rank r's grid size.
+ * rows; W_shard is the byte range of those rows, x is replicated. There is no
+ * separate collective and, on the exchange path, no fence, flag or counter:
+ * every CTA of the kernel sends its finished rows to ALL ranks through peer
+ * pointers (NVLink stores) as 8-byte words that carry the value and the call's
+ * number, and then receives its slice of the whole vector by polling the words
+ * the peers sent - at most one second - and writing the values into this rank's
+ * result vector. When the kernel has completed, this rank holds the whole
+ * result vector.
+ *   peer_out[q]   rank q's exchange memory, 24 * total_rows bytes: TWO result
+ *                 vectors of total_rows FP32, used alternately (after the n-th
+ *                 call on this state the result is vector (n & 1); only rank q
+ *                 itself reads and writes them), then 2 x total_rows 8-byte
+ *                 transfer words that every rank writes. Zero-initialised device
+ *                 memory mapped into this process (e.g. CUDA IPC).
  *   state         this rank's own four uint32 (CTA counter, calls of both forms,
- *                 calls of the candidate form, calls of this form), zero-initialised;
- *                 its second word is the call count n.
- * All ranks must make the same sequence of calls. A rank that never arrives
+ *                 calls of the candidate form, reserved), zero-initialised; its
+ *                 second word is the call count n.
+ * All ranks must make the same sequence of calls. A rank that never sends
  * makes the others report B200Q_ERR_TIMEOUT through b200q_device_status(): the
  * kernel gives up after the wait limit (one second, or the "wait_limit_us"
  * option), records status 105 and returns; nothing traps or hangs. After such
  * a timeout this rank's call counter has advanced without its peers', so the
- * exchange memory of ALL ranks (peer_out, peer_flags, state) must be zeroed or
+ * exchange memory of ALL ranks (peer_out, peer_cand, state) must be zeroed or
  * created anew before the head is used again; plain b200q_gemv calls on the
  * device are unaffected.
  * brotensor has no sharded form; the closest is its P2P bring-up
  * (src/cuda/register.cu:90-103).
  *
  * b200q_gemv_shard_topk is the candidate form for greedy / top-k sampling
- * (k = 1 .. 8, fewer than 1048575 rows): nothing but eight 8-byte candidates per
- * rank crosses the links. Each rank keeps its shard's logits in its OWN result
- * vector only, selects its k best and stores them - value, row and a tag of the
- * call count in one indivisible word each - into every rank's candidate table;
- * it then polls its own table until every peer's words carry this call's tag
- * (no fence, flag or counter on the path; the same wait limit and timeout
- * status) and leaves the k best of all ranks in top_val (k FP32, largest
- * first) and top_idx (k int32 global rows) on this device. Equal values keep
- * the lower row, as brotensor's greedy sampling does
- * (include/brotensor/ops/sampling.h:27-28); top_idx[0] is what sample_logits
- * returns at temperature 0 on the full logit vector.
- *   peer_cand[q]  rank q's candidate memory, 17408 bytes, zero-initialised, mapped
- *                 like peer_out: 2 x 8 x 8 uint64 (parity of the call, writing rank,
- *                 candidate) that the peers write, then 256 x 16 uint32 of scratch
- *                 for the rank's own CTAs.
+ * (k = 1 .. 8, fewer than 1048575 rows, at most 256 CTAs): no logits cross the
+ * links. Each rank keeps its shard's logits in its OWN result vector only;
+ * every CTA reduces its rows to k candidates and stores them - value, row and a
+ * tag of the call count in one indivisible 8-byte word each - into every rank's
+ * candidate table; CTA 0 of each rank polls its table until all words carry
+ * this call's tag (the same wait limit and timeout status) and leaves the k
+ * best of all ranks in top_val (k FP32, largest first) and top_idx (k int32
+ * global rows) on this device. Equal values keep the lower row, as brotensor's
+ * greedy sampling does (include/brotensor/ops/sampling.h:27-28); top_idx[0] is
+ * what sample_logits returns at temperature 0 on the full logit vector.
+ *   peer_cand[q]  rank q's candidate table, 262144 bytes, zero-initialised,
+ *                 mapped like peer_out: 2 x 8 x 256 x 8 uint64 (parity of the
+ *                 call, writing rank, CTA slot, candidate).
  * The two forms may be mixed on one set of exchange memory.
  */
 int b200q_gemv_shard(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
-                     int row_offset, int total_rows, int rank, int world, void* const* peer_out,
-                     void* const* peer_flags, void* state, void* stream);
+                     int row_offset, int total_rows, int rank, int world, void* const* peer_out, void* state, void* stream);
 int b200q_gemv_shard_topk(int fmt, const void* W_shard, const void* x, int x_dtype, const void* bias_shard, int rows, int K,
                           int row_offset, int total_rows, int rank, int world, void* const* peer_out,
-                          void* const* peer_flags, void* const* peer_cand, void* state, int k, void* top_val, void* top_idx,
-                          void* stream);
+                          void* const* peer_cand, void* state, int k, void* top_val, void* top_idx, void* stream);
 
 /*
  * Prefill GEMM on the tensor cores, any M >= 1:

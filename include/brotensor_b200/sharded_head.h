@@ -1,13 +1,14 @@
 // Row-sharded LM head over the GPUs of one node, one process per GPU.
 //
 // Each rank owns a contiguous row range of a quantized (out, in) matrix and a block of
-// "exchange memory": two result vectors of `out` floats, the arrival words and a small table of
-// sampling candidates.
+// "exchange memory": two result vectors of `out` floats, two vectors of 8-byte transfer words and a
+// table of sampling candidates.
 // The ranks exchange CUDA IPC handles of these blocks once (the caller moves the 64-byte
 // handles between processes with whatever it has: torch.distributed, MPI, a file), map each
 // other's blocks, and from then on a forward is ONE kernel per rank: the decode GEMV of the
-// shard whose epilogue stores every row into all ranks' result vectors over NVLink and
-// then signals / awaits arrival (b200q_gemv_shard). No collective library on the data path.
+// shard whose epilogue sends every row to all ranks over NVLink as a word that carries the call's
+// number, and receives the peers' words the same way (b200q_gemv_shard): no collective library, fence,
+// flag or counter on the data path.
 // forward_topk is the form for greedy / top-k sampling: k (value, row) candidates per rank cross
 // the links instead of the logits (b200q_gemv_shard_topk).
 //
@@ -64,12 +65,14 @@ private:
     int row_offset_, total_rows_, rank_, world_;
     void* local_ = nullptr;                  // exchange memory of this rank
     std::vector<void*> peer_base_;           // mapped exchange memory of every rank (own = local_)
-    std::vector<void*> peer_out_, peer_flags_, peer_cand_;
+    std::vector<void*> peer_out_, peer_cand_;
     void* state_ = nullptr;
     IpcHandle handle_{};
     std::uint64_t calls_ = 0;
     bool connected_ = false;
-    std::size_t out_bytes() const { return 2u * sizeof(float) * static_cast<std::size_t>(total_rows_); }
+    static constexpr std::size_t kCandBytes = 2u * 8u * 256u * 8u * 8u;
+    // two result vectors of floats and two vectors of 8-byte transfer words
+    std::size_t out_bytes() const { return 24u * static_cast<std::size_t>(total_rows_); }
     void run(const Tensor& W, const Tensor& x, const Tensor* bias_shard, int k);
 };
 

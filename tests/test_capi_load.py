@@ -58,7 +58,7 @@ def test_argument_validation_needs_no_device(L):
     # the sharded form checks its rank / row arguments before it touches the device
     tab = (ctypes.c_void_p * 8)(*([p16] * 8))
     sh = lambda rows, off, total, rank, world: L.b200q_gemv_shard(capi.Q4_K, p16, p16, capi.F32, None, rows, 256, off,
-                                                                  total, rank, world, tab, tab, p16, None)
+                                                                  total, rank, world, tab, p16, None)
     assert sh(4, 0, 4, 2, 2) == capi.ERR_BAD_ARG and b"rank 2 of 2" in L.b200q_last_error()
     assert sh(4, 0, 4, 0, 9) == capi.ERR_BAD_ARG
     assert sh(4, 2, 4, 0, 1) == capi.ERR_BAD_ARG and b"do not lie in" in L.b200q_last_error()

@@ -21,18 +21,17 @@ def test_peer_wait_runs_out_and_the_device_stays_usable(cpu_oracle):
     xh = synth.make_activations(1, K, seed=31)
     W = torch.from_numpy(Wh).cuda()
     x = torch.from_numpy(xh).cuda()
-    # rank 0 of 2 on one GPU: rank 1's result memory and arrival words are a second local buffer
-    # that nobody ever signals, so rank 0's wait for rank 1 cannot complete
-    outs = [torch.zeros(2 * total, dtype=torch.float32, device="cuda") for _ in range(world)]
-    flags = [torch.zeros(16, dtype=torch.int32, device="cuda") for _ in range(world)]  # 8 counters + 8 grid sizes
+    # rank 0 of 2 on one GPU: rank 1's exchange memory is a second local buffer that nobody ever writes
+    # rows into, so rank 0's wait for rank 1's rows cannot complete
+    # (two result vectors of floats + two vectors of 8-byte transfer words = 6 floats per row)
+    outs = [torch.zeros(6 * total, dtype=torch.float32, device="cuda") for _ in range(world)]
     state = torch.zeros(4, dtype=torch.int32, device="cuda")
     po = (C.c_void_p * world)(*[t.data_ptr() for t in outs])
-    pf = (C.c_void_p * world)(*[t.data_ptr() for t in flags])
     assert ops.device_status() == 0
     ops.set_option("wait_limit_us", 2000)  # two milliseconds instead of a second
     try:
         stream = torch.cuda.current_stream().cuda_stream
-        rc = L.b200q_gemv_shard(fmt, W.data_ptr(), x.data_ptr(), capi.F32, None, rows, K, 0, total, 0, world, po, pf,
+        rc = L.b200q_gemv_shard(fmt, W.data_ptr(), x.data_ptr(), capi.F32, None, rows, K, 0, total, 0, world, po,
                                 state.data_ptr(), stream)
         assert rc == capi.OK, L.b200q_last_error()
         torch.cuda.synchronize()  # the kernel returned by itself
@@ -42,14 +41,14 @@ def test_peer_wait_runs_out_and_the_device_stays_usable(cpu_oracle):
         assert b"wait" in L.b200q_last_error()
         rc = L.b200q_device_status(C.byref(v))  # reading the status resets it
         assert rc == capi.OK and v.value == 0
-        # this rank's own rows did arrive in its result vector (call 1 -> vector 1), and at the "peer"
+        # this rank's own rows did arrive in its result vector (call 1 -> vector 1), and at the "peer" as
+        # transfer words (value, call number 1) behind its two result vectors
         want = cpu_oracle.matmul(fmt, Wh, xh, threads=4).reshape(-1)
         got = outs[0].cpu().numpy()[total:total + rows]
         assert oracle.rel_l2(got, want) < 2e-3
-        assert np.array_equal(outs[1].cpu().numpy()[total:total + rows], got)
-        # every CTA of rank 0 announced itself at the "peer" (counter == grid size); nobody announced at rank 0
-        f1, f0 = flags[1].cpu().numpy(), flags[0].cpu().numpy()
-        assert int(state.cpu()[1]) == 1 and f1[0] == f1[8] and f1[8] > 0 and f0[1] == 0 and f0[9] == 0
+        words = outs[1].cpu().numpy()[2 * total:].view(np.uint32).reshape(2, total, 2)[1, :rows]
+        assert np.array_equal(words[:, 0].view(np.float32), got) and np.all(words[:, 1] == 1)
+        assert int(state.cpu()[1]) == 1
     finally:
         ops.set_option("wait_limit_us", 0)
     # the device is as usable as before: a plain GEMV right after the timeout
