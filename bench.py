@@ -50,7 +50,7 @@ from brotensor_b200 import synth  # noqa: E402
 WORKLOAD = "llama3_8b_decode_layer_set_m1"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (the Q4_K decode
 # GEMV on 14336x4096), from an ncu capture of `bench.py --case gemv:q4k:14336:4096:1`
-DOMINANT_KERNEL_DRAM_TRAFFIC = 33112064
+DOMINANT_KERNEL_DRAM_TRAFFIC = 33069568
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -316,11 +316,18 @@ def main():
     ap.add_argument("--case", default=None, metavar="OP:FMT:N:K:M",
                     help="profiling driver: a handful of launches of one shape (op gemv|gemm|dequant, fmt q4k|q6k|q8_0) and nothing else")
     ap.add_argument("--launches", type=int, default=4, help="launches of --case")
+    ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE",
+                    help="library option for --case / --phases (b200q_set_option), e.g. gemv_xr=0 for the tile kernel")
     ap.add_argument("--no-pdl", action="store_true", help="--phases without programmatic dependent launch")
     ap.add_argument("--phases", nargs="?", const="", default=None, metavar="FMT:N:K,...",
                     help="phase breakdown of the decode GEMV from %%globaltimer stamps (needs the trace build: "
                          "python -m brotensor_b200.build --trace; B200Q_LIB=brotensor_b200/lib/libb200q_trace.so)")
     args = ap.parse_args()
+    if args.opt:
+        from brotensor_b200 import ops as _ops
+        for kv in args.opt:
+            key, val = kv.split("=")
+            _ops.set_option(key, int(val))
     if args.case:
         return run_case(args.case, args.launches)
     if args.phases is not None:
