@@ -408,6 +408,66 @@ def reference_cuda(peaks, stream, root):
     return out
 
 
+def upload_case(N=57344, K=4096):
+    """Weight upload from a GGUF file (page cache warm): the host layer's staged upload (two pinned 8 MiB
+    buffers, memcpy of the next piece overlapping the DMA of the previous one; gguf::upload_rows) against one
+    blocking cudaMemcpy from the pageable mapping, which is what brotensor's upload_raw does
+    (src/gguf.cpp:473-500 through Tensor::from_raw_bytes_on)."""
+    import ctypes as C
+    import os
+    import struct
+    import tempfile
+    import time
+    from brotensor_b200 import hostapi
+    hostapi.init()
+    L = hostapi.lib()
+    fmt = synth.Q4_K
+    payload = synth.make_blocks(fmt, N, K, seed=11).tobytes()
+    align, name, key = 32, b"blk.0.ffn_gate.weight", b"general.alignment"
+    head = struct.pack("<IIQQ", 0x46554747, 3, 1, 1) + struct.pack("<Q", len(key)) + key + struct.pack("<II", 4, align)
+    head += struct.pack("<Q", len(name)) + name + struct.pack("<I", 2) + struct.pack("<QQ", K, N) + struct.pack("<IQ", 12, 0)  # 12 = GGML_TYPE_Q4_K
+    head += b"\0" * ((align - len(head) % align) % align)
+    fd, path = tempfile.mkstemp(suffix=".gguf")
+    try:
+        with os.fdopen(fd, "wb") as f:
+            f.write(head + payload)
+        L.b200h_gguf_open.restype = C.c_void_p
+        L.b200h_gguf_open.argtypes = [C.c_char_p]
+        L.b200h_gguf_close.argtypes = [C.c_void_p]
+        L.b200h_gguf_upload_rows.restype = C.c_void_p
+        L.b200h_gguf_upload_rows.argtypes = [C.c_void_p] + [C.c_int] * 6
+        L.b200h_tensor_free.argtypes = [C.c_void_p]
+        h = L.b200h_gguf_open(path.encode())
+        assert h, L.b200h_last_error()
+        dev = torch.cuda.current_device()
+        staged = []
+        for _ in range(4):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            t = L.b200h_gguf_upload_rows(h, 0, N, K, 0, N, dev)  # returns when the bytes are on the device
+            staged.append(time.perf_counter() - t0)
+            assert t, L.b200h_last_error()
+            L.b200h_tensor_free(t)
+        L.b200h_gguf_close(h)
+        mm = np.memmap(path, dtype=np.uint8, mode="c", offset=len(head), shape=(len(payload),))  # copy-on-write: pageable, never written
+        dst = torch.empty(len(payload), dtype=torch.uint8, device="cuda")
+        blocking = []
+        for _ in range(4):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            dst.copy_(torch.from_numpy(mm))  # pageable source: one blocking copy
+            torch.cuda.synchronize()
+            blocking.append(time.perf_counter() - t0)
+        same = bool(torch.equal(dst[:4096].cpu(), torch.frombuffer(bytearray(payload[:4096]), dtype=torch.uint8)))
+        del mm
+    finally:
+        os.unlink(path)
+    nb = len(payload)
+    return {"fmt": "q4k", "N": N, "K": K, "bytes": nb, "staged_GBps": nb / min(staged[1:]) / 1e9, "staged_ms": min(staged[1:]) * 1e3,
+            "blocking_pageable_GBps": nb / min(blocking[1:]) / 1e9, "blocking_ms": min(blocking[1:]) * 1e3, "bytes_checked": same,
+            "note": "file in the page cache; best of three after one warm-up; host time from call to bytes resident"}
+
+
 def run(rank, world, peaks, stream):
     out = {}
     if world == 1:
@@ -421,5 +481,9 @@ def run(rank, world, peaks, stream):
         out["layer_set_grouped"] = grouped_layer_set(stream, peaks["hbm_gbs"])
         out["dequant_to_fp16_4096x4096"] = [dequant_case(f, 4096, 4096, stream, peaks["hbm_gbs"]) for f in (synth.Q4_K, synth.Q6_K, synth.Q8_0)]
         out["repack_q6k_down_proj"] = repack_case(stream, peaks["hbm_gbs"])
+        try:
+            out["upload_gguf_q4k_132MB"] = upload_case()
+        except Exception as ex:  # noqa: BLE001 - a full /tmp must not cost the benchmark line
+            out["upload_gguf_q4k_132MB"] = {"error": repr(ex)[:300]}
     out["lm_head"] = lm_head_case(rank, world, stream, peaks["hbm_gbs"])
     return out

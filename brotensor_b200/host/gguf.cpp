@@ -11,6 +11,9 @@
 #include "brotensor_b200/repack.h"
 
 #include <cuda_runtime_api.h>
+
+#include <mutex>
+#include <thread>
 #include <fcntl.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -290,9 +293,43 @@ std::pair<int, int> shape_to_2d(const std::vector<std::int64_t>& shape) {
 namespace {
 
 // Host bytes -> device through two pinned buffers: while one buffer is on its way to the
-// device the next piece of the mapping is read (page-faulted) into the other one.
+// device the next piece of the mapping is read (page-faulted) into the other one, by four threads (one
+// thread copies at ~7 GB/s, a quarter of what the link takes). The buffers are allocated once per
+// process (page-locking 2 x 32 MiB costs milliseconds) and uploads take turns on them.
+struct PinnedPair {
+    void* buf[2] = {nullptr, nullptr};
+    cudaEvent_t ev[2] = {nullptr, nullptr};
+    std::mutex mu;
+    ~PinnedPair() {
+        for (int i = 0; i < 2; ++i) {
+            if (buf[i]) cudaFreeHost(buf[i]);
+            if (ev[i]) cudaEventDestroy(ev[i]);
+        }
+    }
+};
+constexpr std::size_t kPiece = 32u << 20;
+constexpr int kCopyThreads = 4;
+
+void parallel_copy(void* dst, const std::uint8_t* src, std::size_t n) {
+    if (n < (4u << 20)) {
+        std::memcpy(dst, src, n);
+        return;
+    }
+    const std::size_t part = ((n / kCopyThreads) + 4095) & ~std::size_t(4095);
+    std::thread th[kCopyThreads - 1];
+    for (int t = 1; t < kCopyThreads; ++t) {
+        const std::size_t o = part * t;
+        th[t - 1] = std::thread([=] {
+            if (o < n) std::memcpy(static_cast<std::uint8_t*>(dst) + o, src + o, (n - o) < part ? (n - o) : part);
+        });
+    }
+    std::memcpy(dst, src, n < part ? n : part);
+    for (auto& t : th) t.join();
+}
+
 void staged_upload(void* dst, const std::uint8_t* src, std::size_t n, int dev) {
-    constexpr std::size_t kPiece = 8u << 20;
+    static PinnedPair pp;
+    std::lock_guard<std::mutex> lock(pp.mu);
     int prev = 0;
     cudaGetDevice(&prev);
     auto check = [&](cudaError_t e, const char* what) {
@@ -304,28 +341,21 @@ void staged_upload(void* dst, const std::uint8_t* src, std::size_t n, int dev) {
     };
     check(cudaSetDevice(dev), "cudaSetDevice");
     cudaStream_t st = static_cast<cudaStream_t>(cuda_current_stream(dev));
-    void* pin[2] = {nullptr, nullptr};
-    cudaEvent_t ev[2];
-    const std::size_t piece = n < kPiece ? n : kPiece;
     for (int i = 0; i < 2; ++i) {
-        check(cudaMallocHost(&pin[i], piece), "cudaMallocHost");
-        check(cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming), "cudaEventCreate");
+        if (!pp.buf[i]) check(cudaMallocHost(&pp.buf[i], kPiece), "cudaMallocHost");
+        if (!pp.ev[i]) check(cudaEventCreateWithFlags(&pp.ev[i], cudaEventDisableTiming), "cudaEventCreate");
     }
     std::size_t off = 0;
     for (int i = 0; off < n; ++i) {
         const int b = i & 1;
-        const std::size_t len = (n - off) < piece ? (n - off) : piece;
-        if (i >= 2) check(cudaEventSynchronize(ev[b]), "cudaEventSynchronize");  // buffer b is free again
-        std::memcpy(pin[b], src + off, len);
-        check(cudaMemcpyAsync(static_cast<std::uint8_t*>(dst) + off, pin[b], len, cudaMemcpyHostToDevice, st), "cudaMemcpyAsync");
-        check(cudaEventRecord(ev[b], st), "cudaEventRecord");
+        const std::size_t len = (n - off) < kPiece ? (n - off) : kPiece;
+        if (i >= 2) check(cudaEventSynchronize(pp.ev[b]), "cudaEventSynchronize");  // buffer b is free again
+        parallel_copy(pp.buf[b], src + off, len);
+        check(cudaMemcpyAsync(static_cast<std::uint8_t*>(dst) + off, pp.buf[b], len, cudaMemcpyHostToDevice, st), "cudaMemcpyAsync");
+        check(cudaEventRecord(pp.ev[b], st), "cudaEventRecord");
         off += len;
     }
     check(cudaStreamSynchronize(st), "cudaStreamSynchronize");
-    for (int i = 0; i < 2; ++i) {
-        cudaFreeHost(pin[i]);
-        cudaEventDestroy(ev[i]);
-    }
     cudaSetDevice(prev);
 }
 

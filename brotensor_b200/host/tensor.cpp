@@ -158,7 +158,17 @@ Tensor Tensor::view(Device dev, void* p, int r, int c, Dtype dt) {
 
 Tensor Tensor::clone() const { return to(device); }
 
+namespace {
+// A weight regrouped on the device (repack_weights) is a byte permutation of the GGUF block layout that
+// only the device kernels read: host code handed those bytes would decode garbage without any error.
+void refuse_regrouped_to_host(const Tensor& t, const char* what) {
+    if (!t.device.is_cpu() && dtype_is_quant(t.dtype) && t.data && detail::repacked_ptr(t.data))
+        fail(std::string(what) + ": the weight is in the regrouped device layout; call unpack_weights() first");
+}
+}  // namespace
+
 Tensor Tensor::to(Device target) const {
+    if (target.is_cpu()) refuse_regrouped_to_host(*this, "Tensor::to");
     Tensor t = empty_on(target, rows, cols, dtype);
     const std::size_t n = bytes();
     if (!n || !data) return t;
@@ -198,6 +208,7 @@ void Tensor::copy_raw_to_host(void* dst) const {
     const std::size_t n = bytes();
     if (!n) return;
     if (!data) fail("copy_to_host: tensor has no storage");
+    refuse_regrouped_to_host(*this, "copy_to_host");
     if (device.is_cpu()) std::memcpy(dst, data, n);
     else detail::alloc_for(device).memcpy_d2h(dst, data, n, device.index);
 }
@@ -216,6 +227,7 @@ void Tensor::copy_raw_to_host_async(void* dst) const {
     const std::size_t n = bytes();
     if (!n) return;
     if (!data) fail("copy_to_host_async: tensor has no storage");
+    refuse_regrouped_to_host(*this, "copy_to_host_async");
     if (device.is_cpu()) std::memcpy(dst, data, n);
     else detail::alloc_for(device).memcpy_d2h_async(dst, data, n, device.index);
 }

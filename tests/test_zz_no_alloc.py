@@ -31,7 +31,6 @@ def test_static_matches_workspace_form_twice(fmt, N, K, M):
     from brotensor_b200 import ops
     W = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=N + M)).cuda()
     bias = torch.from_numpy(synth.make_activations(1, N, seed=5)).cuda().view(-1)
-    free0 = torch.cuda.mem_get_info()[0]
     outs = []
     # two calls in a row with different activations: the second must not see the first's image
     for call in range(2):
@@ -39,14 +38,17 @@ def test_static_matches_workspace_form_twice(fmt, N, K, M):
         ref = ops.gemm(fmt, W, X, N, bias=bias)
         ops.tc_calls_consume(fmt)
         got = torch.empty_like(ref)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         ops.gemm_static(fmt, W, X, N, bias=bias, out=got)
         torch.cuda.synchronize()
+        if call == 1:  # the kernels' code is resident after the first call: the second must not take a byte of device memory
+            assert torch.cuda.mem_get_info()[0] == free_before, "gemm_static allocated device memory"
         assert ops.tc_calls_consume(fmt) == 1  # the tensor-core kernel ran, not a fallback
         assert torch.equal(got, ref), f"call {call}: max diff {(got - ref).abs().max().item()}"
         outs.append(got)
     assert not torch.equal(outs[0], outs[1])
     assert ops.device_status() == 0
-    del free0
 
 
 @pytest.mark.gpu
