@@ -24,7 +24,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH + ["-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "--use_fast_math=false"]
 NVCC_FLAGS = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
 
-KERNEL_SOURCES = ["api.cu", "dequant.cu", "repack.cu", "gemv_simple.cu", "gemv_stream.cu", "gemv_dp.cu", "gemv_xr.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_static.cu"]
+KERNEL_SOURCES = ["api.cu", "dequant.cu", "repack.cu", "gemv_simple.cu", "gemv_stream.cu", "gemv_dp.cu", "gemv_xr.cu", "gemv_i8.cu", "gemm_tc.cu", "gemm_tc2.cu", "gemm_static.cu"]
 
 
 def _newer(src_list, target) -> bool:

@@ -36,6 +36,10 @@ void dp_set_lean(int v);
 void dp_set_step_fill(int v);
 int launch_gemv_xr(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N, int K,
                    int sms, int* status, cudaStream_t st, bool* taken);
+int launch_gemv_i8(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N, int K,
+                   int sms, int* status, cudaStream_t st, bool* taken);
+void i8_set_enabled(int v);
+int i8_get_enabled();
 void xr_set_enabled(int v);
 int xr_get_enabled();
 int dp_get_wait_limit_us();
@@ -233,6 +237,10 @@ static int gemv_streaming(DevInfo* d, int fmt, const void* W, const void* X, int
                           int y_dtype, int M, int N, int K, cudaStream_t st, bool* taken) {
     *taken = false;
     const size_t smem = d->smem_optin - 1024;
+    if (M >= 2) {  // Q8_0, K = 2048 / 4096: the integer tensor-core kernel streams at the one-row rate for any M <= 8
+        if (int rc = launch_gemv_i8(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, d->status, st, taken)) return rc;
+        if (*taken) return B200Q_OK;
+    }
     const bool mma_first = M >= (fmt == kQ8_0 ? 3 : 4);
     if (mma_first) {
         if (int rc = launch_gemv_stream(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, d->sms, smem, d->status, st, taken)) return rc;
@@ -498,6 +506,7 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "wait_limit_us")) dp_set_wait_limit_us(value);
     else if (!strcmp(key, "gemv_lean")) dp_set_lean(value);
     else if (!strcmp(key, "gemv_xr")) xr_set_enabled(value);
+    else if (!strcmp(key, "gemv_i8")) i8_set_enabled(value);
     else if (!strcmp(key, "gemv_step_fill")) dp_set_step_fill(value);
     else return fail(B200Q_ERR_BAD_ARG, "set_option: unknown key '%s'", key);
     return B200Q_OK;
@@ -512,6 +521,7 @@ int b200q_get_option(const char* key, int* out) {
     else if (!strcmp(key, "gemv_grid")) *out = stream_get_option(3);
     else if (!strcmp(key, "gemv_groups")) *out = dp_get_groups();
     else if (!strcmp(key, "gemv_xr")) *out = xr_get_enabled();
+    else if (!strcmp(key, "gemv_i8")) *out = i8_get_enabled();
     else if (!strcmp(key, "gemv_tile_pairs")) *out = dp_get_tile_pairs();
     else if (!strcmp(key, "gemm_pair")) *out = gemm_get_pair();
     else if (!strcmp(key, "wait_limit_us")) *out = dp_get_wait_limit_us();
