@@ -280,7 +280,8 @@ int b200q_device_status(int* status_out);
  *   "gemm_pair"   0 = one-CTA tcgen05 kernel, otherwise the CTA-pair kernel (default)
  *   "gemv_xr"     Q4_K, one activation row, K <= 4096: 1 = the activation-resident kernel where it is the
  *                 faster one (default), 2 = for every such call, 0 = never
- *   "gemv_i8"     Q8_0, 2..8 activation rows, K = 2048 / 4096: 1 = the integer tensor-core kernel (default), 0 = never
+ *   "gemv_i8"     Q8_0 / Q4_K, 2..8 activation rows, K = 2048 / 4096: 1 = the integer tensor-core kernel where it is
+ *                 the faster one (default), 2 = for every such call, 0 = never
  *   "gemv_lean"   0 = never take the trimmed instantiation of the integer-dot kernel (FP32 in and out, no bias)
  *   "wait_limit_us" bound of the decode kernels' device-side waits (stage barriers, peer arrival) in
  *                 microseconds; 0 = one second. Tests shorten it to see a wait run out.
