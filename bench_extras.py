@@ -475,6 +475,7 @@ def run(rank, world, peaks, stream):
         out["layer_set_per_kernel"] = [gemv_case(fmt, N, K, 1, stream, peaks["hbm_gbs"]) | {"name": name}
                                        for name, fmt, N, K in synth.LLAMA3_8B_LAYER_SET if name not in ("v_proj", "up_proj", "o_proj")]
         out["config2_q8_0_14336x4096"] = [gemv_case(synth.Q8_0, 14336, 4096, M, stream, peaks["hbm_gbs"]) for M in (1, 2, 4, 8)]
+        out["small_batch_q4k_14336x4096"] = [gemv_case(synth.Q4_K, 14336, 4096, M, stream, peaks["hbm_gbs"]) for M in (2, 4, 8)]
         out["config3_q4k_prefill_512"] = [gemm_case(synth.Q4_K, 14336, 4096, 512, dt, stream, peaks)
                                           for dt in (torch.float32, torch.bfloat16)]
         out["prefill_other_formats_512"] = [gemm_case(f, 14336, 4096, 512, torch.float32, stream, peaks) for f in (synth.Q6_K, synth.Q8_0)]
