@@ -1,4 +1,4 @@
-// Decode GEMV for one activation row and rows of at most 4096 elements, Q4_K (sm_100a): the
+// Decode GEMV for one activation row and rows of at most 4096 elements, Q4_K and Q6_K (sm_100a): the
 // activation-resident form of the integer-dot-product GEMV of gemv_dp.cu.
 //
 // What is different from gemv_dp.cu, and why:
@@ -29,10 +29,17 @@
 // (7.6-8.5 us) - half of the SM's warps sit parked in griddepcontrol.wait, and the items are bound
 // by instruction issue, not by memory.
 //
+// Q6_K (K = 2048 or 4096) runs through the same kernel with the half-group work unit of gemv_dp.cu: a lane
+// keeps the 64 activations of its half group of each 2048-element slice, their 16-element sums and the
+// group scales; a row pair is 6720 bytes, so a warp has two ring slots instead of three. The gain is
+// smaller than for Q4_K (the 6-bit unpack, not the activation loads, is most of a Q6_K item):
+// 16032 x 4096 11.2 against 11.6 us, 32064 x 4096 18.5 against 19.7; below 8192 rows it loses.
+//
 // Arithmetic is exactly gemv_dp.cu's (same staging of the activations, same integer dot products,
 // same FP32 combination per group, same butterfly over the lanes), so results are bit-identical to it.
 //
-// Takes the place of brotensor's linear_q4k_fp16_gemv_kernel (src/cuda/q4k.cu:159-224).
+// Takes the place of brotensor's linear_q4k_fp16_gemv_kernel (src/cuda/q4k.cu:159-224) and
+// linear_q6k_fp16_gemv_kernel (src/cuda/q6k.cu:117-176).
 #include "dp_common.cuh"
 
 namespace b200q {
@@ -60,12 +67,13 @@ struct XrParams {
 // shared-memory layout (bytes from the 128-byte aligned base)
 constexpr uint32_t kXrOffX = 0;                                 // 32 groups x 272 bytes of int16 activations
 constexpr uint32_t kXrOffScale = 32 * kXGroupStride;            // 32 floats: 2^-e per group
-constexpr uint32_t kXrOffSums = kXrOffScale + 128;              // 128 ints: sums over 32 elements
-constexpr uint32_t kXrOffRing = kXrOffSums + 512;               // n_slots x 2 rows
+constexpr uint32_t kXrOffSums = kXrOffScale + 128;              // Q4_K: 128 sums over 32 elements; Q6_K: 256 sums over 16
+constexpr uint32_t kXrOffRing = kXrOffSums + 1024;              // n_slots x 2 rows
 constexpr size_t kXrFixedSmem = kXrOffRing + 128;               // plus alignment slack
 
 // Stages segment `idx` (eight activations) of the row: int16 with the group's power-of-two scale,
 // as x_store_seg of gemv_dp.cu does for one activation row. Called by whole warps.
+template <int FMT>
 __device__ __forceinline__ void xr_stage_seg(uint32_t sbase, int idx, const float (&v)[8]) {
     const int gg = idx >> 4, i = idx & 15;
     float amax = 0.f;
@@ -93,8 +101,12 @@ __device__ __forceinline__ void xr_stage_seg(uint32_t sbase, int idx, const floa
     sts128(sbase + kXrOffX + (uint32_t)(gg * kXGroupStride + (i << 4)), o);
     if (i == 0) sts32(sbase + kXrOffScale + (uint32_t)gg * 4, (uint32_t)(127 - e) << 23);
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    if ((i & 3) == 0) sts32(sbase + kXrOffSums + (uint32_t)(idx >> 2) * 4, (uint32_t)sum);
+    if constexpr (FMT == kQ6_K) {  // sums over 16 elements = 2 segments
+        if ((i & 1) == 0) sts32(sbase + kXrOffSums + (uint32_t)(idx >> 1) * 4, (uint32_t)sum);
+    } else {                        // sums over 32 elements = 4 segments
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((i & 3) == 0) sts32(sbase + kXrOffSums + (uint32_t)(idx >> 2) * 4, (uint32_t)sum);
+    }
 }
 
 // q4k_dot of dp_common.cuh against activations x[OFF .. OFF + 7] of the resident group (constant
@@ -139,8 +151,66 @@ __device__ __forceinline__ float xr_row(uint32_t pr, int hb, const uint4 (&x)[16
     return xs * (d * (float)isum - dm * (float)imin);
 }
 
-template <int CW>
-__global__ void __launch_bounds__(CW * 32, 1) gemv_xr_q4k_kernel(const __grid_constant__ XrParams p) {
+// ---- Q6_K: one row's half group (64 elements: {32 Q + 16 H + i}, Q = 0..3, i = 0..15, of group gi) against
+// the lane's resident activations x[2 Q], x[2 Q + 1] and their 16-element sums sx[Q]; the arithmetic of
+// item_q6k_half / q6_sub_h in gemv_dp.cu. Returns d * sum_Q sc_Q * (dot_Q - 32 * sx_Q).
+__device__ __forceinline__ uint32_t xr_lds32(uint32_t a) { return lds32i<0>(a); }
+__device__ __forceinline__ float xr_q6k_row(uint32_t row, int gi, int H, const uint4 (&x)[8], const int (&sx)[4], float& d_out) {
+    const int bi = gi >> 1, G = gi & 1;
+    const uint32_t sh = (uint32_t)(bi & 1) * 16u;  // odd blocks start at 2 (mod 4): aligned words + funnel shift
+    const uint32_t L = row + (uint32_t)(bi * 210 - (bi & 1) * 2);
+    const uint32_t La = L + 64u * G + 16u * H, Lh = L + 128u + 32u * G + 16u * H, Ls = L + 192u + 8u * G;
+    uint32_t ql[8], qh[4], su[2];
+    {
+        uint32_t ra[5], rb[5], rh[5], rs[3];
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+            ra[k] = xr_lds32(La + 4u * k);
+            rb[k] = xr_lds32(La + 32u + 4u * k);
+            rh[k] = xr_lds32(Lh + 4u * k);
+        }
+#pragma unroll
+        for (int k = 0; k < 3; ++k) rs[k] = xr_lds32(Ls + 4u * k);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            ql[k] = __funnelshift_r(ra[k], ra[k + 1], sh);
+            ql[4 + k] = __funnelshift_r(rb[k], rb[k + 1], sh);
+            qh[k] = __funnelshift_r(rh[k], rh[k + 1], sh);
+        }
+        su[0] = __funnelshift_r(rs[0], rs[1], sh) ^ 0x80808080u;
+        su[1] = __funnelshift_r(rs[1], rs[2], sh) ^ 0x80808080u;
+    }
+    d_out = h2f((lds32i<208>(L) >> sh) & 0xFFFFu);
+    float accg = 0.f;
+#pragma unroll
+    for (int Q = 0; Q < 4; ++Q) {
+        uint32_t v[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const uint32_t a = ql[4 * (Q & 1) + w], hb = qh[w];
+            const uint32_t nib = (Q < 2 ? a : (a >> 4)) & 0x0F0F0F0Fu;
+            const uint32_t h2 = (Q == 0 ? hb << 4 : Q == 1 ? hb << 2 : Q == 2 ? hb : hb >> 2) & 0x30303030u;
+            v[w] = nib | h2;
+        }
+        // int8 scale byte 2 (Q & 1) + H of the word (bytes xor-ed with 0x80) -> exact float
+        const float scf = __uint_as_float(__byte_perm(su[Q >> 1], 0x4B000000u, 0x7440 | (2 * (Q & 1) + H))) - 8388736.0f;
+        const uint4 x0 = x[2 * Q], x1 = x[2 * Q + 1];
+        int c0 = 0, c1 = 0;
+        c0 = dp2a_lo_su(x0.x, v[0], c0);
+        c0 = dp2a_hi_su(x0.y, v[0], c0);
+        c1 = dp2a_lo_su(x0.z, v[1], c1);
+        c1 = dp2a_hi_su(x0.w, v[1], c1);
+        c0 = dp2a_lo_su(x1.x, v[2], c0);
+        c0 = dp2a_hi_su(x1.y, v[2], c0);
+        c1 = dp2a_lo_su(x1.z, v[3], c1);
+        c1 = dp2a_hi_su(x1.w, v[3], c1);
+        accg = fmaf(scf, (float)(c0 + c1 - 32 * sx[Q]), accg);
+    }
+    return accg;
+}
+
+template <int FMT, int CW>
+__global__ void __launch_bounds__(CW * 32, 1) gemv_xr_kernel(const __grid_constant__ XrParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 127u) & ~127u;
     __shared__ uint64_t bar_full[kXrMaxSlots];
@@ -231,16 +301,38 @@ __global__ void __launch_bounds__(CW * 32, 1) gemv_xr_q4k_kernel(const __grid_co
         }
 #pragma unroll
         for (int u = 0; u < U; ++u)
-            if (tid + u * CW * 32 < segs) xr_stage_seg(sbase, tid + u * CW * 32, v[u]);
+            if (tid + u * CW * 32 < segs) xr_stage_seg<FMT>(sbase, tid + u * CW * 32, v[u]);
     }
     if (lane == 0) feed(warp + 2 * CW, warp + 2 * CW);
     asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
-    // the lane's group, resident from here on; lanes past the row's last group work on zeros
-    const bool active = lane < (p.K >> 7);
+    // the lane's activations, resident from here on.
+    // Q4_K: its 128-element group (lanes past the row's last group work on zeros).
+    // Q6_K: the half group (lane % 16, lane / 16) of the row's first 2048 elements in x[0..7] and of the
+    // second 2048 (K = 4096) in x[8..15], with their 16-element sums and group scales.
+    const bool active = FMT == kQ6_K ? true : lane < (p.K >> 7);
     uint4 x[16];
     uint4 sv = make_uint4(0u, 0u, 0u, 0u);
     float xs = 0.f;
-    {
+    int sx6[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    float xs6[2] = {0.f, 0.f};
+    const int H6 = lane >> 4, g6 = lane & 15;
+    const bool two = p.K > 2048;  // Q6_K: a second slice
+    if constexpr (FMT == kQ6_K) {
+#pragma unroll
+        for (int sl = 0; sl < 2; ++sl) {
+            const int gg = (sl && two) ? 16 + g6 : g6;  // without a second slice the loads repeat the first (scale 0)
+            const uint32_t xg = sbase + kXrOffX + (uint32_t)(gg * kXGroupStride + 32 * H6);
+            x[8 * sl + 0] = lds128i<0>(xg);   x[8 * sl + 1] = lds128i<16>(xg);
+            x[8 * sl + 2] = lds128i<64>(xg);  x[8 * sl + 3] = lds128i<80>(xg);
+            x[8 * sl + 4] = lds128i<128>(xg); x[8 * sl + 5] = lds128i<144>(xg);
+            x[8 * sl + 6] = lds128i<192>(xg); x[8 * sl + 7] = lds128i<208>(xg);
+            if (sl == 0 || two) {
+#pragma unroll
+                for (int Q = 0; Q < 4; ++Q) sx6[sl][Q] = (int)lds32i<0>(sbase + kXrOffSums + (uint32_t)((8 * gg + 2 * Q + H6) * 4));
+                xs6[sl] = __uint_as_float(lds32i<0>(sbase + kXrOffScale + (uint32_t)gg * 4u));
+            }
+        }
+    } else {
         const uint32_t xg = sbase + kXrOffX + (uint32_t)((active ? lane : 0) * kXGroupStride);
         x[0] = lds128i<0>(xg); x[1] = lds128i<16>(xg); x[2] = lds128i<32>(xg); x[3] = lds128i<48>(xg);
         x[4] = lds128i<64>(xg); x[5] = lds128i<80>(xg); x[6] = lds128i<96>(xg); x[7] = lds128i<112>(xg);
@@ -254,7 +346,7 @@ __global__ void __launch_bounds__(CW * 32, 1) gemv_xr_q4k_kernel(const __grid_co
     TRACE_STAMP(tid == 0, 3);
 
     // the lane's half block inside a row: block lane / 2, half lane % 2 (inactive lanes read block 0, scale 0)
-    const uint32_t lane_off = active ? (uint32_t)(lane >> 1) * 144u : 0u;
+    const uint32_t lane_off = FMT == kQ6_K ? 0u : (active ? (uint32_t)(lane >> 1) * 144u : 0u);
     const int hb = lane & 1;
     bool live = true;
     // Deferred reduction: the lanes' partial sums of up to four items (eight rows) are kept and
@@ -275,8 +367,25 @@ __global__ void __launch_bounds__(CW * 32, 1) gemv_xr_q4k_kernel(const __grid_co
             const int row = 2 * (pair_first + i);
             const uint32_t prA = ring + (uint32_t)slot * slot_bytes + lane_off;
             const uint32_t prB = (row + 1 < p.N) ? prA + (uint32_t)p.row_bytes : prA;  // odd row count: the sum is dropped
-            a0 = xr_row(prA, hb, x, sv, xs);
-            a1 = xr_row(prB, hb, x, sv, xs);
+            if constexpr (FMT == kQ6_K) {
+                const uint32_t rA = prA - lane_off, rB = prB - lane_off;  // row bases
+                const uint4(&xa)[8] = *reinterpret_cast<const uint4(*)[8]>(&x[0]);
+                const uint4(&xb)[8] = *reinterpret_cast<const uint4(*)[8]>(&x[8]);
+                float d;
+                float g0 = xr_q6k_row(rA, g6, H6, xa, sx6[0], d);
+                a0 = fmaf(d * xs6[0], g0, 0.f);
+                g0 = xr_q6k_row(rB, g6, H6, xa, sx6[0], d);
+                a1 = fmaf(d * xs6[0], g0, 0.f);
+                if (two) {
+                    g0 = xr_q6k_row(rA, 16 + g6, H6, xb, sx6[1], d);
+                    a0 = fmaf(d * xs6[1], g0, a0);
+                    g0 = xr_q6k_row(rB, 16 + g6, H6, xb, sx6[1], d);
+                    a1 = fmaf(d * xs6[1], g0, a1);
+                }
+            } else {
+                a0 = xr_row(prA, hb, x, sv, xs);
+                a1 = xr_row(prB, hb, x, sv, xs);
+            }
             // the slot's bytes are in registers (the sums above depend on every load): refill it
             asm volatile("" ::"f"(a0), "f"(a1) : "memory");
             __syncwarp();
@@ -339,15 +448,17 @@ void xr_set_enabled(int v) { g_opt_xr = v < 0 ? 0 : (v > 2 ? 2 : v); }
 int xr_get_enabled() { return g_opt_xr; }
 int dp_get_wait_limit_us();
 
-// Launches the activation-resident kernel when the call qualifies (*taken = true): Q4_K, one
-// activation row, K a multiple of 256 and at most 4096, 16-byte aligned weights.
-template <int CW>
+// Launches the activation-resident kernel when the call qualifies (*taken = true): Q4_K (K a multiple of
+// 256, at most 4096) or Q6_K (K = 2048 or 4096), one activation row, 16-byte aligned weights.
+template <int FMT, int CW>
 static int launch_gemv_xr_cw(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N, int K,
                    int sms, int* status, cudaStream_t st, bool* taken) {
     *taken = false;
-    if (!g_opt_xr || fmt != kQ4_K || M != 1 || K % 256 != 0 || K > kXrMaxK || K < 256 || N < 1) return B200Q_OK;
-    // measured crossovers (see the head of this file); very long streams run a few percent faster in gemv_dp.cu
-    if (g_opt_xr == 1 && ((N > 3072 && N < 10240) || N > 65536)) return B200Q_OK;
+    if (!g_opt_xr || fmt != FMT || M != 1 || K % 256 != 0 || K > kXrMaxK || K < 256 || N < 1) return B200Q_OK;
+    if (FMT == kQ6_K && K != 2048 && K != 4096) return B200Q_OK;  // whole slices of 2048 elements
+    // measured crossovers (see the head of this file); very long Q4_K streams run a few percent faster in gemv_dp.cu
+    if (g_opt_xr == 1 && FMT == kQ4_K && ((N > 3072 && N < 10240) || N > 65536)) return B200Q_OK;
+    if (g_opt_xr == 1 && FMT == kQ6_K && N < 8192) return B200Q_OK;
     if ((reinterpret_cast<uintptr_t>(W) & 15) != 0) return B200Q_OK;
     XrParams p = {};
     p.W = static_cast<const uint8_t*>(W);
@@ -359,7 +470,7 @@ static int launch_gemv_xr_cw(int fmt, const void* W, const void* X, int x_dtype,
     p.K = K;
     p.x_dtype = x_dtype;
     p.y_dtype = y_dtype;
-    p.row_bytes = (K / 256) * 144;
+    p.row_bytes = (K / 256) * (FMT == kQ6_K ? 210 : 144);
     const int pairs = (N + 1) / 2;
     int grid = stream_get_option(3) > 0 ? stream_get_option(3) : sms;
     if (grid > pairs) grid = pairs;
@@ -383,7 +494,7 @@ static int launch_gemv_xr_cw(int fmt, const void* W, const void* X, int x_dtype,
     p.trace = dp_trace_next(grid);
 #endif
     const size_t smem = kXrFixedSmem + (size_t)slots * slot;
-    auto kern = gemv_xr_q4k_kernel<CW>;
+    auto kern = gemv_xr_kernel<FMT, CW>;
     static bool configured[64] = {};
     int dev = 0;
     B200Q_CUDA_TRY(cudaGetDevice(&dev));
@@ -411,7 +522,8 @@ static int launch_gemv_xr_cw(int fmt, const void* W, const void* X, int x_dtype,
 
 int launch_gemv_xr(int fmt, const void* W, const void* X, int x_dtype, const void* bias, void* Y, int y_dtype, int M, int N, int K,
                    int sms, int* status, cudaStream_t st, bool* taken) {
-    return launch_gemv_xr_cw<16>(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, status, st, taken);
+    if (fmt == kQ6_K) return launch_gemv_xr_cw<kQ6_K, 16>(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, status, st, taken);
+    return launch_gemv_xr_cw<kQ4_K, 16>(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, sms, status, st, taken);
 }
 
 }  // namespace b200q

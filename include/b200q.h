@@ -278,7 +278,7 @@ int b200q_device_status(int* status_out);
  *                 one pipeline with 32-row tiles; "gemv_split_full" (Q6_K only) -1 = automatic, 0 = one full
  *                 barrier per stage, 1 = one per consumer warp and stage
  *   "gemm_pair"   0 = one-CTA tcgen05 kernel, otherwise the CTA-pair kernel (default)
- *   "gemv_xr"     Q4_K, one activation row, K <= 4096: 1 = the activation-resident kernel where it is the
+ *   "gemv_xr"     Q4_K / Q6_K, one activation row, K <= 4096: 1 = the activation-resident kernel where it is the
  *                 faster one (default), 2 = for every such call, 0 = never
  *   "gemv_i8"     Q8_0 / Q4_K, 2..8 activation rows, K = 2048 / 4096: 1 = the integer tensor-core kernel where it is
  *                 the faster one (default), 2 = for every such call, 0 = never

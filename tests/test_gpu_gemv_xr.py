@@ -1,4 +1,4 @@
-"""The activation-resident Q4_K decode GEMV (csrc/gemv_xr.cu) against the CPU oracle and against the
+"""The activation-resident Q4_K / Q6_K decode GEMV (csrc/gemv_xr.cu) against the CPU oracle and against the
 16-row-tile kernel it stands in for: same arithmetic, so the two must agree bit for bit, for every
 element type, with and without bias, on ragged row counts (odd, fewer pairs than warps, fewer than
 SMs) and short rows (K < 4096 leaves lanes without a group)."""
@@ -22,25 +22,28 @@ def xr_option():
     ops.set_option("pdl", 0)
 
 
+Q6_SHAPES = [(1, 2048), (2, 4096), (31, 2048), (600, 4096), (1025, 4096), (4736, 4096), (16032, 4096)]
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("N,K", SHAPES)
-def test_xr_matches_oracle_and_tile_kernel_bit_for_bit(N, K, xr_option):
+@pytest.mark.parametrize("fmt,N,K", [(synth.Q4_K, n, k) for n, k in SHAPES] + [(synth.Q6_K, n, k) for n, k in Q6_SHAPES])
+def test_xr_matches_oracle_and_tile_kernel_bit_for_bit(fmt, N, K, xr_option):
     ops = xr_option
     cpu = oracle.cpu()
-    Wh = synth.make_blocks(synth.Q4_K, N, K, seed=N + K)
+    Wh = synth.make_blocks(fmt, N, K, seed=N + K)
     Xh = synth.make_activations(1, K, seed=K)
     bh = synth.make_activations(1, N, seed=7).reshape(-1)
     W, X, b = torch.from_numpy(Wh).cuda(), torch.from_numpy(Xh).cuda(), torch.from_numpy(bh).cuda()
-    want = cpu.matmul(synth.Q4_K, Wh, Xh, threads=8)
+    want = cpu.matmul(fmt, Wh, Xh, threads=8)
     for dt in (torch.float32, torch.float16, torch.bfloat16):
         for bias in (None, b.to(dt)):
             got = {}
             for xr in (0, 2):
                 ops.set_option("gemv_xr", xr)
-                got[xr] = ops.gemv(synth.Q4_K, W, X.to(dt), N, bias=bias, out_dtype=dt).float().cpu().numpy()
+                got[xr] = ops.gemv(fmt, W, X.to(dt), N, bias=bias, out_dtype=dt).float().cpu().numpy()
             assert np.array_equal(got[0], got[2]), f"{dt} bias={bias is not None}: kernels differ"
     ops.set_option("gemv_xr", 2)
-    y = ops.gemv(synth.Q4_K, W, X, N).cpu().numpy()
+    y = ops.gemv(fmt, W, X, N).cpu().numpy()
     assert oracle.rel_l2(y, want) < 2e-3  # tolerance of the decode GEMV against the FP32 oracle
     assert ops.device_status() == 0
 
