@@ -199,7 +199,7 @@ def lm_head_summary(extras, world):
         return None
     fused = lh.get("fused") or {}
     out = {"workload": "Q6_K 128256x4096 LM head, M=1, vocab rows split over the ranks (strong scaling)", "n_gpus": world,
-           "variant": "one kernel: shard GEMV + peer stores + arrival words" if "us_per_token" in fused else "shard GEMV + NCCL all-gather",
+           "variant": "one kernel: shard GEMV whose CTAs send their rows as self-validating words and receive the peers' slices" if "us_per_token" in fused else "shard GEMV + NCCL all-gather",
            "us_per_token": fused.get("us_per_token", lh.get("us_per_token")),
            "tok_per_s": fused.get("tok_per_s", lh.get("tok_per_s")),
            "nccl_all_gather_us_per_token": lh.get("us_per_token"), "shard_gemv_only_us": lh.get("gemv_only_us"),
