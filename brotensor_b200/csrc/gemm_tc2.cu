@@ -320,15 +320,20 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
 #pragma unroll
         for (int i = 0; i < 3; ++i) c8[i] = c8n[i] = make_uint4(0, 0, 0, 0);
         if constexpr (FMT == kQ8_0) q8_load(0, c8n);
-        // Q6_K: the thread's quad of the next stage, loaded one stage ahead. Blocks are 210 bytes and
-        // only 2-byte aligned: the 32 nibble bytes and the 32 high-bit bytes the quad needs are read
+        // Q6_K: the thread's two quads of the next PAIR of stages, loaded one pair ahead. Stages 2j and
+        // 2j + 1 of a block decode quads H and 2 + H of group j: the low and the high nibbles of the
+        // same 32 bytes, and two bit pairs of the same 32 high-bit bytes - loaded once for both (loaded
+        // per stage, these reads, 3.7 times the bytes a stage holds, were most of the L2 -> SM traffic
+        // beside the activation slabs, and that traffic is what bounds the kernel). Blocks are 210
+        // bytes and only 2-byte aligned: the 32 nibble bytes and the 32 high-bit bytes are read
         // as three 16-byte words each from the 16-byte boundary at or before the block (both
         // regions start on a multiple of 32 bytes inside the block, so 48 bytes from the boundary
         // cover them for any alignment); `f6` keeps the block's byte offset from that boundary.
+        // `S` holds the scales of quad H in its low half and those of quad 2 + H in its high half.
         uint4 l6[3], h6[3], l6n[3], h6n[3];
         uint32_t s6 = 0, d6 = 0, f6 = 0, s6n = 0, d6n = 0, f6n = 0;
         auto q6_load = [&](int kbb, uint4 (&L)[3], uint4 (&Hh)[3], uint32_t& S, uint32_t& D, uint32_t& F) {
-            const int blk = kbb >> 2, P = kbb & 3, grp = P >> 1, quad = 2 * (P & 1) + H;
+            const int blk = kbb >> 2, grp = (kbb & 3) >> 1;  // kbb is even
             if constexpr (FMT == kQ6_KP) {
                 // regrouped by field in runs of eight blocks: both 32-byte pieces are 16-byte aligned
                 const uint8_t* run = rowp + (size_t)(blk >> 3) * kQ6RunBytes;
@@ -337,7 +342,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                 const uint4* ah = reinterpret_cast<const uint4*>(run + 1024 + s * 64 + 32 * grp);
                 L[0] = __ldg(al); L[1] = __ldg(al + 1);
                 Hh[0] = __ldg(ah); Hh[1] = __ldg(ah + 1);
-                S = __ldg(reinterpret_cast<const unsigned short*>(run + 1536 + s * 16 + grp * 8 + quad * 2));
+                S = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(run + 1536 + s * 16 + grp * 8 + H * 2)) |
+                    (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(run + 1536 + s * 16 + grp * 8 + 4 + H * 2)) << 16;
                 D = __ldg(reinterpret_cast<const unsigned short*>(run + 1664 + 2 * s));
                 F = 0;
                 return;
@@ -349,7 +355,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
             for (int i = 0; i < 3; ++i) L[i] = __ldg(al + 4 * grp + 2 * H + i);
 #pragma unroll
             for (int i = 0; i < 3; ++i) Hh[i] = __ldg(al + 8 + 2 * grp + i);
-            S = __ldg(reinterpret_cast<const unsigned short*>(b0 + 192 + grp * 8 + quad * 2));
+            S = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(b0 + 192 + grp * 8 + H * 2)) |
+                (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(b0 + 192 + grp * 8 + 4 + H * 2)) << 16;
             D = __ldg(reinterpret_cast<const unsigned short*>(b0 + 208));
         };
 #pragma unroll
@@ -357,10 +364,12 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
         if constexpr (FMT == kQ6_K || FMT == kQ6_KP) q6_load(0, l6n, h6n, s6n, d6n, f6n);
         for (int kb = 0; kb < n_kb; ++kb) {
             if constexpr (FMT == kQ6_K || FMT == kQ6_KP) {
+                if ((kb & 1) == 0) {
 #pragma unroll
-                for (int i = 0; i < 3; ++i) { l6[i] = l6n[i]; h6[i] = h6n[i]; }
-                s6 = s6n; d6 = d6n; f6 = f6n;
-                if (kb + 1 < n_kb) q6_load(kb + 1, l6n, h6n, s6n, d6n, f6n);
+                    for (int i = 0; i < 3; ++i) { l6[i] = l6n[i]; h6[i] = h6n[i]; }
+                    s6 = s6n; d6 = d6n; f6 = f6n;
+                    if (kb + 2 < n_kb) q6_load(kb + 2, l6n, h6n, s6n, d6n, f6n);
+                }
             }
             if constexpr (FMT == kQ8_0) {
 #pragma unroll
@@ -422,7 +431,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                         case 2: for (int i = 0; i < 8; ++i) { ql[i] = __funnelshift_r(wl[2 + i], wl[3 + i], bits); qh[i] = __funnelshift_r(wh[2 + i], wh[3 + i], bits); } break;
                         default: for (int i = 0; i < 8; ++i) { ql[i] = __funnelshift_r(wl[3 + i], wl[4 + i], bits); qh[i] = __funnelshift_r(wh[3 + i], wh[4 + i], bits); } break;
                     }
-                    q6k_quad_to_smem(ql, qh, s6, d6, 2 * (kb & 1) + H, rowaddr, r7, H);
+                    q6k_quad_to_smem(ql, qh, (kb & 1) ? s6 >> 16 : s6, d6, 2 * (kb & 1) + H, rowaddr, r7, H);
                 }
                 fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor cores of the pair
             }
