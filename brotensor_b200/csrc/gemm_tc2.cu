@@ -95,31 +95,44 @@ __device__ __forceinline__ uint32_t instr_desc_pair(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
-// Pair P of a Q4_K block held in registers: low nibbles are sub-block 2P (k 0..31 of the
-// stage), high nibbles sub-block 2P+1 (k 32..63). Thread half H = 0 writes the low-nibble
-// sub-block (16-byte chunks 0..3 of the row), H = 1 the high-nibble one (chunks 4..7).
+// Pair P of a Q4_K block: its 32 quant bytes hold sub-block 2P in the low nibbles (k 0..31 of the
+// stage) and sub-block 2P+1 in the high ones (k 32..63). The row's two threads split the BYTES: thread
+// half H holds bytes 16H .. 16H+15 of every pair (`blk[1 + P]`, beside the 16-byte header `blk[0]`),
+// so together they load each byte of the block once, and H writes k 16H .. 16H+15 (16-byte chunks
+// 2H, 2H+1 of the row) from the low nibbles and k 32+16H .. (chunks 4+2H, 5+2H) from the high ones.
 template <int P>
-__device__ __forceinline__ void q4k_half_to_smem(const uint4 (&blk)[9], uint32_t rowaddr, uint32_t r7, int H) {
+__device__ __forceinline__ void q4k_split_to_smem(const uint4 (&blk)[5], uint32_t rowaddr, uint32_t r7, int H) {
     const uint4 h = blk[0];
-    uint32_t sc, m;
+    uint32_t sc0, m0, sc1, m1;
     if constexpr (P < 2) {
-        sc = (h.y >> (16 * P + 8 * H)) & 63u;
-        m = (h.z >> (16 * P + 8 * H)) & 63u;
+        sc0 = (h.y >> (16 * P)) & 63u;
+        m0 = (h.z >> (16 * P)) & 63u;
+        sc1 = (h.y >> (16 * P + 8)) & 63u;
+        m1 = (h.z >> (16 * P + 8)) & 63u;
     } else {
-        const int J = 2 * (P - 2) + H;
-        sc = ((h.w >> (8 * J)) & 0xFu) | (((h.y >> (8 * J + 6)) & 3u) << 4);
-        m = ((h.w >> (8 * J + 4)) & 0xFu) | (((h.z >> (8 * J + 6)) & 3u) << 4);
+        constexpr int J = 2 * (P - 2);
+        sc0 = ((h.w >> (8 * J)) & 0xFu) | (((h.y >> (8 * J + 6)) & 3u) << 4);
+        m0 = ((h.w >> (8 * J + 4)) & 0xFu) | (((h.z >> (8 * J + 6)) & 3u) << 4);
+        sc1 = ((h.w >> (8 * J + 8)) & 0xFu) | (((h.y >> (8 * J + 14)) & 3u) << 4);
+        m1 = ((h.w >> (8 * J + 12)) & 0xFu) | (((h.z >> (8 * J + 14)) & 3u) << 4);
     }
-    const float ds = h2f(h.x & 0xFFFFu) * (float)sc, dm = h2f(h.x >> 16) * (float)m;
-    const uint4 qa = blk[1 + 2 * P], qb = blk[2 + 2 * P];
-    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-    const uint32_t sh = 4u * (uint32_t)H;
+    const float d = h2f(h.x & 0xFFFFu), dmin = h2f(h.x >> 16);
+    const float ds0 = d * (float)sc0, dm0 = dmin * (float)m0, ds1 = d * (float)sc1, dm1 = dmin * (float)m1;
+    const uint4 q = blk[1 + P];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
         uint4 o;
-        nib4_to_h2((w[2 * c] >> sh) & 0x0F0F0F0Fu, ds, dm, o.x, o.y);
-        nib4_to_h2((w[2 * c + 1] >> sh) & 0x0F0F0F0Fu, ds, dm, o.z, o.w);
-        sts128(rowaddr + (((uint32_t)(c + 4 * H) ^ r7) << 4), o);
+        nib4_to_h2(w[2 * c] & 0x0F0F0F0Fu, ds0, dm0, o.x, o.y);
+        nib4_to_h2(w[2 * c + 1] & 0x0F0F0F0Fu, ds0, dm0, o.z, o.w);
+        sts128(rowaddr + (((uint32_t)(c + 2 * H) ^ r7) << 4), o);
+    }
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        uint4 o;
+        nib4_to_h2((w[2 * c] >> 4) & 0x0F0F0F0Fu, ds1, dm1, o.x, o.y);
+        nib4_to_h2((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, ds1, dm1, o.z, o.w);
+        sts128(rowaddr + (((uint32_t)(4 + c + 2 * H) ^ r7) << 4), o);
     }
 }
 // One Q8_0 block (FP16 d + 32 int8) held as the nine aligned words that cover it: an even block
@@ -299,15 +312,19 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
         int slot = 0;
         uint32_t phase = 0;
         bool live = true;
-        // The row's Q4_K block for the next four stages is loaded into registers one block ahead
+        // This thread's share of the row's Q4_K block for the next four stages (the header and bytes
+        // 16H .. 16H+15 of each of the four 32-byte pairs) is loaded into registers one block ahead
         // of its use, so its latency (an L2 or DRAM round trip) hides behind four stages of decode.
-        uint4 cur[9], nxt[9];
+        uint4 cur[5], nxt[5];
 #pragma unroll
-        for (int i = 0; i < 9; ++i) cur[i] = nxt[i] = make_uint4(0, 0, 0, 0);
-        if constexpr (FMT == kQ4_K) {
+        for (int i = 0; i < 5; ++i) cur[i] = nxt[i] = make_uint4(0, 0, 0, 0);
+        auto q4_load = [&](int b, uint4 (&dst)[5]) {
+            const uint4* src = reinterpret_cast<const uint4*>(rowp + (size_t)b * 144);
+            dst[0] = __ldg(src);
 #pragma unroll
-            for (int i = 0; i < 9; ++i) nxt[i] = __ldg(reinterpret_cast<const uint4*>(rowp) + i);
-        }
+            for (int i = 0; i < 4; ++i) dst[1 + i] = __ldg(src + 1 + 2 * i + H);
+        };
+        if constexpr (FMT == kQ4_K) q4_load(0, nxt);
         // Q8_0: eight blocks (256 k, 272 bytes = 17 x 16) form a 16-byte aligned chunk. The thread's
         // block of stage P = kb & 3 is block 2P + H of the chunk: it lies inside the three 16-byte
         // words 4P + 2H .. +2, starting at byte 4P + 2H of them. They are loaded one stage ahead.
@@ -380,11 +397,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                 if ((kb & 3) == 0) {
                     const int b = kb >> 2;
 #pragma unroll
-                    for (int i = 0; i < 9; ++i) cur[i] = nxt[i];
-                    if (b + 1 < n_blk) {
-#pragma unroll
-                        for (int i = 0; i < 9; ++i) nxt[i] = __ldg(reinterpret_cast<const uint4*>(rowp + (size_t)(b + 1) * 144) + i);
-                    }
+                    for (int i = 0; i < 5; ++i) cur[i] = nxt[i];
+                    if (b + 1 < n_blk) q4_load(b + 1, nxt);
                 }
             }
             if (live) {
@@ -395,10 +409,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                 const uint32_t rowaddr = sbase + slot * (kGemmRows * 128) + row_off;
                 if constexpr (FMT == kQ4_K) {
                     switch (kb & 3) {
-                        case 0: q4k_half_to_smem<0>(cur, rowaddr, r7, H); break;
-                        case 1: q4k_half_to_smem<1>(cur, rowaddr, r7, H); break;
-                        case 2: q4k_half_to_smem<2>(cur, rowaddr, r7, H); break;
-                        default: q4k_half_to_smem<3>(cur, rowaddr, r7, H); break;
+                        case 0: q4k_split_to_smem<0>(cur, rowaddr, r7, H); break;
+                        case 1: q4k_split_to_smem<1>(cur, rowaddr, r7, H); break;
+                        case 2: q4k_split_to_smem<2>(cur, rowaddr, r7, H); break;
+                        default: q4k_split_to_smem<3>(cur, rowaddr, r7, H); break;
                     }
                 } else if constexpr (FMT == kQ8_0) {
                     const uint32_t w12[12] = {c8[0].x, c8[0].y, c8[0].z, c8[0].w, c8[1].x, c8[1].y, c8[1].z, c8[1].w,
