@@ -28,6 +28,8 @@ int launch_gemv_dp_swiglu(int fmt, const void* Wg, const void* Wu, const void* X
 void stream_set_option(int which, int value);
 void gemm_set_pair(int v);
 int gemm_get_pair();
+void gemm_set_split(int v);
+int gemm_get_split();
 void dp_set_groups(int v);
 void dp_set_tile_pairs(int v);
 void dp_set_split_full(int v);
@@ -503,6 +505,7 @@ int b200q_set_option(const char* key, int value) {
     else if (!strcmp(key, "gemv_tile_pairs")) dp_set_tile_pairs(value);
     else if (!strcmp(key, "gemv_split_full")) dp_set_split_full(value);
     else if (!strcmp(key, "gemm_pair")) gemm_set_pair(value);
+    else if (!strcmp(key, "gemm_split")) gemm_set_split(value);
     else if (!strcmp(key, "wait_limit_us")) dp_set_wait_limit_us(value);
     else if (!strcmp(key, "gemv_lean")) dp_set_lean(value);
     else if (!strcmp(key, "gemv_xr")) xr_set_enabled(value);
@@ -524,6 +527,7 @@ int b200q_get_option(const char* key, int* out) {
     else if (!strcmp(key, "gemv_i8")) *out = i8_get_enabled();
     else if (!strcmp(key, "gemv_tile_pairs")) *out = dp_get_tile_pairs();
     else if (!strcmp(key, "gemm_pair")) *out = gemm_get_pair();
+    else if (!strcmp(key, "gemm_split")) *out = gemm_get_split();
     else if (!strcmp(key, "wait_limit_us")) *out = dp_get_wait_limit_us();
     else return fail(B200Q_ERR_BAD_ARG, "get_option: unknown key '%s'", key);
     return B200Q_OK;

@@ -47,6 +47,8 @@ static int static_scratch(void** out) {
     return B200Q_OK;
 }
 
+size_t gemm_tc_workspace_min_bytes(int fmt, int x_dtype, int M, int N, int K);
+
 }  // namespace b200q
 
 extern "C" {
@@ -57,7 +59,9 @@ int b200q_gemm_static(int fmt, const void* W, const void* X, int x_dtype, const 
                       int N, int K, void* stream) {
     using namespace b200q;
     // Size check first, so that an oversized request fails the same way with or without a device.
-    const size_t need = b200q_gemm_workspace_bytes(fmt, x_dtype, M, N, K);
+    // (the activation image alone: where b200q_gemm would split K through a larger workspace, it runs
+    // unsplit in whatever part of the array the image leaves, or split if the partial sums fit too)
+    const size_t need = gemm_tc_workspace_min_bytes(fmt, x_dtype, M, N, K);
     if (need > kStaticScratchBytes)
         return fail(B200Q_ERR_WORKSPACE,
                     "gemm_static: M %d x K %d needs %zu bytes of scratch, the built-in array holds %zu; "

@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
 static int round_up16(int v) { return (v + 15) & ~15; }
 
 int launch_gemm_pair_pass(int fmt, const void* W, const uint8_t* Xp, int tok_stride, const void* bias, int bias_dtype,
-                          void* Y, int y_dtype, int tokens, int N, int K, int* status, cudaStream_t st);
+                          void* Y, int y_dtype, int tokens, int N, int K, int n_split, float* ypart, int* status, cudaStream_t st);
 // non-zero: passes run on CTA pairs (gemm_tc2.cu, the default); 0: one CTA per 128 weight rows
 // (this file; kept as the reference the pair kernel is compared with bit for bit)
 static int g_gemm_pair = -1;
@@ -213,10 +213,36 @@ static bool gemm_tc_takes(int fmt, const void* W, int M, int K) {
     return fmt == kQ4_K || fmt == kQ6_K || fmt == kQ8_0;
 }
 
-size_t gemm_tc_workspace_bytes(int fmt, int x_dtype, int M, int N, int K) {
+// Split K. A pass runs one CTA pair per 256 weight rows: 4096 rows are 16 pairs on 32 of the 148 SMs.
+// With at most half of the SMs busy the k-blocks of a row tile are split over up to eight pairs
+// (equal shares, whole 256-element blocks, at least eight k-blocks each); the partial sums go through
+// the workspace and are added in a fixed order. 1 = no split.
+static int g_gemm_split = 1;
+void gemm_set_split(int v) { g_gemm_split = v ? 1 : 0; }
+int gemm_get_split() { return g_gemm_split; }
+static int gemm_split_factor(int fmt, int N, int K) {
+    if (!g_gemm_split || g_gemm_pair == 0 || N % 4 != 0) return 1;
+    const int pairs = ((N + kGemmRows - 1) / kGemmRows + 1) / 2, n_kb = K / kBK;
+    if (pairs > 37) return 1;
+    int s = 74 / pairs;
+    if (s > 8) s = 8;
+    while (s > 1 && (n_kb % (4 * s) != 0 || n_kb / s < 8)) --s;
+    return s;
+}
+static size_t gemm_xp_bytes(int M, int K) { return ((size_t)(K / kBK) * (size_t)round_up16(M) * 128u + 255u) & ~(size_t)255u; }
+
+// What a call needs at least (the activation image) and what it asks for (with room for the partial
+// sums of a split K; given less, the call runs unsplit).
+size_t gemm_tc_workspace_min_bytes(int fmt, int x_dtype, int M, int N, int K) {
     (void)x_dtype; (void)N;
     if (!gemm_tc_takes(fmt, nullptr, M, K)) return 0;
-    return (size_t)(K / kBK) * (size_t)round_up16(M) * 128u;
+    return gemm_xp_bytes(M, K);
+}
+size_t gemm_tc_workspace_bytes(int fmt, int x_dtype, int M, int N, int K) {
+    (void)x_dtype;
+    if (!gemm_tc_takes(fmt, nullptr, M, K)) return 0;
+    const int s = gemm_split_factor(fmt, N, K);
+    return gemm_xp_bytes(M, K) + (s > 1 ? (size_t)s * (size_t)(M < kMaxTokens ? M : kMaxTokens) * N * sizeof(float) : 0);
 }
 
 template <int FMT>
@@ -240,7 +266,8 @@ int launch_gemm_tc(int fmt, const void* W, const void* X, int x_dtype, const voi
     (void)sms;
     *taken = gemm_tc_takes(fmt, W, M, K);
     if (!*taken) return B200Q_OK;
-    const size_t need = gemm_tc_workspace_bytes(fmt, x_dtype, M, N, K);
+    const size_t need = gemm_tc_workspace_min_bytes(fmt, x_dtype, M, N, K);
+    const int n_split = ws && ws_bytes >= gemm_tc_workspace_bytes(fmt, x_dtype, M, N, K) ? gemm_split_factor(fmt, N, K) : 1;
     if (!ws || ws_bytes < need) return fail(B200Q_ERR_WORKSPACE, "gemm: workspace of %zu bytes needed, %zu given", need, ws ? ws_bytes : (size_t)0);
     if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(B200Q_ERR_WORKSPACE, "gemm: workspace must be 256-byte aligned");
     const int tok_total = round_up16(M);
@@ -259,7 +286,8 @@ int launch_gemm_tc(int fmt, const void* W, const void* X, int x_dtype, const voi
         if (g_gemm_pair != 0) {
             const int tokens = M - t0 < kMaxTokens ? M - t0 : kMaxTokens;
             if (int rc = launch_gemm_pair_pass(fmt, W, static_cast<const uint8_t*>(ws) + (size_t)t0 * 128u, tok_total, bias, x_dtype,
-                                               static_cast<char*>(Y) + (size_t)t0 * N * ysz, y_dtype, tokens, N, K, status, st))
+                                               static_cast<char*>(Y) + (size_t)t0 * N * ysz, y_dtype, tokens, N, K, n_split,
+                                               reinterpret_cast<float*>(static_cast<char*>(ws) + gemm_xp_bytes(M, K)), status, st))
                 return rc;
             continue;
         }

@@ -45,6 +45,11 @@ struct PairParams {
     int n_a, n_b;        // ring depths in k-blocks: decoded weights (16 KB slots) and slabs; n_b <= n_a
     int g_bytes;         // bytes of one token group's half in a slab slot: (min(tok_pad, 256) / 2) * 128
     int b_bytes;         // one slab slot of this CTA: g_bytes * groups
+    // Split K (few row tiles, long rows): blockIdx.y = s works on k-blocks [s * kb_split, (s + 1) * kb_split) and
+    // writes its FP32 partial sums, without bias, to Ypart[s][token][N]; a second kernel adds them up in order.
+    int n_split, kb_split;
+    size_t w_split_bytes;  // bytes of kb_split k-blocks of one weight row
+    float* Ypart;
 };
 
 // ---- cluster / cta_group::2 wrappers ----------------------------------------------------------
@@ -199,7 +204,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t crank = cluster_ctarank();         // 0 = leader
     const int row0 = blockIdx.x * kGemmRows;          // the pair's CTAs own consecutive row tiles
-    const int n_kb = p.K / kBK;
+    const int n_kb = p.n_split > 1 ? p.kb_split : p.K / kBK;  // k-blocks of this CTA; its first one is blockIdx.y * kb_split
     const uint32_t tmem_cols = p.tok_pad <= 32 ? 32u : p.tok_pad <= 64 ? 64u : p.tok_pad <= 128 ? 128u : p.tok_pad <= 256 ? 256u : 512u;
     // token groups of up to 256: group g is one MMA of N = ng tokens into accumulator columns 256 g ..;
     // this CTA holds tokens [256 g + crank * ng / 2, + ng / 2) of it
@@ -243,7 +248,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                 const uint32_t full = smem_u32(&bar_b_full[bs]);
                 const uint32_t h0 = (uint32_t)(n0 / 2) * 128u, h1 = (uint32_t)(n1 / 2) * 128u;
                 mbar_arrive_expect_tx(full, h0 + h1);
-                const uint8_t* src = p.Xp + (size_t)kb * p.xp_tok_stride * 128u;
+                const uint8_t* src = p.Xp + (size_t)(kb + (int)blockIdx.y * p.kb_split) * p.xp_tok_stride * 128u;
                 const uint32_t dst = b_base + bs * p.b_bytes;
                 bulk_g2s(dst, src + (size_t)crank * h0, h0, full);
                 if (groups == 2) bulk_g2s(dst + p.g_bytes, src + 256u * 128u + (size_t)crank * h1, h1, full);
@@ -305,7 +310,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
         const int H = (warp - kPairCtrlWarps) >> 2;
         const int pt = (warp & 3) * 32 + lane;                   // tile row = TMEM lane of this thread
         const int wrow = min(row0 + pt, p.N - 1);                // rows past N decode row N-1, never stored
-        const uint8_t* rowp = p.W + (size_t)wrow * p.row_bytes;
+        const uint8_t* rowp = p.W + (size_t)wrow * p.row_bytes + (size_t)blockIdx.y * p.w_split_bytes;
         const uint32_t r7 = (uint32_t)(pt & 7);
         const uint32_t row_off = (uint32_t)((pt >> 3) * 1024 + (pt & 7) * 128);
         const int n_blk = p.K / 256;
@@ -378,14 +383,15 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
         };
 #pragma unroll
         for (int i = 0; i < 3; ++i) l6[i] = h6[i] = l6n[i] = h6n[i] = make_uint4(0, 0, 0, 0);
-        if constexpr (FMT == kQ6_K || FMT == kQ6_KP) q6_load(0, l6n, h6n, s6n, d6n, f6n);
+        const int kb0 = (int)blockIdx.y * p.kb_split;  // Q6_K addresses its blocks by the k-block's number in the whole row
+        if constexpr (FMT == kQ6_K || FMT == kQ6_KP) q6_load(kb0, l6n, h6n, s6n, d6n, f6n);
         for (int kb = 0; kb < n_kb; ++kb) {
             if constexpr (FMT == kQ6_K || FMT == kQ6_KP) {
                 if ((kb & 1) == 0) {
 #pragma unroll
                     for (int i = 0; i < 3; ++i) { l6[i] = l6n[i]; h6[i] = h6n[i]; }
                     s6 = s6n; d6 = d6n; f6 = f6n;
-                    if (kb + 2 < n_kb) q6_load(kb + 2, l6n, h6n, s6n, d6n, f6n);
+                    if (kb + 2 < n_kb) q6_load(kb0 + kb + 2, l6n, h6n, s6n, d6n, f6n);
                 }
             }
             if constexpr (FMT == kQ8_0) {
@@ -475,7 +481,12 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
                 uint32_t r[16];
                 tmem_ld16(tlane + (uint32_t)c0, r);
                 tmem_ld_wait();
-                if (n < p.N) {
+                if (n < p.N && p.n_split > 1) {
+                    float* part = p.Ypart + (size_t)blockIdx.y * p.tokens * p.N;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < p.tokens) part[(size_t)(c0 + j) * p.N + n] = __uint_as_float(r[j]);
+                } else if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = c0 + j;
@@ -516,7 +527,7 @@ static int launch_pair_fmt(const PairParams& p, size_t smem, cudaStream_t st) {
     }
     const unsigned tiles = (unsigned)((p.N + kGemmRows - 1) / kGemmRows);
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((tiles + 1u) & ~1u);  // whole pairs; a CTA past the last row tile decodes row N-1 and stores nothing
+    cfg.gridDim = dim3((tiles + 1u) & ~1u, (unsigned)(p.n_split > 1 ? p.n_split : 1));  // whole pairs; a CTA past the last row tile decodes row N-1 and stores nothing
     cfg.blockDim = dim3(kPairThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -531,11 +542,56 @@ static int launch_pair_fmt(const PairParams& p, size_t smem, cudaStream_t st) {
     return B200Q_OK;
 }
 
+// Y[t][n] = bias[n] + part[0][t][n] + part[1][t][n] + ... in that order (the same on every run), four
+// neighbouring n per thread.
+__global__ void __launch_bounds__(256) gemm_split_reduce_kernel(const float* __restrict__ part, int n_split, int tokens, int N,
+                                                                const void* __restrict__ bias, int bias_dtype, void* __restrict__ Y, int y_dtype) {
+    const size_t total = (size_t)tokens * N, quads = total / 4;  // N % 4 == 0 is checked by the caller
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += (size_t)gridDim.x * blockDim.x) {
+        const int n = (int)((4 * i) % (size_t)N);
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (bias) {
+            if (bias_dtype == B200Q_DT_F32) a = *reinterpret_cast<const float4*>(static_cast<const float*>(bias) + n);
+            else if (bias_dtype == B200Q_DT_F16) {
+                const __half* b = static_cast<const __half*>(bias) + n;
+                a = make_float4(__half2float(b[0]), __half2float(b[1]), __half2float(b[2]), __half2float(b[3]));
+            } else {
+                const __nv_bfloat16* b = static_cast<const __nv_bfloat16*>(bias) + n;
+                a = make_float4(__bfloat162float(b[0]), __bfloat162float(b[1]), __bfloat162float(b[2]), __bfloat162float(b[3]));
+            }
+        }
+        // the tensor cores' sum of a split first, then the bias: with one split this is the order of the unsplit epilogue
+        float4 sum = __ldcs(reinterpret_cast<const float4*>(part) + i);
+        for (int s = 1; s < n_split; ++s) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(part + (size_t)s * total) + i);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        sum.x += a.x; sum.y += a.y; sum.z += a.z; sum.w += a.w;
+        if (y_dtype == B200Q_DT_F32) reinterpret_cast<float4*>(Y)[i] = sum;
+        else if (y_dtype == B200Q_DT_F16) {
+            __half2* y = reinterpret_cast<__half2*>(Y) + 2 * i;
+            y[0] = __floats2half2_rn(sum.x, sum.y);
+            y[1] = __floats2half2_rn(sum.z, sum.w);
+        } else {
+            __nv_bfloat162* y = reinterpret_cast<__nv_bfloat162*>(Y) + 2 * i;
+            y[0] = __floats2bfloat162_rn(sum.x, sum.y);
+            y[1] = __floats2bfloat162_rn(sum.z, sum.w);
+        }
+    }
+}
+
 // One pass (<= 512 tokens) of the prefill GEMM on CTA pairs. The caller has run the activation
-// pre-pass; Xp points at this pass's first token row inside the workspace.
+// pre-pass; Xp points at this pass's first token row inside the workspace. n_split > 1: K is split
+// over blockIdx.y and `ypart` (n_split * tokens * N floats) takes the partial sums.
 int launch_gemm_pair_pass(int fmt, const void* W, const uint8_t* Xp, int tok_stride, const void* bias, int bias_dtype,
-                          void* Y, int y_dtype, int tokens, int N, int K, int* status, cudaStream_t st) {
+                          void* Y, int y_dtype, int tokens, int N, int K, int n_split, float* ypart, int* status, cudaStream_t st) {
     PairParams p = {};
+    p.n_split = n_split > 1 ? n_split : 1;
+    p.kb_split = (K / kBK) / p.n_split;
+    // (the Q6_K producers find a block from the k-block's number in the whole row - the regrouped layout has no
+    // per-split row offset - so their row pointer stays put)
+    p.w_split_bytes = (fmt == kQ6_K || fmt == kQ6_KP) ? 0 : (size_t)(p.kb_split * kBK / b200q_block_elems(fmt)) * b200q_block_bytes(fmt);
+    p.Ypart = ypart;
     p.W = static_cast<const uint8_t*>(W);
     p.Xp = Xp;
     p.bias = bias;
@@ -562,10 +618,18 @@ int launch_gemm_pair_pass(int fmt, const void* W, const uint8_t* Xp, int tok_str
     if (p.n_a > kPairMaxStages) p.n_a = kPairMaxStages;
     if (p.n_a < p.n_b) return fail(B200Q_ERR_UNSUPPORTED, "gemm: pair rings do not fit (%d weight slots, %d slab stages)", p.n_a, p.n_b);
     const size_t smem = (size_t)p.n_a * kb_a + (size_t)p.n_b * p.b_bytes + 1024;
-    if (fmt == kQ4_K) return launch_pair_fmt<kQ4_K>(p, smem, st);
-    if (fmt == kQ6_K) return launch_pair_fmt<kQ6_K>(p, smem, st);
-    if (fmt == kQ6_KP) return launch_pair_fmt<kQ6_KP>(p, smem, st);
-    return launch_pair_fmt<kQ8_0>(p, smem, st);
+    int rc;
+    if (fmt == kQ4_K) rc = launch_pair_fmt<kQ4_K>(p, smem, st);
+    else if (fmt == kQ6_K) rc = launch_pair_fmt<kQ6_K>(p, smem, st);
+    else if (fmt == kQ6_KP) rc = launch_pair_fmt<kQ6_KP>(p, smem, st);
+    else rc = launch_pair_fmt<kQ8_0>(p, smem, st);
+    if (rc || p.n_split == 1) return rc;
+    const size_t quads = (size_t)tokens * N / 4;
+    size_t blocks = (quads + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    gemm_split_reduce_kernel<<<(unsigned)blocks, 256, 0, st>>>(ypart, p.n_split, tokens, N, bias, bias_dtype, Y, y_dtype);
+    B200Q_CUDA_TRY(cudaGetLastError());
+    return B200Q_OK;
 }
 
 }  // namespace b200q

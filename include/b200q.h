@@ -210,7 +210,9 @@ int b200q_gemv_shard_topk(int fmt, const void* W_shard, const void* x, int x_dty
  * Prefill GEMM on the tensor cores, any M >= 1:
  *   Y(M,N) = X(M,K) * decode(W(N,K))^T (+ bias(N)),   FP16 operands, FP32 accumulation.
  * `ws` is caller-owned scratch of at least b200q_gemm_workspace_bytes() bytes,
- * 256-byte aligned (it holds the activations converted to the operand layout);
+ * 256-byte aligned (it holds the activations converted to the operand layout
+ * and, for matrices of few rows, whose k range is split over several CTA
+ * pairs, the FP32 partial sums: splits x min(M, 512) x N floats);
  * it may be NULL when that size is 0. Calls that share a workspace must be
  * ordered on one stream.
  * Replaces the tensor-core branch of linear_forward_batched_q4k_fp16 / _q6k_ /
@@ -278,6 +280,9 @@ int b200q_device_status(int* status_out);
  *                 one pipeline with 32-row tiles; "gemv_split_full" (Q6_K only) -1 = automatic, 0 = one full
  *                 barrier per stage, 1 = one per consumer warp and stage
  *   "gemm_pair"   0 = one-CTA tcgen05 kernel, otherwise the CTA-pair kernel (default)
+ *   "gemm_split"  0 = never split K; 1 (default) = matrices whose row tiles occupy at most half of the SMs
+ *                 (N <= 9472) have their k-blocks split over up to eight CTA pairs, partial sums added in a
+ *                 fixed order by a second kernel (b200q_gemm_workspace_bytes() grows accordingly)
  *   "gemv_xr"     Q4_K / Q6_K, one activation row, K <= 4096: 1 = the activation-resident kernel where it is the
  *                 faster one (default), 2 = for every such call, 0 = never
  *   "gemv_i8"     Q8_0 / Q4_K, 2..8 activation rows, K = 2048 / 4096: 1 = the integer tensor-core kernel where it is

@@ -364,6 +364,7 @@ def test_gemm_cta_pair_equals_single_cta(fmt, N, K, M, cpu_oracle):
     xh = synth.make_activations(M, K, seed=M)
     W, X = torch.from_numpy(Wh).cuda(), torch.from_numpy(xh).cuda()
     try:
+        ops.set_option("gemm_split", 0)  # a split K adds the partial sums in another order
         ops.set_option("gemm_pair", 0)
         y0 = ops.gemm(fmt, W, X, N)
         ops.set_option("gemm_pair", 1)
@@ -371,10 +372,51 @@ def test_gemm_cta_pair_equals_single_cta(fmt, N, K, M, cpu_oracle):
         y2 = ops.gemm(fmt, W, X, N)
     finally:
         ops.set_option("gemm_pair", -1)
+        ops.set_option("gemm_split", 1)
     torch.cuda.synchronize()
     assert torch.equal(y1, y2)  # same on every run
     assert torch.equal(y0, y1)
     assert oracle.rel_l2(y1.cpu().numpy(), cpu_oracle.matmul(fmt, Wh, xh, threads=8)) < 2e-3
+    assert ops.device_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt,N,K,M", [(synth.Q4_K, 1024, 1024, 272), (synth.Q4_K, 4096, 4096, 512), (synth.Q6_K, 4096, 14336, 200),
+                                       (synth.Q8_0, 1000, 4096, 64), (synth.Q4_K, 2048, 2048, 600), (synth.Q6_K, 300, 8192, 17)])
+def test_gemm_split_k(fmt, N, K, M, cpu_oracle):
+    """Few row tiles and long rows: the k-blocks of a row tile are split over several CTA pairs and the partial
+    sums added in a fixed order by a second kernel. Same result on every run, equal to the unsplit kernel up
+    to the order of the FP32 additions, within the prefill bound of the oracle; bias and FP16 output included;
+    more than one pass of 512 tokens reuses the partial-sum buffer."""
+    import torch
+    import oracle
+    from brotensor_b200 import _capi
+    Wh = synth.make_blocks(fmt, N, K, seed=N + M)
+    xh = synth.make_activations(M, K, seed=M)
+    bh = synth.make_activations(1, N, seed=5).reshape(-1)
+    W, X, b = torch.from_numpy(Wh).cuda(), torch.from_numpy(xh).cuda(), torch.from_numpy(bh).cuda()
+    L = _capi.lib()
+    try:
+        ops.set_option("gemm_split", 0)
+        need0 = L.b200q_gemm_workspace_bytes(fmt, _capi.F32, M, N, K)
+        y0 = ops.gemm(fmt, W, X, N, bias=b)
+        ops.set_option("gemm_split", 1)
+        need1 = L.b200q_gemm_workspace_bytes(fmt, _capi.F32, M, N, K)
+        y1 = ops.gemm(fmt, W, X, N, bias=b)
+        y2 = ops.gemm(fmt, W, X, N, bias=b)
+        yh = ops.gemm(fmt, W, X.half(), N, bias=b.half(), out_dtype=torch.float16)
+        ysmall = ops.gemm(fmt, W, X, N, bias=b, ws=torch.empty(need0, dtype=torch.uint8, device="cuda"))  # room for the image only
+    finally:
+        ops.set_option("gemm_split", 1)
+    torch.cuda.synchronize()
+    assert need1 > need0 and (need1 - need0) % (min(M, 512) * N * 4) == 0  # the partial sums of 2..8 splits
+    assert torch.equal(y1, y2)
+    assert torch.equal(ysmall, y0)  # given no room for partial sums the call runs unsplit
+    r = oracle.rel_l2(y1.cpu().numpy(), y0.cpu().numpy())
+    assert r < 1e-4, r  # the order of the FP32 additions alone
+    want = cpu_oracle.matmul(fmt, Wh, xh, threads=16) + bh[None, :]
+    assert oracle.rel_l2(y1.cpu().numpy(), want) < 2e-3
+    assert oracle.rel_l2(yh.float().cpu().numpy(), want) < 4e-3
     assert ops.device_status() == 0
 
 
