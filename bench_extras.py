@@ -479,6 +479,9 @@ def run(rank, world, peaks, stream):
         out["config3_q4k_prefill_512"] = [gemm_case(synth.Q4_K, 14336, 4096, 512, dt, stream, peaks)
                                           for dt in (torch.float32, torch.bfloat16)]
         out["prefill_other_formats_512"] = [gemm_case(f, 14336, 4096, 512, torch.float32, stream, peaks) for f in (synth.Q6_K, synth.Q8_0)]
+        # the other matrices of the layer at 512 tokens: 32 and 8 row tiles, k range split over CTA pairs
+        out["prefill_layer_set_512"] = [gemm_case(fmt, N, K, 512, torch.float32, stream, peaks, n_launch=6) | {"name": name}
+                                        for name, fmt, N, K in synth.LLAMA3_8B_LAYER_SET if name in ("q_proj", "k_proj", "down_proj")]
         out["layer_set_grouped"] = grouped_layer_set(stream, peaks["hbm_gbs"])
         out["dequant_to_fp16_4096x4096"] = [dequant_case(f, 4096, 4096, stream, peaks["hbm_gbs"]) for f in (synth.Q4_K, synth.Q6_K, synth.Q8_0)]
         out["repack_q6k_down_proj"] = repack_case(stream, peaks["hbm_gbs"])
