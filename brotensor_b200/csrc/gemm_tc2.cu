@@ -313,7 +313,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_tc2_kernel(const PairPar
         const uint8_t* rowp = p.W + (size_t)wrow * p.row_bytes + (size_t)blockIdx.y * p.w_split_bytes;
         const uint32_t r7 = (uint32_t)(pt & 7);
         const uint32_t row_off = (uint32_t)((pt >> 3) * 1024 + (pt & 7) * 128);
-        const int n_blk = p.K / 256;
+        const int n_blk = n_kb / 4;  // blocks of this CTA's k range (the prefetch must not run past it: the last row ends there)
         int slot = 0;
         uint32_t phase = 0;
         bool live = true;
