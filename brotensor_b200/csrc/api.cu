@@ -439,6 +439,22 @@ int b200q_gemm(int fmt, const void* W, const void* X, int x_dtype, const void* b
     DevInfo* d;
     if (int rc = dev_info(&d)) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // Nine to sixteen rows: the tensor-core GEMM's producers decode the whole matrix for however few tokens
+    // (14336 x 4096: 46-48 us for any M up to 32), two passes of the small-batch GEMV on the integer tensor
+    // cores take 28-30 us (Q4_K, Q8_0; 4096 x 4096: 14-15 against 18-20), and for Q6_K from 8192 rows two
+    // passes of the warp-MMA GEMV 53-55 against 67. From 24 rows the GEMM is the faster one.
+    if (g_opt_gemm_path == 0 && M > 8 && M <= 16 && K <= 4096 &&
+        (((fmt == kQ4_K || fmt == kQ8_0) && (K == 2048 || K == 4096) && i8_get_enabled()) || (fmt == kQ6_K && N >= 8192))) {
+        const size_t xs = (size_t)dt_size(x_dtype) * K, ys = (size_t)dt_size(y_dtype) * N;
+        for (int m0 = 0; m0 < M; m0 += 8) {
+            const int mm = M - m0 < 8 ? M - m0 : 8;
+            if (int rc = b200q_gemv(fmt, W, static_cast<const char*>(X) + xs * m0, x_dtype, bias,
+                                    static_cast<char*>(Y) + ys * m0, y_dtype, mm, N, K, stream))
+                return rc;
+        }
+        d->tc_calls[fmt_slot(fmt)].fetch_add(1);  // mma.sync on the tensor cores, int8 or FP16
+        return B200Q_OK;
+    }
     if (g_opt_gemm_path != 1) {
         bool taken = false;
         if (int rc = launch_gemm_tc(fmt, W, X, x_dtype, bias, Y, y_dtype, M, N, K, ws, ws_bytes, d->sms, d->status, st, &taken))

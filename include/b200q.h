@@ -279,6 +279,9 @@ int b200q_device_status(int* status_out);
  *   "gemv_groups" pipelines per CTA of the integer-dot kernel (1 or 2); "gemv_tile_pairs" 2 = prefer
  *                 one pipeline with 32-row tiles; "gemv_split_full" (Q6_K only) -1 = automatic, 0 = one full
  *                 barrier per stage, 1 = one per consumer warp and stage
+ *   "gemm_path"   0 = automatic (tcgen05 GEMM from 9 rows, except 9..16 rows of Q4_K / Q8_0 with K = 2048 / 4096 and
+ *                 of Q6_K from 8192 weight rows, which run as two passes of the small-batch GEMV), 1 = passes of the
+ *                 decode GEMV only, 2 = the tcgen05 GEMM or an error
  *   "gemm_pair"   0 = one-CTA tcgen05 kernel, otherwise the CTA-pair kernel (default)
  *   "gemm_split"  0 = never split K; 1 (default) = matrices whose row tiles occupy at most half of the SMs
  *                 (N <= 9472) have their k-blocks split over up to eight CTA pairs, partial sums added in a

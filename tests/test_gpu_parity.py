@@ -381,6 +381,40 @@ def test_gemm_cta_pair_equals_single_cta(fmt, N, K, M, cpu_oracle):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("fmt,N,K,M", [(synth.Q4_K, 600, 4096, 16), (synth.Q8_0, 333, 2048, 9), (synth.Q6_K, 8192, 2048, 12),
+                                       (synth.Q4_K, 14336, 4096, 13)])
+def test_gemm_of_nine_to_sixteen_rows(fmt, N, K, M, cpu_oracle):
+    """9..16 rows of these shapes run as two passes of the small-batch GEMV instead of the tcgen05 GEMM (the faster
+    form there): within the GEMV's bound of the oracle, close to the tensor-core GEMM, counted as a tensor-core
+    call, bias and 16-bit types included, no workspace needed."""
+    import torch
+    import oracle
+    Wh = synth.make_blocks(fmt, N, K, seed=N + M)
+    xh = synth.make_activations(M, K, seed=M)
+    bh = synth.make_activations(1, N, seed=5).reshape(-1)
+    W, X, b = torch.from_numpy(Wh).cuda(), torch.from_numpy(xh).cuda(), torch.from_numpy(bh).cuda()
+    try:
+        ops.set_option("gemm_path", 2)
+        y_tc = ops.gemm(fmt, W, X, N, bias=b)
+        ops.set_option("gemm_path", 0)
+        ops.tc_calls_consume(fmt)
+        y = ops.gemm(fmt, W, X, N, bias=b)
+        assert ops.tc_calls_consume(fmt) == 1
+        yh = ops.gemm(fmt, W, X.half(), N, bias=b.half(), out_dtype=torch.float16)
+    finally:
+        ops.set_option("gemm_path", 0)
+    rows = np.arange(0, N, max(1, N // 500))
+    want = cpu_oracle.matmul(fmt, Wh.reshape(N, -1)[rows].reshape(-1), xh, threads=16) + bh[None, rows]
+    cols = torch.from_numpy(rows).cuda()
+    assert oracle.rel_l2(y[:, cols].cpu().numpy(), want) < 2e-3
+    assert oracle.rel_l2(yh[:, cols].float().cpu().numpy(), want) < 2e-3
+    assert oracle.rel_l2(y.cpu().numpy(), y_tc.cpu().numpy()) < 2e-3  # FP16 operands there, fixed-point activations here
+    for m0 in range(0, M, 8):
+        assert torch.equal(y[m0:m0 + 8], ops.gemv(fmt, W, X[m0:m0 + 8].contiguous(), N, bias=b))
+    assert ops.device_status() == 0
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("fmt,N,K,M", [(synth.Q4_K, 1024, 1024, 272), (synth.Q4_K, 4096, 4096, 512), (synth.Q6_K, 4096, 14336, 200),
                                        (synth.Q8_0, 1000, 4096, 64), (synth.Q4_K, 2048, 2048, 600), (synth.Q6_K, 300, 8192, 17)])
 def test_gemm_split_k(fmt, N, K, M, cpu_oracle):
