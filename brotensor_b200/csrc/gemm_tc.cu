@@ -267,7 +267,10 @@ int launch_gemm_tc(int fmt, const void* W, const void* X, int x_dtype, const voi
     *taken = gemm_tc_takes(fmt, W, M, K);
     if (!*taken) return B200Q_OK;
     const size_t need = gemm_tc_workspace_min_bytes(fmt, x_dtype, M, N, K);
-    const int n_split = ws && ws_bytes >= gemm_tc_workspace_bytes(fmt, x_dtype, M, N, K) ? gemm_split_factor(fmt, N, K) : 1;
+    // (the reduction kernel moves four neighbouring outputs at a time: Y and an FP32 bias must be aligned for that)
+    const bool quads_ok = (reinterpret_cast<uintptr_t>(Y) & (y_dtype == B200Q_DT_F32 ? 15 : 3)) == 0 &&
+                          (!bias || x_dtype != B200Q_DT_F32 || (reinterpret_cast<uintptr_t>(bias) & 15) == 0);
+    const int n_split = ws && quads_ok && ws_bytes >= gemm_tc_workspace_bytes(fmt, x_dtype, M, N, K) ? gemm_split_factor(fmt, N, K) : 1;
     if (!ws || ws_bytes < need) return fail(B200Q_ERR_WORKSPACE, "gemm: workspace of %zu bytes needed, %zu given", need, ws ? ws_bytes : (size_t)0);
     if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(B200Q_ERR_WORKSPACE, "gemm: workspace must be 256-byte aligned");
     const int tok_total = round_up16(M);

@@ -381,6 +381,29 @@ def test_gemm_cta_pair_equals_single_cta(fmt, N, K, M, cpu_oracle):
 
 
 @pytest.mark.gpu
+def test_gemm_split_k_needs_aligned_outputs():
+    """The reduction after a split K moves four outputs at a time; a result or FP32 bias that is only aligned to its
+    element size gets the unsplit kernel (bit for bit), not a misaligned access."""
+    import torch
+    fmt, N, K, M = synth.Q4_K, 1024, 4096, 40
+    W = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=9)).cuda()
+    X = torch.from_numpy(synth.make_activations(M, K, seed=9)).cuda()
+    b = torch.from_numpy(synth.make_activations(1, N + 1, seed=5).reshape(-1)).cuda()
+    try:
+        ops.set_option("gemm_split", 0)
+        y0 = ops.gemm(fmt, W, X, N, bias=b[1:].clone())
+    finally:
+        ops.set_option("gemm_split", 1)
+    big = torch.zeros(M * N + 1, dtype=torch.float32, device="cuda")
+    y_off = big[1:].view(M, N)                      # 4-byte aligned only
+    ops.gemm(fmt, W, X, N, bias=b[1:].clone(), out=y_off)
+    assert torch.equal(y_off, y0)
+    y_b = ops.gemm(fmt, W, X, N, bias=b[1:])        # bias 4-byte aligned only
+    assert torch.equal(y_b, y0)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("fmt,N,K,M", [(synth.Q4_K, 600, 4096, 16), (synth.Q8_0, 333, 2048, 9), (synth.Q6_K, 8192, 2048, 12),
                                        (synth.Q4_K, 14336, 4096, 13)])
 def test_gemm_of_nine_to_sixteen_rows(fmt, N, K, M, cpu_oracle):
