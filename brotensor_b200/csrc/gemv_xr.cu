@@ -27,7 +27,9 @@
 // A variant sized for two CTAs per SM (7 or 8 warps, half the shared memory), so that the next launch
 // of the stream could move in beside the running one and prefetch, was measured too: it is slower
 // (7.6-8.5 us) - half of the SM's warps sit parked in griddepcontrol.wait, and the items are bound
-// by instruction issue, not by memory.
+// by instruction issue, not by memory. Giving the one pair that a CTA with 16 n + 1 pairs ends on (14336 rows:
+// 48 or 49 pairs per CTA; the 49th costs one warp 0.54 us while fifteen wait) to two warps, a row each, was
+// measured as well: 6.87 against 6.74 us - the bookkeeping in every item costs more than the shorter tail saves.
 //
 // Q6_K (K = 2048 or 4096) runs through the same kernel with the half-group work unit of gemv_dp.cu: a lane
 // keeps the 64 activations of its half group of each 2048-element slice, their 16-element sums and the
