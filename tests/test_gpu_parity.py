@@ -381,6 +381,38 @@ def test_gemm_cta_pair_equals_single_cta(fmt, N, K, M, cpu_oracle):
 
 
 @pytest.mark.gpu
+def test_gemm_seeded_shapes_against_the_oracle(cpu_oracle):
+    """Two dozen seeded shapes across the prefill routes (tcgen05 pairs with and without a split K, GEMV passes for
+    small M, odd row counts, several passes of 512 tokens, every format the tensor-core kernel takes, bias on or
+    off, FP32 / FP16 / BF16 activations): each within the prefill bound of the oracle and the same on a second run."""
+    import torch
+    import oracle
+    rng = np.random.default_rng(20240611)
+    fmts = [synth.Q4_K, synth.Q6_K, synth.Q8_0]
+    for case in range(24):
+        fmt = fmts[case % 3]
+        N = int(rng.choice([1, 7, 64, 100, 129, 255, 256, 300, 511, 1000, 1028, 2052, 4096]))
+        K = 256 * int(rng.choice([1, 2, 3, 4, 8, 12, 16, 32]))
+        M = int(rng.choice([9, 12, 16, 17, 31, 64, 100, 257, 513, 600]))
+        if N * K * M > 1.5e9:
+            M = 17
+        dt = [torch.float32, torch.float16, torch.bfloat16][int(rng.integers(0, 3))]
+        with_bias = bool(rng.integers(0, 2))
+        Wh = synth.make_blocks(fmt, N, K, seed=1000 + case)
+        xh = synth.make_activations(M, K, seed=2000 + case)
+        bh = synth.make_activations(1, N, seed=3000 + case).reshape(-1)
+        W, X = torch.from_numpy(Wh).cuda(), torch.from_numpy(xh).cuda().to(dt)
+        b = torch.from_numpy(bh).cuda().to(dt) if with_bias else None
+        y1 = ops.gemm(fmt, W, X, N, bias=b)
+        y2 = ops.gemm(fmt, W, X, N, bias=b)
+        assert torch.equal(y1, y2), (case, fmt, N, K, M)
+        want = cpu_oracle.matmul(fmt, Wh, X.float().cpu().numpy(), bias=b.float().cpu().numpy() if with_bias else None, threads=16)
+        r = oracle.rel_l2(y1.float().cpu().numpy(), want)
+        assert r < 2e-3, (case, fmt, N, K, M, str(dt), with_bias, r)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.gpu
 def test_gemm_split_k_needs_aligned_outputs():
     """The reduction after a split K moves four outputs at a time; a result or FP32 bias that is only aligned to its
     element size gets the unsplit kernel (bit for bit), not a misaligned access."""
