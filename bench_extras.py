@@ -57,8 +57,11 @@ def gemv_case(fmt, N, K, M, stream, peak_gbs, n_launch=48):
             "frac_of_hbm_peak": gbs / peak_gbs, "replicas": len(Ws)}
 
 
-def gemm_case(fmt, N, K, M, x_dtype, stream, peaks, n_launch=8):
+def gemm_case(fmt, N, K, M, x_dtype, stream, peaks, n_launch=8, regrouped=False):
     W = torch.from_numpy(synth.make_blocks(fmt, N, K, seed=3)).cuda()
+    if regrouped:  # the device-side regrouped layout of the same blocks (b200q_repack)
+        W = ops.repack(fmt, W, N, K)
+        fmt = ops.repacked_fmt(fmt, K)
     X = torch.from_numpy(synth.make_activations(M, K, seed=3)).cuda().to(x_dtype)
     Y = torch.empty((M, N), dtype=torch.float32, device="cuda")
     from brotensor_b200 import _capi
@@ -332,8 +335,8 @@ def repack_case(stream, peak_gbs, N=4096, K=14336, R=12):
     med, _ = _time_graph(rp, 12, stream)
     res["repack_us"] = med * 1e3
     res["repack_GBps_read_plus_written"] = 2 * nbytes / (med * 1e-3) / 1e9
-    res["note"] = ("opt-in at load (brotensor_b200::repack_weights, gguf::upload_rows_repacked); the prefill GEMM is "
-                   "faster on the GGUF layout, so the loader keeps it unless asked")
+    res["note"] = ("opt-in at load (brotensor_b200::repack_weights, gguf::upload_rows_repacked): a regrouped weight has no "
+                   "raw host image to read back, so the loader keeps the GGUF layout unless asked")
     return res
 
 
@@ -479,6 +482,7 @@ def run(rank, world, peaks, stream):
         out["config3_q4k_prefill_512"] = [gemm_case(synth.Q4_K, 14336, 4096, 512, dt, stream, peaks)
                                           for dt in (torch.float32, torch.bfloat16)]
         out["prefill_other_formats_512"] = [gemm_case(f, 14336, 4096, 512, torch.float32, stream, peaks) for f in (synth.Q6_K, synth.Q8_0)]
+        out["prefill_q6k_regrouped_512"] = gemm_case(synth.Q6_K, 14336, 4096, 512, torch.float32, stream, peaks, regrouped=True)
         # the other matrices of the layer at 512 tokens: 32 and 8 row tiles, k range split over CTA pairs
         out["prefill_layer_set_512"] = [gemm_case(fmt, N, K, 512, torch.float32, stream, peaks, n_launch=6) | {"name": name}
                                         for name, fmt, N, K in synth.LLAMA3_8B_LAYER_SET if name in ("q_proj", "k_proj", "down_proj")]
