@@ -619,13 +619,16 @@ int launch_gemm_pair_pass(int fmt, const void* W, const uint8_t* Xp, int tok_str
     const int groups = p.tok_pad > 256 ? 2 : 1;
     p.g_bytes = (n0 / 2) * 128;
     p.b_bytes = p.g_bytes * groups;
-    // Ring depths: slabs four k-blocks ahead (they come from L2 with about a microsecond of
-    // latency), decoded weights in the rest so the producers can hide their block loads.
-    const unsigned budget = 227u * 1024u - 2048u;
+    // Ring depths: slabs three k-blocks ahead (they come from L2 with about a microsecond of latency), decoded
+    // weights in the rest - of 196 KB, not of all the shared memory an SM has: what the kernel leaves of the
+    // 256 KB array is the L1 its producers' weight loads go through, and the carve-out steps from 196 KB to the
+    // full size at once. With 224 KB of rings (6 + 4 slots at 512 tokens) the L1 is ~28 KB and the Q6_K
+    // producers, whose rows advance through 27 KB per block step, miss in it: Q6_K 85.4 us, its regrouped
+    // layout 89.0; with 192 KB (6 + 3) 81.7 and 68.5; Q4_K 59.7 -> 59.1, Q8_0 67.5 -> 66.2 (512 x 14336 x 4096,
+    // one box). Two slabs cost Q4_K 12 us, fewer than five weight slots 2.
+    const unsigned budget = 196u * 1024u - 2048u;
     const unsigned kb_a = kGemmRows * 128;
-    // (Q6_K stages are twice as long - its decode sets the pace - so two slabs are the same lead in time, and
-    // two fewer in flight measured 3 % faster at 512 tokens: 82.0-82.4 against 84.1-85.5 us; Q4_K with two: 71 against 60)
-    p.n_b = (fmt == kQ6_K || fmt == kQ6_KP) ? 2 : 4;
+    p.n_b = 3;
     p.n_a = (int)((budget - (unsigned)p.n_b * (unsigned)p.b_bytes) / kb_a);
     if (p.n_a > kPairMaxStages) p.n_a = kPairMaxStages;
     if (p.n_a < p.n_b) return fail(B200Q_ERR_UNSUPPORTED, "gemm: pair rings do not fit (%d weight slots, %d slab stages)", p.n_a, p.n_b);
